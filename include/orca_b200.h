@@ -1,0 +1,270 @@
+/*
+ * orca_b200 -- C ABI of the B200 (sm_100a) implementation of Orca's per-batch temporal-embedding
+ * path.  Every entry point replaces one function of the reference (LuckyLYM/Orca, pure Python +
+ * numba); the reference location is cited beside each declaration.
+ *
+ * Conventions
+ *   - All functions return 0 on success or one of the ORCA_E_* codes; orca_last_error() gives the
+ *     message of the calling thread's last failure.
+ *   - Pointers named d_* are device pointers, h_* host pointers.  `stream` is a cudaStream_t passed
+ *     as void*.  Unless stated otherwise a function only enqueues work on `stream`, allocates
+ *     nothing and keeps no pointer after it returns (the reference replaces its state tensors
+ *     on restore, modules/memory.py:43, so state is passed per call).
+ *   - Row counts that are only known on the device (the number of uncached neighbours, the number
+ *     of unique positive nodes) are passed as a capacity `*_cap` plus a device pointer
+ *     `d_n_*`; kernels launched for the capacity read the count and idle beyond it.
+ *   - Feature width is fixed at 172 floats (node = memory = time = edge dimension) and the number
+ *     of heads at 2, the only widths the headline workloads use; ORCA_E_UNSUPPORTED otherwise.
+ *   - Ids are int32 on the device (node 0 and edge 0 are padding), times are float64 where the
+ *     reference keeps float64.
+ */
+#ifndef ORCA_B200_H
+#define ORCA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ORCA_OK 0
+#define ORCA_E_BADARG 1      /* null pointer, negative size, K out of range            */
+#define ORCA_E_UNSUPPORTED 2 /* dimension or mode this build has no kernel for          */
+#define ORCA_E_CUDA 3        /* a CUDA runtime call failed (message has the CUDA error) */
+#define ORCA_E_CAPACITY 4    /* a device-side count exceeded the capacity it was given  */
+#define ORCA_E_BOUNDS 5      /* a kernel met an id outside its table (debug checks)     */
+#define ORCA_E_TIMEOUT 6     /* a bounded device-side wait gave up                      */
+
+#define ORCA_DIM 172
+#define ORCA_HEADS 2
+#define ORCA_MAX_K 32
+#define ORCA_MSG_DIM (4 * ORCA_DIM)          /* [mem_src | mem_dst | edge feat | time enc] */
+#define ORCA_KEY_DIM (3 * ORCA_DIM)          /* [neighbour | edge feat | time enc]         */
+#define ORCA_QT_DIM (ORCA_HEADS * ORCA_KEY_DIM)
+
+const char *orca_last_error(void);
+int orca_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Time-sorted adjacency.  Replaces get_neighbor_finder (utils/util.py:91-105): every edge is
+ * listed under both endpoints; each node's list is stably sorted by timestamp with insertion
+ * order = stream order, the source-side entry of an edge ahead of its destination-side entry.
+ * Host function (runs on the CPU, once per graph).  indptr has n_nodes+1 entries, the other
+ * three outputs 2*n_edges entries.
+ */
+int orca_csr_build_host(const int64_t *h_src, const int64_t *h_dst, const int64_t *h_eidx,
+                        const double *h_ts, int64_t n_edges, int64_t n_nodes, int64_t *h_indptr,
+                        int32_t *h_nbr, int32_t *h_eid, double *h_adj_ts);
+
+/* ------------------------------------------------------------------------------------------
+ * Temporal neighbour sampling.  Replaces NeighborFinder.get_temporal_neighbor and find_before
+ * (utils/util.py:129-151): per query the interactions strictly before the query time, the last k
+ * of them, right-aligned, zero-padded on the left.  Outputs are [n_query_cap, k] row-major;
+ * d_edge_times (float32, the reference's return dtype) and d_delta may be NULL.  d_delta is the
+ * fused time difference of modules/embedding_module.py:266-267: float32(t_query - float64(
+ * float32(t_edge))), and t_query itself on padded slots.
+ * d_n_query may be NULL (then all n_query_cap rows are queries).
+ */
+int orca_sample_topk(const int64_t *d_indptr, const int32_t *d_adj_nbr, const int32_t *d_adj_eid,
+                     const double *d_adj_ts, int64_t n_nodes, const int32_t *d_nodes,
+                     const double *d_ts, int32_t n_query_cap, const int32_t *d_n_query, int32_t k,
+                     int32_t *d_nbr, int32_t *d_eid, float *d_edge_times, float *d_delta,
+                     int32_t *d_status, void *stream);
+
+/* find_before (utils/util.py:129-131) on its own: the number of interactions of d_nodes[i]
+ * strictly before d_ts[i]. */
+int orca_find_before(const int64_t *d_indptr, const double *d_adj_ts, int64_t n_nodes,
+                     const int32_t *d_nodes, const double *d_ts, int32_t n_query,
+                     int32_t *d_count, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Uncached out-of-batch neighbours.  Replaces find_uncached_out_of_batch_neighbors
+ * (modules/embedding_module.py:200-212): ascending unique ids of the neighbour table that are not
+ * query nodes and whose cache flag is 0, minus the first entry.  The ids are APPENDED to the
+ * query list: d_nodes_io[n_query .. n_query+|U|) = U, d_ts_io likewise = max over the n_query
+ * timestamps (modules/embedding_module.py:253-257), and *d_n_total = n_query + |U|.
+ * If |U| > u_cap the surplus is dropped and ORCA_E_CAPACITY is written to *d_status.
+ * d_bitmap: scratch of orca_find_uncached_scratch_bytes(n_nodes) bytes.
+ */
+int64_t orca_find_uncached_scratch_bytes(int64_t n_nodes);
+int orca_find_uncached(const int32_t *d_nbr, int32_t n_query, int32_t k, const uint8_t *d_cache_flag,
+                       int64_t n_nodes, int32_t *d_nodes_io, double *d_ts_io, int32_t u_cap,
+                       int32_t *d_n_total, void *d_bitmap, int32_t *d_status, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Last-occurrence selection.  Replaces the np.unique(np.flip(nodes), return_index=True) rule of
+ * TGN.get_raw_messages (model/tgn_model.py:172-176) and gives History.push its deterministic
+ * winner (modules/history.py:38-40 under deterministic execution): d_is_last[i] = 1 iff no
+ * j > i has d_ids[j] == d_ids[i].
+ * d_last_pos: int64 [n_nodes] scratch owned by the caller, zero-initialised once; `epoch_base`
+ * must grow by at least n_cap between calls that share the scratch (no clearing is needed).
+ * If d_compact is non-NULL the positions with is_last == 1 are also written there in ascending
+ * position order and their number to *d_n_compact.
+ */
+int orca_last_occurrence(const int32_t *d_ids, int32_t n_cap, const int32_t *d_n, int64_t n_nodes,
+                         int64_t *d_last_pos, int64_t epoch_base, uint8_t *d_is_last,
+                         int32_t *d_compact, int32_t *d_n_compact, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Prepared weights of one attention layer (host side composes them once per weight update from
+ * the reference's parameters; see orca_b200/weights.py for the algebra):
+ *   qt   = h_src . Mq + cq                                  [*, 1032]  (scaled, K-projected query)
+ *   hid  = relu([ctx | h_src] . G + b1 + valid * g)         [*, 172]
+ *   out  = LayerNorm(hid . W2t + b2) * ln_w + ln_b          [*, 172]
+ * All matrices are row-major [in, out] float32.
+ */
+typedef struct {
+  const float *Mq;   /* [172, 1032]  */
+  const float *cq;   /* [1032]       */
+  const float *G;    /* [1204, 172]  */
+  const float *b1;   /* [172]        */
+  const float *g;    /* [172]        */
+  const float *W2t;  /* [172, 172]   */
+  const float *b2;   /* [172]        */
+  const float *ln_w; /* [172]        */
+  const float *ln_b; /* [172]        */
+} orca_attn_weights_t;
+
+/* Step 1 of TemporalAttentionLayer.forward (model/temporal_attention.py:41-48, the query side of
+ * nn.MultiheadAttention): qt[r] = feat[idx ? idx[r] : r] . Mq + cq. */
+int orca_attn_query(const orca_attn_weights_t *w, const float *d_feat, const int32_t *d_idx,
+                    int32_t n_rows_cap, const int32_t *d_n_rows, float *d_qt, void *stream);
+
+/* Step 2, the fused gather-attention kernel (model/temporal_attention.py:43-53 with
+ * model/time_encoding.py:23-28 and the gathers of modules/embedding_module.py:262-270 and
+ * modules/history.py:32-36): per row, gather the k neighbour rows of d_nbr_table and edge-feature
+ * rows, encode cos(delta * w_time), masked 2-head softmax over the slots, weighted key sum.
+ *   d_ctx   [n_rows_cap, 1032]   sum_j a_hj * [nbr_j | efeat_j | tenc_j] per head
+ *   d_valid [n_rows_cap]         0 where every slot is padding (the layer output of such a row
+ *                                ignores the attention term, model/temporal_attention.py:46,52)
+ */
+int orca_attn_gather(const float *d_qt, const float *d_nbr_table, const float *d_edge_table,
+                     const float *d_time_w, const int32_t *d_nbr, const int32_t *d_eid,
+                     const float *d_delta, int32_t k, int32_t n_rows_cap, const int32_t *d_n_rows,
+                     float *d_ctx, uint8_t *d_valid, int32_t *d_status, void *stream);
+
+/* Step 3 (out-projection, merger and LayerNorm, model/temporal_attention.py:48-55 and
+ * utils/util.py:21-24): d_out[r] = LN(fc2(relu(fc1([attn | h_src])))).  If d_push_table is
+ * non-NULL the row is also written to d_push_table[d_push_ids[r]] when d_push_win[r] != 0, which
+ * is History.push (modules/history.py:38-40) with the last occurrence of an id winning. */
+int orca_attn_output(const orca_attn_weights_t *w, const float *d_ctx, const uint8_t *d_valid,
+                     const float *d_feat, const int32_t *d_idx, int32_t n_rows_cap,
+                     const int32_t *d_n_rows, float *d_out, float *d_push_table,
+                     const int32_t *d_push_ids, const uint8_t *d_push_win, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Historical-embedding cache.  Replace History.pull / push / update_flag
+ * (modules/history.py:25-40).
+ */
+int orca_history_pull(const float *d_emb, const int32_t *d_ids, int64_t n, float *d_out, void *stream);
+/* rows with d_win[i] == 0 are skipped (pass the is_last flags of orca_last_occurrence) */
+int orca_history_push(float *d_emb, const float *d_x, const int32_t *d_ids, const uint8_t *d_win,
+                      int32_t n_cap, const int32_t *d_n, void *stream);
+/* cache_flag = 0 everywhere, then 1 on d_plan; the previous plan is passed so that only its
+ * entries are cleared (NULL/0 clears all n_nodes flags).  With d_plan == NULL the flags of
+ * d_ids are set and nothing is cleared (the reference's plan-less branch). */
+int orca_history_set_flags(uint8_t *d_cache_flag, int64_t n_nodes, const int32_t *d_prev_plan,
+                           int32_t n_prev, const int32_t *d_plan, int32_t n_plan, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Link scorer.  Replaces affinity_score + sigmoid of TGN.compute_edge_probabilities
+ * (model/tgn_model.py:154-157; MergeLayer utils/util.py:12-24).  d_emb is [3*b, 172] =
+ * [src | dst | neg]; d_prob is [2*b] = [pos | neg].
+ */
+typedef struct {
+  const float *W1t; /* [344, 172] */
+  const float *b1;  /* [172]      */
+  const float *w2;  /* [172]      */
+  float b2;
+} orca_score_weights_t;
+int orca_score(const orca_score_weights_t *w, const float *d_emb, int32_t b, float *d_prob, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Raw messages and memory update.
+ */
+typedef struct {
+  float *memory;       /* [n_nodes, 172]                    modules/memory.py:18 */
+  float *last_update;  /* [n_nodes]                         modules/memory.py:19 */
+  float *messages;     /* [n_nodes, 688]                    modules/memory.py:22 */
+  float *msg_ts;       /* [n_nodes]                         modules/memory.py:23 */
+  uint8_t *msg_flag;   /* [n_nodes], the `nodes` bool array modules/memory.py:21 */
+  int64_t n_nodes;
+} orca_memory_t;
+
+/* Replaces TGN.get_raw_messages + Memory.store_raw_messages (model/tgn_model.py:172-191,
+ * modules/memory.py:25-28).  d_cat_src/d_cat_dst are the 2*b concatenations [src|dst], [dst|src];
+ * position p carries time d_ts[p % b] and edge d_eidx[p % b].  d_win_pos/d_n_win are the compact
+ * winner positions from orca_last_occurrence.  Message of node a = cat_src[p]:
+ * [memory[a] | memory[cat_dst[p]] | efeat[e] | cos((float32(t) - last_update[a]) * w_time)].
+ * d_win_nodes (may be NULL) receives the node id of every winner, the list the memory update runs
+ * over. */
+int orca_message_store(const orca_memory_t *mem, const float *d_edge_table, const float *d_time_w,
+                       const int32_t *d_cat_src, const int32_t *d_cat_dst, const double *d_ts,
+                       const int32_t *d_eidx, int32_t b, const int32_t *d_win_pos, int32_t n_win_cap,
+                       const int32_t *d_n_win, int32_t *d_win_nodes, void *stream);
+
+/* GRU weights: Wg is [860, 688] = [message 688 ; memory 172] x [172 units x 4 gate columns
+ * (r, z, n_input, n_hidden) interleaved], bg [688] likewise. */
+typedef struct {
+  const float *Wg;
+  const float *bg;
+} orca_gru_weights_t;
+
+/* Replaces SequenceMemoryUpdater.update_memory / update_memory_in_test with nn.GRUCell
+ * (modules/memory_updater.py:25-53,86): for every listed node whose msg_flag is set:
+ * last_update = msg_ts, memory = GRU(messages, memory); if clear_flags the flag is cleared
+ * afterwards (Memory.clear_messages, modules/memory.py:49-50).  d_nodes may hold duplicates only if
+ * they are flagged once (the callers pass unique ids). */
+int orca_gru_update(const orca_gru_weights_t *w, const orca_memory_t *mem, const int32_t *d_nodes,
+                    int32_t n_cap, const int32_t *d_n, int32_t clear_flags, float *d_scratch_h,
+                    void *stream);
+int64_t orca_gru_scratch_bytes(int32_t n_cap);
+
+/* ------------------------------------------------------------------------------------------
+ * One whole eval batch: TGN.compute_edge_probabilities(..., reuse=True, train=False, cache_plan)
+ * with budget != 0 (model/tgn_model.py:95-157 over modules/embedding_module.py:215-285), enqueued
+ * on `stream` without any host synchronisation.
+ */
+typedef struct {
+  /* graph */
+  const int64_t *indptr; const int32_t *adj_nbr; const int32_t *adj_eid; const double *adj_ts;
+  const float *edge_table; int64_t n_nodes; int64_t n_edge_rows;
+  /* weights */
+  const float *time_w;
+  orca_attn_weights_t attn[2];
+  orca_score_weights_t score;
+  orca_gru_weights_t gru;
+  int32_t n_layers; int32_t k;
+  /* state */
+  orca_memory_t mem;
+  float *hist_emb;          /* [n_nodes,172] (n_layers == 2) */
+  uint8_t *cache_flag;      /* [n_nodes]                     */
+  int32_t *prev_plan;       /* [plan_cap] device copy of the plan whose flags are set */
+  int32_t *n_prev_plan;     /* host-resident counter owned by the caller              */
+  int32_t plan_cap;
+  int64_t *last_pos;        /* [n_nodes] scratch of orca_last_occurrence              */
+  int64_t *epoch_base;      /* host-resident counter owned by the caller              */
+} orca_tgn_t;
+
+/* Workspace sizing: bytes needed for batches of up to b_cap edges with at most u_cap uncached
+ * neighbours per batch. */
+int64_t orca_eval_workspace_bytes(int32_t b_cap, int32_t u_cap, int32_t k, int64_t n_nodes);
+
+/* d_batch_i32: [src | dst | neg | eidx] (4*b int32), d_batch_ts: [b] float64, d_plan: ids of the
+ * batch's cache plan (NULL = plan-less flag rule).  Outputs: d_prob [2*b] = [pos | neg] and, if
+ * non-NULL, d_emb_out [3*b,172] = [src | dst | neg] embeddings.  d_status: int32[4] device words
+ * (0 = ok; see orca_read_status). */
+int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const double *d_batch_ts,
+                        int32_t b, const int32_t *d_plan, int32_t n_plan, int32_t u_cap,
+                        void *d_workspace, int64_t workspace_bytes, float *d_prob,
+                        float *d_emb_out, int32_t *d_status, void *stream);
+
+/* Copies the device status words to the host (synchronises `stream`), returns the first nonzero
+ * code and resets the device words. h_counts (may be NULL) receives {status, n_layer1_rows,
+ * n_unique_positives, kernels launched by the last batch}. */
+int orca_read_status(int32_t *d_status, int32_t *h_counts, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ORCA_B200_H */

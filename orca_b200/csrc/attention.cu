@@ -1,0 +1,209 @@
+// The fused gather-attention kernel: for one query row, gather the K neighbour rows and K
+// edge-feature rows (688 B each) with bulk asynchronous copies into shared memory, compute the
+// time encoding cos(delta * w) while the copies fly, and run the masked two-head attention over
+// the K staged keys entirely on chip.  No weight matrix is touched: the K and V projections are
+// folded into the query (qt) and into the output GEMM, so this kernel is pure HBM traffic:
+//   in : qt row (4128 B) + up to K * (688 + 688) B of gathered rows + K * 12 B of indices
+//   out: ctx row (4128 B) + 1 flag
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace orca {
+
+constexpr int GA_THREADS = 256;
+constexpr int GA_WARPS = GA_THREADS / 32;
+constexpr unsigned GA_SPIN_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// 1-D bulk copy global -> shared, completion counted in bytes on `bar`.  Both addresses must be
+// 16-byte aligned and `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Shared memory layout (floats): qt[1032] | keys[K][516] | score[2][32] | weight[2][32]
+__global__ void __launch_bounds__(GA_THREADS)
+attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_table,
+                   const float *__restrict__ edge_table, const float *__restrict__ time_w,
+                   const int32_t *__restrict__ nbr, const int32_t *__restrict__ eid,
+                   const float *__restrict__ delta, int k, int n_cap, const int32_t *__restrict__ d_n,
+                   float *__restrict__ ctx, uint8_t *__restrict__ valid_out, int32_t *status) {
+  extern __shared__ __align__(128) float smem[];
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int s_nbr[ORCA_MAX_K];
+  __shared__ int s_eid[ORCA_MAX_K];
+  __shared__ float s_dt[ORCA_MAX_K];
+  __shared__ float s_logit[H][ORCA_MAX_K];
+  __shared__ float s_w[H][ORCA_MAX_K];
+
+  const int n = rows_of(n_cap, d_n);
+  float *s_qt = smem;
+  float *s_key = smem + QT;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  uint32_t parity = 0;
+
+  // persistent over rows: the grid is sized for the machine, not for the row capacity
+  for (int row = blockIdx.x; row < n; row += gridDim.x) {
+    if (tid < k) {
+      const size_t o = (size_t)row * k + tid;
+      s_nbr[tid] = nbr[o];
+      s_eid[tid] = eid[o];
+      s_dt[tid] = delta[o];
+    }
+    __syncthreads();
+
+    int n_valid = 0;
+    for (int j = 0; j < k; ++j) n_valid += (s_nbr[j] != 0);
+    if (n_valid == 0) {
+      // every slot is padding: the layer ignores the attention term for this row
+      if (tid == 0) valid_out[row] = 0;
+      __syncthreads();
+      continue;
+    }
+
+    if (tid == 0) {
+      // the previous row's reads of the staging area are ordered before these writes
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_expect_tx(&bar, (uint32_t)(QT * 4 + n_valid * 2 * ROW_BYTES));
+      bulk_g2s(s_qt, qt + (size_t)row * QT, QT * 4, &bar);
+      for (int j = 0; j < k; ++j) {
+        if (s_nbr[j] != 0) {
+          bulk_g2s(s_key + j * KEY, nbr_table + (size_t)s_nbr[j] * D, ROW_BYTES, &bar);
+          bulk_g2s(s_key + j * KEY + D, edge_table + (size_t)s_eid[j] * D, ROW_BYTES, &bar);
+        }
+      }
+    }
+    // time encoding of the valid slots while the copies are in flight (cosf with full range
+    // reduction: delta * w reaches 1e8)
+    for (int i = tid; i < k * D; i += GA_THREADS) {
+      const int j = i / D, d = i - j * D;
+      if (s_nbr[j] != 0) s_key[j * KEY + 2 * D + d] = cosf(s_dt[j] * __ldg(time_w + d));
+    }
+    // bounded wait for the gathered rows
+    {
+      unsigned spins = 0;
+      while (!mbar_try_wait(&bar, parity)) {
+        if (++spins > GA_SPIN_LIMIT) {
+          report(status, ORCA_E_TIMEOUT, row);
+          break;
+        }
+      }
+      parity ^= 1u;
+    }
+    __syncthreads();
+
+    // logits: one warp per slot, both heads
+    for (int j = warp; j < k; j += GA_WARPS) {
+      if (s_nbr[j] == 0) continue;
+      const float4 *kv = reinterpret_cast<const float4 *>(s_key + j * KEY);
+      const float4 *q0 = reinterpret_cast<const float4 *>(s_qt);
+      const float4 *q1 = reinterpret_cast<const float4 *>(s_qt + KEY);
+      float a0 = 0.f, a1 = 0.f;
+      for (int c = lane; c < KEY / 4; c += 32) {
+        const float4 x = kv[c], y0 = q0[c], y1 = q1[c];
+        a0 += x.x * y0.x + x.y * y0.y + x.z * y0.z + x.w * y0.w;
+        a1 += x.x * y1.x + x.y * y1.y + x.z * y1.z + x.w * y1.w;
+      }
+      a0 = warp_sum(a0);
+      a1 = warp_sum(a1);
+      if (lane == 0) {
+        s_logit[0][j] = a0;
+        s_logit[1][j] = a1;
+      }
+    }
+    __syncthreads();
+    // softmax over the valid slots, one warp per head
+    if (warp < H) {
+      const bool on = lane < k && s_nbr[lane] != 0;
+      const float v = on ? s_logit[warp][lane] : -INFINITY;
+      float m = v;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      const float e = on ? expf(v - m) : 0.f;
+      const float sum = warp_sum(e);
+      if (lane < k) s_w[warp][lane] = e / sum;
+    }
+    __syncthreads();
+    // weighted key sum, both heads
+    float *out = ctx + (size_t)row * QT;
+    for (int c = tid; c < KEY; c += GA_THREADS) {
+      float a0 = 0.f, a1 = 0.f;
+      for (int j = 0; j < k; ++j) {
+        if (s_nbr[j] != 0) {
+          const float x = s_key[j * KEY + c];
+          a0 += s_w[0][j] * x;
+          a1 += s_w[1][j] * x;
+        }
+      }
+      out[c] = a0;
+      out[KEY + c] = a1;
+    }
+    if (tid == 0) valid_out[row] = 1;
+    __syncthreads();
+  }
+}
+
+}  // namespace orca
+
+using namespace orca;
+
+extern "C" int orca_attn_gather(const float *d_qt, const float *d_nbr_table, const float *d_edge_table,
+                                const float *d_time_w, const int32_t *d_nbr, const int32_t *d_eid,
+                                const float *d_delta, int32_t k, int32_t n_rows_cap,
+                                const int32_t *d_n_rows, float *d_ctx, uint8_t *d_valid,
+                                int32_t *d_status, void *stream) {
+  ORCA_CHECK_ARG(d_qt && d_nbr_table && d_edge_table && d_time_w && d_nbr && d_eid && d_delta && d_ctx &&
+                 d_valid);
+  ORCA_CHECK_ARG(k >= 1 && k <= ORCA_MAX_K && n_rows_cap >= 0);
+  ORCA_CHECK_ARG(((uintptr_t)d_qt % 16 == 0) && ((uintptr_t)d_nbr_table % 16 == 0) &&
+                 ((uintptr_t)d_edge_table % 16 == 0));
+  if (n_rows_cap == 0) return ORCA_OK;
+  const size_t smem = (size_t)(QT + k * KEY) * sizeof(float);
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  ORCA_CUDA(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    ORCA_CUDA(cudaFuncSetAttribute(attn_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (QT + ORCA_MAX_K * KEY) * (int)sizeof(float)));
+    configured_device = dev;
+  }
+  attn_gather_kernel<<<std::min(n_rows_cap, 148 * 8), GA_THREADS, smem, (cudaStream_t)stream>>>(
+      d_qt, d_nbr_table, d_edge_table, d_time_w, d_nbr, d_eid, d_delta, k, n_rows_cap, d_n_rows, d_ctx,
+      d_valid, d_status);
+  ORCA_COUNT_LAUNCH();
+  ORCA_LAUNCH_CHECK();
+  return ORCA_OK;
+}

@@ -1,0 +1,66 @@
+// Shared helpers of the orca_b200 kernels: error reporting, launch checks, small device utilities.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/orca_b200.h"
+
+namespace orca {
+
+constexpr int D = ORCA_DIM;          // 172 floats = 688 bytes = 43 x 16 bytes
+constexpr int H = ORCA_HEADS;        // 2
+constexpr int KEY = ORCA_KEY_DIM;    // 516
+constexpr int QT = ORCA_QT_DIM;      // 1032
+constexpr int MSG = ORCA_MSG_DIM;    // 688
+constexpr int ROW_BYTES = D * 4;     // 688
+
+// status word layout (int32[4]): [0] first error code, [1] rows at layer 1, [2] unique positives,
+// [3] detail of the error (row / id)
+int set_error(int code, const char *fmt, ...);
+
+#define ORCA_CHECK_ARG(cond)                                                        \
+  do {                                                                              \
+    if (!(cond)) return orca::set_error(ORCA_E_BADARG, "%s: bad argument: %s", __func__, #cond); \
+  } while (0)
+
+#define ORCA_CUDA(call)                                                             \
+  do {                                                                              \
+    cudaError_t e_ = (call);                                                        \
+    if (e_ != cudaSuccess)                                                          \
+      return orca::set_error(ORCA_E_CUDA, "%s: %s failed: %s", __func__, #call,     \
+                             cudaGetErrorString(e_));                               \
+  } while (0)
+
+#define ORCA_LAUNCH_CHECK()                                                         \
+  do {                                                                              \
+    cudaError_t e_ = cudaGetLastError();                                            \
+    if (e_ != cudaSuccess)                                                          \
+      return orca::set_error(ORCA_E_CUDA, "%s: kernel launch failed: %s", __func__, \
+                             cudaGetErrorString(e_));                               \
+  } while (0)
+
+// number of kernels launched by this thread since the counter was last reset
+int &launch_counter();
+#define ORCA_COUNT_LAUNCH() (++orca::launch_counter())
+
+__device__ __forceinline__ int rows_of(int cap, const int32_t *d_n) {
+  if (d_n == nullptr) return cap;
+  int n = *d_n;
+  return n < cap ? n : cap;
+}
+
+__device__ __forceinline__ void report(int32_t *status, int code, int detail) {
+  if (status != nullptr && atomicCAS(status, 0, code) == 0) status[3] = detail;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace orca

@@ -1,0 +1,219 @@
+// One eval batch of the budgeted-reuse path, enqueued on a stream without host synchronisation:
+// sample -> find uncached -> sample -> attention layer 1 (memory rows) -> history push / flags ->
+// attention layer 2 (history rows) -> link scores -> raw messages -> GRU memory update.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace orca {
+
+static inline size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct Workspace {
+  int32_t *nodes1; double *ts1; int32_t *n1;
+  int32_t *nbr2, *eid2; float *dt2;
+  int32_t *nbr1, *eid1; float *dt1;
+  uint8_t *win1, *valid;
+  float *qt, *ctx, *emb1, *emb2;
+  int32_t *cat_dst; uint8_t *is_last2; int32_t *win_pos; int32_t *n_win; int32_t *win_nodes;
+  float *gru_h;
+  void *bitmap;
+  size_t bytes;
+};
+
+static Workspace carve(void *base, int b_cap, int u_cap, int k, int64_t n_nodes) {
+  Workspace w{};
+  size_t off = 0;
+  char *p = (char *)base;
+  const size_t N = 3 * (size_t)b_cap, R1 = N + (size_t)u_cap;
+  auto take = [&](size_t bytes) { void *r = p ? p + off : nullptr; off += align_up(bytes); return r; };
+  w.nodes1 = (int32_t *)take(R1 * 4);
+  w.ts1 = (double *)take(R1 * 8);
+  w.n1 = (int32_t *)take(4);
+  w.nbr2 = (int32_t *)take(N * k * 4);
+  w.eid2 = (int32_t *)take(N * k * 4);
+  w.dt2 = (float *)take(N * k * 4);
+  w.nbr1 = (int32_t *)take(R1 * k * 4);
+  w.eid1 = (int32_t *)take(R1 * k * 4);
+  w.dt1 = (float *)take(R1 * k * 4);
+  w.win1 = (uint8_t *)take(R1);
+  w.valid = (uint8_t *)take(R1);
+  w.qt = (float *)take(R1 * QT * 4);
+  w.ctx = (float *)take(R1 * QT * 4);
+  w.emb1 = (float *)take(R1 * D * 4);
+  w.emb2 = (float *)take(N * D * 4);
+  w.cat_dst = (int32_t *)take(2 * (size_t)b_cap * 4);
+  w.is_last2 = (uint8_t *)take(2 * (size_t)b_cap);
+  w.win_pos = (int32_t *)take(2 * (size_t)b_cap * 4);
+  w.n_win = (int32_t *)take(4);
+  w.win_nodes = (int32_t *)take(2 * (size_t)b_cap * 4);
+  w.gru_h = (float *)take(2 * (size_t)b_cap * D * 4);
+  w.bitmap = take((size_t)orca_find_uncached_scratch_bytes(n_nodes));
+  w.bytes = off;
+  return w;
+}
+
+// nodes1[0..3b) = [src|dst|neg], ts1[r] = ts[r % b], cat_dst = [dst|src]
+__global__ void batch_prep_kernel(const int32_t *__restrict__ batch, const double *__restrict__ ts, int b,
+                                  int32_t *__restrict__ nodes1, double *__restrict__ ts1,
+                                  int32_t *__restrict__ cat_dst, int32_t *__restrict__ n1) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < 3 * b) {
+    nodes1[i] = batch[i];
+    ts1[i] = ts[i % b];
+  }
+  if (i < 2 * b) cat_dst[i] = i < b ? batch[b + i] : batch[i - b];
+  if (i == 0) *n1 = 3 * b;
+}
+
+__global__ void copy_i32_kernel(const int32_t *__restrict__ src, int32_t *__restrict__ dst, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = src[i];
+}
+
+__global__ void set_flags_counted_kernel(uint8_t *__restrict__ flag, int64_t n_nodes,
+                                         const int32_t *__restrict__ ids, int cap, const int32_t *d_n) {
+  const int n = rows_of(cap, d_n);
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int v = ids[i];
+    if (v >= 0 && v < n_nodes) flag[v] = 1;
+  }
+}
+
+__global__ void publish_counts_kernel(const int32_t *n1, const int32_t *n_win, int32_t *status) {
+  status[1] = *n1;
+  status[2] = *n_win;
+}
+
+static thread_local int g_last_batch_launches = 0;
+
+}  // namespace orca
+
+using namespace orca;
+
+#define ORCA_TRY(call)        \
+  do {                        \
+    int rc_ = (call);         \
+    if (rc_ != ORCA_OK) return rc_; \
+  } while (0)
+
+extern "C" {
+
+int64_t orca_eval_workspace_bytes(int32_t b_cap, int32_t u_cap, int32_t k, int64_t n_nodes) {
+  if (b_cap <= 0 || u_cap < 0 || k < 1 || k > ORCA_MAX_K || n_nodes <= 0) return -1;
+  return (int64_t)carve(nullptr, b_cap, u_cap, k, n_nodes).bytes;
+}
+
+int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const double *d_batch_ts,
+                        int32_t b, const int32_t *d_plan, int32_t n_plan, int32_t u_cap,
+                        void *d_workspace, int64_t workspace_bytes, float *d_prob,
+                        float *d_emb_out, int32_t *d_status, void *stream) {
+  ORCA_CHECK_ARG(m && d_batch_i32 && d_batch_ts && d_workspace && d_prob && d_status);
+  ORCA_CHECK_ARG(b > 0 && u_cap >= 0 && n_plan >= 0);
+  ORCA_CHECK_ARG(m->n_layers == 1 || m->n_layers == 2);
+  ORCA_CHECK_ARG(m->k >= 1 && m->k <= ORCA_MAX_K);
+  ORCA_CHECK_ARG(m->last_pos && m->epoch_base && *m->epoch_base > 0);
+  if (m->n_layers == 2) ORCA_CHECK_ARG(m->hist_emb && m->cache_flag && m->n_prev_plan && (n_plan == 0 || m->prev_plan));
+  if (m->n_layers == 2) ORCA_CHECK_ARG(n_plan <= m->plan_cap);
+  const int k = m->k;
+  if (m->n_layers == 1) u_cap = 0;
+  Workspace w = carve(d_workspace, b, u_cap, k, m->n_nodes);
+  if ((int64_t)w.bytes > workspace_bytes)
+    return set_error(ORCA_E_CAPACITY, "orca_tgn_eval_batch: workspace of %lld bytes, %lld needed",
+                     (long long)workspace_bytes, (long long)w.bytes);
+  cudaStream_t s = (cudaStream_t)stream;
+  launch_counter() = 0;
+  const int N = 3 * b, R1 = N + u_cap;
+
+  batch_prep_kernel<<<ceil_div(N, 256), 256, 0, s>>>(d_batch_i32, d_batch_ts, b, w.nodes1, w.ts1, w.cat_dst, w.n1);
+  ORCA_COUNT_LAUNCH();
+  ORCA_LAUNCH_CHECK();
+
+  float *emb_top = d_emb_out ? d_emb_out : w.emb2;
+  if (m->n_layers == 1) {
+    ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
+                              nullptr, k, w.nbr1, w.eid1, nullptr, w.dt1, d_status, s));
+    ORCA_TRY(orca_attn_query(&m->attn[0], m->mem.memory, w.nodes1, N, nullptr, w.qt, s));
+    ORCA_TRY(orca_attn_gather(w.qt, m->mem.memory, m->edge_table, m->time_w, w.nbr1, w.eid1, w.dt1, k, N,
+                              nullptr, w.ctx, w.valid, d_status, s));
+    ORCA_TRY(orca_attn_output(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.nodes1, N, nullptr, emb_top,
+                              nullptr, nullptr, nullptr, s));
+  } else {
+    // top-level neighbour table, then the uncached out-of-batch neighbours join the row list
+    ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
+                              nullptr, k, w.nbr2, w.eid2, nullptr, w.dt2, d_status, s));
+    ORCA_TRY(orca_find_uncached(w.nbr2, N, k, m->cache_flag, m->n_nodes, w.nodes1, w.ts1, u_cap, w.n1,
+                                w.bitmap, d_status, s));
+    ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, R1,
+                              w.n1, k, w.nbr1, w.eid1, nullptr, w.dt1, d_status, s));
+    ORCA_TRY(orca_last_occurrence(w.nodes1, R1, w.n1, m->n_nodes, m->last_pos, *m->epoch_base, w.win1,
+                                  nullptr, nullptr, s));
+    *m->epoch_base += R1;
+    // layer 1 over memory rows; its output rows are pushed into the history table
+    ORCA_TRY(orca_attn_query(&m->attn[0], m->mem.memory, w.nodes1, R1, w.n1, w.qt, s));
+    ORCA_TRY(orca_attn_gather(w.qt, m->mem.memory, m->edge_table, m->time_w, w.nbr1, w.eid1, w.dt1, k, R1,
+                              w.n1, w.ctx, w.valid, d_status, s));
+    ORCA_TRY(orca_attn_output(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.nodes1, R1, w.n1, w.emb1,
+                              m->hist_emb, w.nodes1, w.win1, s));
+    // cache flags follow the plan of this batch (History.update_flag)
+    if (d_plan != nullptr) {
+      const bool know_prev = *m->n_prev_plan >= 0;
+      ORCA_TRY(orca_history_set_flags(m->cache_flag, m->n_nodes, know_prev ? m->prev_plan : nullptr,
+                                      know_prev ? *m->n_prev_plan : 0, d_plan, n_plan, s));
+      if (n_plan > 0) {
+        copy_i32_kernel<<<ceil_div(n_plan, 256), 256, 0, s>>>(d_plan, m->prev_plan, n_plan);
+        ORCA_COUNT_LAUNCH();
+      }
+      *m->n_prev_plan = n_plan;
+    } else {
+      // plan-less rule: the flags of the pushed ids are set and never cleared
+      set_flags_counted_kernel<<<std::min(ceil_div(R1, 256), 1024), 256, 0, s>>>(m->cache_flag, m->n_nodes,
+                                                                                 w.nodes1, R1, w.n1);
+      ORCA_COUNT_LAUNCH();
+      *m->n_prev_plan = -1;
+    }
+    // layer 2 over the history rows of the top-level neighbours
+    ORCA_TRY(orca_attn_query(&m->attn[1], w.emb1, nullptr, N, nullptr, w.qt, s));
+    ORCA_TRY(orca_attn_gather(w.qt, m->hist_emb, m->edge_table, m->time_w, w.nbr2, w.eid2, w.dt2, k, N,
+                              nullptr, w.ctx, w.valid, d_status, s));
+    ORCA_TRY(orca_attn_output(&m->attn[1], w.ctx, w.valid, w.emb1, nullptr, N, nullptr, emb_top, nullptr,
+                              nullptr, nullptr, s));
+  }
+
+  ORCA_TRY(orca_score(&m->score, emb_top, b, d_prob, s));
+
+  // raw messages of the batch (last occurrence per node in [src|dst]) and the memory update
+  ORCA_TRY(orca_last_occurrence(d_batch_i32, 2 * b, nullptr, m->n_nodes, m->last_pos, *m->epoch_base,
+                                w.is_last2, w.win_pos, w.n_win, s));
+  *m->epoch_base += 2 * b;
+  ORCA_TRY(orca_message_store(&m->mem, m->edge_table, m->time_w, d_batch_i32, w.cat_dst, d_batch_ts,
+                              d_batch_i32 + 3 * b, b, w.win_pos, 2 * b, w.n_win, w.win_nodes, s));
+  ORCA_TRY(orca_gru_update(&m->gru, &m->mem, w.win_nodes, 2 * b, w.n_win, 1, w.gru_h, s));
+
+  publish_counts_kernel<<<1, 1, 0, s>>>(w.n1, w.n_win, d_status);
+  ORCA_COUNT_LAUNCH();
+  ORCA_LAUNCH_CHECK();
+  g_last_batch_launches = launch_counter();
+  return ORCA_OK;
+}
+
+int orca_read_status(int32_t *d_status, int32_t *h_counts, void *stream) {
+  ORCA_CHECK_ARG(d_status);
+  int32_t h[4] = {0, 0, 0, 0};
+  cudaStream_t s = (cudaStream_t)stream;
+  ORCA_CUDA(cudaMemcpyAsync(h, d_status, sizeof(h), cudaMemcpyDeviceToHost, s));
+  ORCA_CUDA(cudaStreamSynchronize(s));
+  if (h_counts) {
+    h_counts[0] = h[0];
+    h_counts[1] = h[1];
+    h_counts[2] = h[2];
+    h_counts[3] = g_last_batch_launches;
+  }
+  if (h[0] != 0) {
+    ORCA_CUDA(cudaMemsetAsync(d_status, 0, sizeof(h), s));
+    return set_error(h[0], "device status %d (detail %d)", h[0], h[3]);
+  }
+  return ORCA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,357 @@
+"""``TGN`` with the constructor, methods and state-dict names of the reference's model
+(model/tgn_model.py:13-195), running the per-batch temporal-embedding path on the GPU through the
+C ABI of liborca_b200.so.
+
+The torch modules below (``nn.MultiheadAttention``, ``nn.GRUCell``, ``nn.Linear`` ...) are parameter
+containers only: they give ``state_dict()`` / ``load_state_dict()`` the reference's names, their
+``forward`` is never called.  The kernels read re-associated copies of the parameters
+(orca_b200/weights.py) that are rebuilt whenever the parameters change.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+from torch import nn
+
+from . import _lib, weights
+from .history import History
+from .memory import Memory, get_memory_updater
+
+
+class MergeLayer(nn.Module):
+    """utils/util.py:12-24 (parameter container; used as the merger and as the link scorer)."""
+
+    def __init__(self, dim1, dim2, dim3, dim4):
+        super().__init__()
+        self.fc1 = nn.Linear(dim1 + dim2, dim3)
+        self.fc2 = nn.Linear(dim3, dim4)
+        self.act = nn.ReLU()
+        nn.init.xavier_normal_(self.fc1.weight)
+        nn.init.xavier_normal_(self.fc2.weight)
+
+
+class TimeEncode(nn.Module):
+    """model/time_encoding.py:6-28: frozen frequencies 10^(-9 i/(d-1)), zero bias."""
+
+    def __init__(self, dimension):
+        super().__init__()
+        self.dimension = dimension
+        self.w = nn.Linear(1, dimension)
+        w = (1 / 10 ** np.linspace(0, 9, dimension, dtype=np.float32)).reshape(dimension, -1)
+        self.w.weight = nn.Parameter(torch.from_numpy(w), requires_grad=False)
+        self.w.bias = nn.Parameter(torch.zeros(dimension), requires_grad=False)
+
+
+class TemporalAttentionLayer(nn.Module):
+    """model/temporal_attention.py:6-22 (parameter container)."""
+
+    def __init__(self, n_node_features, n_neighbors_features, n_edge_features, time_dim, output_dimension,
+                 n_head=2, dropout=0.1):
+        super().__init__()
+        self.n_head = n_head
+        self.feat_dim = n_node_features
+        self.time_dim = time_dim
+        self.query_dim = n_node_features + time_dim
+        self.key_dim = n_neighbors_features + time_dim + n_edge_features
+        self.merger = MergeLayer(self.query_dim, n_node_features, n_node_features, output_dimension)
+        self.multi_head_target = nn.MultiheadAttention(embed_dim=self.query_dim, kdim=self.key_dim,
+                                                       vdim=self.key_dim, num_heads=n_head, dropout=dropout)
+        self.norm = nn.LayerNorm(output_dimension)
+
+
+class GraphAttentionEmbedding(nn.Module):
+    """modules/embedding_module.py:64-113, 294-329: attention layers plus one History per layer
+    below the top; history maintenance calls used by the reference's driver keep their names."""
+
+    def __init__(self, neighbor_finder, time_encoder, n_layers, n_node_features, n_edge_features,
+                 n_time_features, embedding_dimension, device, n_heads=2, dropout=0.1, reuse=False,
+                 history_budget=0, args=None, num_nodes=-1):
+        super().__init__()
+        self.neighbor_finder = neighbor_finder
+        self.time_encoder = time_encoder
+        self.n_layers = n_layers
+        self.device = device
+        self.args = args
+        self.budget = history_budget
+        if reuse:
+            self.histories = nn.ModuleList([History(num_nodes, embedding_dimension, device, history_budget)
+                                            for _ in range(n_layers - 1)])
+        self.attention_models = nn.ModuleList([
+            TemporalAttentionLayer(n_node_features, n_node_features, n_edge_features, n_time_features,
+                                   n_node_features, n_head=n_heads, dropout=dropout)
+            for _ in range(n_layers)])
+
+    def backup_history(self):
+        return [self.histories[i].emb.clone() for i in range(self.n_layers - 1)]
+
+    def restore_history(self, backup):
+        for i in range(self.n_layers - 1):
+            self.histories[i].emb = backup[i]
+
+    def reset_history(self):
+        for i in range(self.n_layers - 1):
+            self.histories[i].reset_parameters()
+
+    def detach_history(self):
+        for i in range(self.n_layers - 1):
+            self.histories[i].detach_history()
+
+
+class _Staging:
+    """Ring of pinned host buffers for the per-batch inputs; a buffer is reused only after the
+    copy that read it has completed."""
+
+    def __init__(self, n_slots=8):
+        self.slots = [None] * n_slots
+        self.events = [None] * n_slots
+        self.i = 0
+
+    def get(self, nbytes):
+        i = self.i
+        self.i = (i + 1) % len(self.slots)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.slots[i]
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, pin_memory=True)
+            self.slots[i] = buf
+        return i, buf
+
+    def mark(self, i):
+        ev = self.events[i]
+        if ev is None:
+            ev = torch.cuda.Event()
+            self.events[i] = ev
+        ev.record()
+
+
+class TGN(nn.Module):
+    def __init__(self, neighbor_finder, node_features, edge_features, device, n_layers=2,
+                 n_heads=2, dropout=0.1, use_memory=True, node_dimension=100, time_dimension=100,
+                 memory_dimension=100, embedding_module_type="graph_attention",
+                 message_function="mlp", n_neighbors=None, aggregator_type="last",
+                 memory_updater_type="gru",
+                 use_destination_embedding_in_message=False,
+                 use_source_embedding_in_message=False,
+                 args=None):
+        super().__init__()
+        self.device = _lib.require_cuda(device)
+        if embedding_module_type != "graph_attention":
+            raise ValueError("Embedding Module {} not supported".format(embedding_module_type))
+        if message_function != "identity":
+            # the reference's "mlp" branch cannot be constructed (model/tgn_model.py:52 reads a
+            # local before assignment); identity is the only working value
+            raise ValueError("message_function must be 'identity'")
+        if aggregator_type != "last":
+            raise ValueError("Message aggregator {} not supported".format(aggregator_type))
+        if not use_memory or use_destination_embedding_in_message or use_source_embedding_in_message:
+            raise ValueError("only the memory-based message of the default configuration is supported")
+        if n_heads != 2 or node_dimension != _lib.DIM or time_dimension != _lib.DIM or memory_dimension != _lib.DIM:
+            raise ValueError("orca_b200 is built for 2 heads and 172-wide node/time/memory features")
+        if n_layers not in (1, 2):
+            raise ValueError("n_layers must be 1 or 2")
+        self.batch_counter = 0
+        self.n_layers = n_layers
+        self.neighbor_finder = neighbor_finder
+        self.args = args
+        ef = np.asarray(edge_features, dtype=np.float32)
+        if ef.shape[1] != _lib.DIM:
+            raise ValueError("orca_b200 is built for 172-wide edge features")
+        self.edge_raw_features = torch.from_numpy(np.ascontiguousarray(ef)).to(self.device)
+        self.n_edge_features = ef.shape[1]
+        self.n_nodes = args.n_nodes
+        self.time_dimension = time_dimension
+        self.memory_dimension = memory_dimension
+        self.embedding_dimension = node_dimension
+        self.n_node_features = node_dimension
+        self.n_neighbors = n_neighbors
+        self.embedding_module_type = embedding_module_type
+        self.use_memory = use_memory
+        self.time_encoder = TimeEncode(dimension=time_dimension)
+        msg_dim = 2 * memory_dimension + self.n_edge_features + time_dimension
+        self.memory = Memory(n_nodes=self.n_nodes, memory_dimension=memory_dimension, input_dimension=msg_dim,
+                             message_dimension=msg_dim, device=self.device)
+        self.memory_updater = get_memory_updater(memory_updater_type, msg_dim, memory_dimension, self.device)
+        self.embedding_module = GraphAttentionEmbedding(
+            neighbor_finder=neighbor_finder, time_encoder=self.time_encoder, n_layers=n_layers,
+            n_node_features=node_dimension, n_edge_features=self.n_edge_features,
+            n_time_features=time_dimension, embedding_dimension=node_dimension, device=self.device,
+            n_heads=n_heads, dropout=dropout, reuse=args.reuse, history_budget=args.budget, args=args,
+            num_nodes=self.n_nodes)
+        self.affinity_score = MergeLayer(node_dimension, node_dimension, node_dimension, 1)
+        self.test_mode = False
+        self.to(self.device)
+        # kernel-side state
+        self._prepared = None
+        self._ws = None
+        self._ws_key = None
+        self._stage = _Staging()
+        self._stage_dev = None
+        self._status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._last_pos = torch.zeros(self.n_nodes, dtype=torch.int64, device=self.device)
+        self._epoch = np.ones(1, dtype=np.int64)
+        self._dummy_prev = np.full(1, -1, dtype=np.int32)
+        self.last_counts = None
+
+    # ---- weights ------------------------------------------------------------------------------
+    def load_state_dict(self, state_dict, strict=True, **kw):
+        r = super().load_state_dict(state_dict, strict=strict, **kw)
+        self.refresh_weights()
+        return r
+
+    def refresh_weights(self):
+        """Call after changing parameters in place; load_state_dict does it itself."""
+        self._prepared = None
+        self.memory_updater.invalidate()
+
+    def _weights(self):
+        if self._prepared is None:
+            sd = {k: v.detach().cpu().numpy() for k, v in self.state_dict().items()}
+            dev = self.device
+            up = lambda d: {k: (torch.from_numpy(v).to(dev) if isinstance(v, np.ndarray) else v) for k, v in d.items()}
+            self._prepared = {
+                "time_w": torch.from_numpy(weights.prepare_time(sd)).to(dev),
+                "attn": [up(weights.prepare_attention(sd, l)) for l in range(self.n_layers)],
+                "score": up(weights.prepare_score(sd)),
+            }
+        return self._prepared
+
+    def attn_struct(self, layer):
+        a = self._weights()["attn"][layer]
+        return _lib.AttnWeights(*[a[k].data_ptr() for k in ("Mq", "cq", "G", "b1", "g", "W2t", "b2", "ln_w", "ln_b")])
+
+    def score_struct(self):
+        s = self._weights()["score"]
+        return _lib.ScoreWeights(s["W1t"].data_ptr(), s["b1"].data_ptr(), s["w2"].data_ptr(), s["b2"])
+
+    def set_neighbor_finder(self, neighbor_finder):
+        self.neighbor_finder = neighbor_finder
+        self.embedding_module.neighbor_finder = neighbor_finder
+
+    # ---- model descriptor for the fused batch entry point ----------------------------------------
+    def _descriptor(self, k):
+        nf = self.embedding_module.neighbor_finder
+        w = self._weights()
+        t = _lib.TgnT()
+        t.indptr, t.adj_nbr, t.adj_eid, t.adj_ts = (nf.indptr.data_ptr(), nf.adj_nbr.data_ptr(),
+                                                    nf.adj_eid.data_ptr(), nf.adj_ts.data_ptr())
+        t.edge_table = self.edge_raw_features.data_ptr()
+        t.n_nodes = self.n_nodes
+        t.n_edge_rows = self.edge_raw_features.shape[0]
+        t.time_w = w["time_w"].data_ptr()
+        for l in range(self.n_layers):
+            t.attn[l] = self.attn_struct(l)
+        t.score = self.score_struct()
+        t.gru = self.memory_updater.c_struct()
+        t.n_layers = self.n_layers
+        t.k = k
+        t.mem = self.memory.c_struct()
+        if self.n_layers == 2:
+            h = self.embedding_module.histories[0]
+            t.hist_emb = h.emb.data_ptr()
+            t.cache_flag = h.cache_flag_dev.data_ptr()
+            t.prev_plan = h.prev_plan.data_ptr()
+            t.n_prev_plan = h.n_prev.ctypes.data_as(C.POINTER(C.c_int32))
+            t.plan_cap = h.prev_plan.numel()
+        else:
+            t.n_prev_plan = self._dummy_prev.ctypes.data_as(C.POINTER(C.c_int32))
+        t.last_pos = self._last_pos.data_ptr()
+        t.epoch_base = self._epoch.ctypes.data_as(C.POINTER(C.c_int64))
+        return t
+
+    def _workspace(self, b, k):
+        u_cap = min(3 * b * k, self.n_nodes) if self.n_layers == 2 else 0
+        key = (b, u_cap, k)
+        if self._ws_key is None or self._ws_key[0] < b or self._ws_key[2] != k:
+            nbytes = _lib.lib().orca_eval_workspace_bytes(b, u_cap, k, self.n_nodes)
+            self._ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            self._ws_key = key
+        return self._ws, u_cap
+
+    # ---- one eval batch ----------------------------------------------------------------------------
+    def _eval_batch(self, source_nodes, destination_nodes, negative_nodes, edge_times, edge_idxs, n_neighbors,
+                    cache_plan, want_emb):
+        L = _lib.lib()
+        b = len(source_nodes)
+        k = int(n_neighbors)
+        if self.n_layers == 2 and cache_plan is not None:
+            h = self.embedding_module.histories[0]
+            if len(cache_plan) > h.prev_plan.numel():
+                h.prev_plan = torch.zeros(len(cache_plan), dtype=torch.int32, device=self.device)
+                h.n_prev[0] = -1
+        n_plan = len(cache_plan) if cache_plan is not None else 0
+        n_i32 = 4 * b + n_plan
+        off_ts = (n_i32 * 4 + 15) // 16 * 16
+        total = off_ts + 8 * b
+        slot, host = self._stage.get(total)
+        hn = host.numpy()
+        hi = hn[:n_i32 * 4].view(np.int32)
+        hi[0:b] = source_nodes
+        hi[b:2 * b] = destination_nodes
+        hi[2 * b:3 * b] = negative_nodes
+        hi[3 * b:4 * b] = edge_idxs
+        if n_plan:
+            hi[4 * b:] = cache_plan
+        hn[off_ts:total].view(np.float64)[:] = edge_times
+        if self._stage_dev is None or self._stage_dev.numel() < total:
+            self._stage_dev = torch.empty(max(total, 1 << 16), dtype=torch.uint8, device=self.device)
+        dev = self._stage_dev
+        dev[:total].copy_(host[:total], non_blocking=True)
+        self._stage.mark(slot)
+        ws, u_cap = self._workspace(b, k)
+        prob = torch.empty(2 * b, device=self.device)
+        emb = torch.empty(3 * b, _lib.DIM, device=self.device) if want_emb else None
+        desc = self._descriptor(k)
+        base = dev.data_ptr()
+        d_plan = base + 16 * b if cache_plan is not None else None
+        _lib.check(L.orca_tgn_eval_batch(desc, base, base + off_ts, b, d_plan, n_plan, u_cap, ws.data_ptr(),
+                                         ws.numel(), prob.data_ptr(), _lib.ptr(emb), self._status.data_ptr(),
+                                         _lib.stream_ptr(self.device)))
+        return prob, emb
+
+    def check_status(self):
+        """Synchronises and raises if a kernel reported an error since the last check; returns
+        (rows at layer 1, unique positives, kernel launches) of the last batch."""
+        h = np.zeros(4, dtype=np.int32)
+        _lib.check(_lib.lib().orca_read_status(self._status.data_ptr(), h.ctypes.data, _lib.stream_ptr(self.device)))
+        self.last_counts = (int(h[1]), int(h[2]), int(h[3]))
+        return self.last_counts
+
+    def _enter(self, reuse, train):
+        if train:
+            raise NotImplementedError("the training path (train=True) is not part of this build")
+        if not reuse or self.args.budget == 0:
+            raise NotImplementedError("only the budgeted-reuse recursion (reuse=True, budget>0) is built")
+        self.batch_counter += 1
+        if self.test_mode is False:
+            # model/tgn_model.py:109-111: pending messages are flushed when eval starts
+            self.update_memory_in_test(self.memory)
+            self.test_mode = True
+
+    # ---- model/tgn_model.py:95-147
+    @torch.no_grad()
+    def compute_temporal_embeddings(self, source_nodes, destination_nodes, negative_nodes, edge_times, edge_idxs,
+                                    n_neighbors, reuse, train, cache_plan):
+        self._enter(reuse, train)
+        b = len(source_nodes)
+        _, emb = self._eval_batch(source_nodes, destination_nodes, negative_nodes, edge_times, edge_idxs,
+                                  n_neighbors, cache_plan, want_emb=True)
+        return emb[:b], emb[b:2 * b], emb[2 * b:]
+
+    # ---- model/tgn_model.py:150-157
+    @torch.no_grad()
+    def compute_edge_probabilities(self, source_nodes, destination_nodes, negative_nodes, edge_times, edge_idxs,
+                                   n_neighbors, reuse, train, cache_plan):
+        self._enter(reuse, train)
+        b = len(source_nodes)
+        prob, _ = self._eval_batch(source_nodes, destination_nodes, negative_nodes, edge_times, edge_idxs,
+                                   n_neighbors, cache_plan, want_emb=False)
+        return prob[:b].unsqueeze(1), prob[b:].unsqueeze(1)
+
+    def update_memory(self, memory, positives):
+        self.memory_updater.update_memory(memory, positives)
+
+    def update_memory_in_test(self, memory):
+        self.memory_updater.update_memory_in_test(memory)
