@@ -221,6 +221,26 @@ int orca_gru_update(const orca_gru_weights_t *w, const orca_memory_t *mem, const
 int64_t orca_gru_scratch_bytes(int32_t n_cap);
 
 /* ------------------------------------------------------------------------------------------
+ * Offline cache planning.  Replaces read_batches + MRD_numba / LRU_numba / TwoQ_numba
+ * (utils/cache.py:19-89, 92-166, 338-403, 175-333).  The neighbour tables of ALL batches are
+ * sampled beforehand with one orca_sample_topk launch over the query list in which batch b (edges
+ * [s, e) of the stream, s = b*bs) contributes rows 2*s .. 2*s+(e-s)-1 = its sources and the next
+ * (e-s) rows = its destinations, each at the edge's own timestamp; h_nbr is that table copied to
+ * the host ([2*n_edges, k] int32).  The batch-sequential policy then runs on the host.
+ * strategy: 0 = MRD, 1 = LRU, 2 = 2Q.  `seed` seeds the Mersenne Twister behind the random
+ * evictions of LRU / 2Q (the reference's numba generator seeded with np.random.seed(seed) from
+ * jitted code).  Plan of batch b = h_plan_flat[h_plan_off[b] .. h_plan_off[b+1]) in the reference's
+ * order (MRD: argsort order; LRU: ascending; 2Q: FIFO half ascending then LRU half ascending).
+ * h_plan_off has n_batches+1 entries; plan_cap >= n_batches*(budget+2) always suffices.
+ * h_stats = {n_reuse, n_recompute, sum of reuse distances} (utils/cache.py:427).
+ * Host function.
+ */
+int orca_plan_host(int32_t strategy, const int64_t *h_src, const int64_t *h_dst, int64_t n_edges,
+                   int32_t bs, int32_t k, const int32_t *h_nbr, int64_t n_nodes, int32_t budget,
+                   uint32_t seed, int32_t *h_plan_flat, int64_t plan_cap, int64_t *h_plan_off,
+                   double *h_stats);
+
+/* ------------------------------------------------------------------------------------------
  * One whole eval batch: TGN.compute_edge_probabilities(..., reuse=True, train=False, cache_plan)
  * with budget != 0 (model/tgn_model.py:95-157 over modules/embedding_module.py:215-285), enqueued
  * on `stream` without any host synchronisation.

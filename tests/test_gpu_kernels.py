@@ -113,7 +113,8 @@ def test_find_uncached(dev, n_nodes):
         n_total = torch.zeros(1, dtype=torch.int32, device=dev)
         status = torch.zeros(4, dtype=torch.int32, device=dev)
         scratch = torch.zeros(max(int(L.orca_find_uncached_scratch_bytes(n_nodes)), 16), dtype=torch.uint8, device=dev)
-        _lib.check(L.orca_find_uncached(_i32(nbr, dev).data_ptr(), nq, k, torch.as_tensor(flag).to(dev).data_ptr(),
+        d_nbr, d_flag = _i32(nbr, dev), torch.as_tensor(flag).to(dev)   # keep the inputs alive
+        _lib.check(L.orca_find_uncached(d_nbr.data_ptr(), nq, k, d_flag.data_ptr(),
                                         n_nodes, nodes_io.data_ptr(), ts_io.data_ptr(), u_cap, n_total.data_ptr(),
                                         scratch.data_ptr(), status.data_ptr(), _lib.stream_ptr(dev)))
         _lib.check(L.orca_read_status(status.data_ptr(), None, _lib.stream_ptr(dev)))
@@ -136,7 +137,8 @@ def test_find_uncached_capacity_is_reported(dev):
     status = torch.zeros(4, dtype=torch.int32, device=dev)
     flag = torch.zeros(1000, dtype=torch.uint8, device=dev)
     scratch = torch.zeros(16, dtype=torch.uint8, device=dev)
-    _lib.check(L.orca_find_uncached(_i32(nbr, dev).data_ptr(), 10, 10, flag.data_ptr(), 1000, nodes_io.data_ptr(),
+    d_nbr = _i32(nbr, dev)
+    _lib.check(L.orca_find_uncached(d_nbr.data_ptr(), 10, 10, flag.data_ptr(), 1000, nodes_io.data_ptr(),
                                     ts_io.data_ptr(), 5, n_total.data_ptr(), scratch.data_ptr(), status.data_ptr(),
                                     _lib.stream_ptr(dev)))
     with pytest.raises(_lib.OrcaError) as e:
@@ -160,7 +162,8 @@ def test_last_occurrence(dev):
         is_last = torch.zeros(n, dtype=torch.uint8, device=dev)
         compact = torch.zeros(n, dtype=torch.int32, device=dev)
         n_c = torch.zeros(1, dtype=torch.int32, device=dev)
-        _lib.check(L.orca_last_occurrence(_i32(ids, dev).data_ptr(), n, None, n_nodes, last_pos.data_ptr(), base,
+        d_ids = _i32(ids, dev)
+        _lib.check(L.orca_last_occurrence(d_ids.data_ptr(), n, None, n_nodes, last_pos.data_ptr(), base,
                                           is_last.data_ptr(), compact.data_ptr(), n_c.data_ptr(),
                                           _lib.stream_ptr(dev)))
         base += n
@@ -280,7 +283,8 @@ def test_score(dev):
         t = {kk: torch.from_numpy(v).to(dev) for kk, v in w.items() if kk != "b2"}
         ws = _lib.ScoreWeights(t["W1t"].data_ptr(), t["b1"].data_ptr(), t["w2"].data_ptr(), w["b2"])
         prob = torch.zeros(2 * b, device=dev)
-        _lib.check(L.orca_score(ws, torch.from_numpy(emb).to(dev).data_ptr(), b, prob.data_ptr(), _lib.stream_ptr(dev)))
+        d_emb = torch.from_numpy(emb).to(dev)
+        _lib.check(L.orca_score(ws, d_emb.data_ptr(), b, prob.data_ptr(), _lib.stream_ptr(dev)))
         assert max_rel(prob.cpu().numpy(), want, floor=0.05) < TOL
 
 
@@ -322,8 +326,9 @@ def test_message_store_and_gru(dev):
                                       win_pos.data_ptr(), n_win.data_ptr(), s))
     tw = torch.from_numpy(weights.prepare_time(sd)).to(dev)
     d_ef = torch.from_numpy(efeat).to(dev)
+    d_ts, d_eidx = torch.as_tensor(ts).to(dev), _i32(eidx, dev)
     _lib.check(L.orca_message_store(mem.c_struct(), d_ef.data_ptr(), tw.data_ptr(), d_cs.data_ptr(), d_cd.data_ptr(),
-                                    torch.as_tensor(ts).to(dev).data_ptr(), _i32(eidx, dev).data_ptr(), b,
+                                    d_ts.data_ptr(), d_eidx.data_ptr(), b,
                                     win_pos.data_ptr(), 2 * b, n_win.data_ptr(), win_nodes.data_ptr(), s))
     assert int(n_win.item()) == len(uniq)
     assert np.array_equal(np.sort(win_nodes[:len(uniq)].cpu().numpy()), uniq)
