@@ -1,0 +1,414 @@
+"""Benchmark of the per-batch temporal-embedding path: scored temporal edges per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5] [--impl ours|reference]
+
+A step is one batch of the workload's stream (bs positive edges + bs negatives scored) run through
+TGN.compute_edge_probabilities in eval mode with budgeted reuse and the batch's cache plan.
+The timed batches are consecutive batches from the middle of the stream (neighbour lists are full
+there); the state tables start cold, which changes values, not the amount of work.
+
+Prints ONE JSON line (rank 0).  `value` = edges/s with the inputs of all timed batches already in
+HBM; `e2e` = the same through the public Python API with host (NumPy) inputs, one pinned H2D copy
+and the D2H read of the scores per step; `roofline` = the fused gather-attention kernel, timed with
+CUDA events around each of its launches; `cpu_baseline` = the CPU oracle on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "temporal edges scored/sec (2-layer, K=10)"
+ROW_BYTES = 688
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="c5")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-batches", type=int, default=None, help="batches of the CPU baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--plan-batches", type=int, default=None,
+                    help="plan only this many leading batches of the stream (quick runs)")
+    return ap.parse_args()
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.stop_flag, self.max_mhz = index, [], set(), False, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                break
+            time.sleep(0.05)
+
+    def result(self):
+        self.stop_flag = True
+        if self.nv is None or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons)}
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def workload_config(g, spec, start, extra=None):
+    cfg = {"workload": f"{spec.name}: {g.n_nodes - 1} nodes, {g.n_edges} edges, bs={spec.bs}, "
+                       f"L={spec.n_layers}, K={spec.n_degree}, budget={spec.budget} {spec.strategy}",
+           "first_timed_batch": int(start),
+           "l2": "inputs larger than L2: edge-feature and state tables total "
+                 f"{(g.n_edges + 1 + 7 * g.n_nodes) * ROW_BYTES / 1e9:.1f} GB and every step gathers different rows"}
+    if extra:
+        cfg.update(extra)
+    return cfg
+
+
+def build_setup(a, device, quiet=True):
+    """Graph, negatives, neighbour finder, plan and model for the workload (every rank)."""
+    import contextlib
+
+    import torch
+
+    from orca_b200 import params, synthetic
+    from orca_b200.cache import get_cache_plan
+    from orca_b200.neighbor_finder import get_neighbor_finder
+    from orca_b200.tgn import TGN
+    t0 = time.time()
+    g = synthetic.make_graph(a.workload)
+    spec = g.spec
+    neg = synthetic.negative_destinations(g, seed=0)
+    nf = get_neighbor_finder(g, device=device)
+    ns = argparse.Namespace(bs=spec.bs, n_degree=spec.n_degree, budget=spec.budget, reuse=True, gradient=False,
+                            n_nodes=g.n_nodes, n_edges=g.n_edges + 1)
+    t1 = time.time()
+    with contextlib.redirect_stdout(sys.stderr):
+        if a.plan_batches:
+            import dataclasses
+            import types
+            m = min(g.n_edges, a.plan_batches * spec.bs)
+            sub = types.SimpleNamespace(sources=g.sources[:m], destinations=g.destinations[:m],
+                                        timestamps=g.timestamps[:m])
+            plan = get_cache_plan(ns, sub, nf, g.n_nodes, spec.strategy)
+        else:
+            plan = get_cache_plan(ns, g, nf, g.n_nodes, spec.strategy)
+    t2 = time.time()
+    tgn = TGN(neighbor_finder=nf, node_features=None, edge_features=g.edge_features, device=device,
+              n_layers=spec.n_layers, n_heads=2, dropout=0.1, use_memory=True, node_dimension=172,
+              time_dimension=172, memory_dimension=172, embedding_module_type="graph_attention",
+              message_function="identity", aggregator_type="last", memory_updater_type="gru",
+              n_neighbors=spec.n_degree, args=ns)
+    sd = {k: torch.from_numpy(v) for k, v in params.random_state_dict(spec.n_layers, seed=0).items()}
+    sd["embedding_module.time_encoder.w.weight"] = sd["time_encoder.w.weight"]
+    sd["embedding_module.time_encoder.w.bias"] = sd["time_encoder.w.bias"]
+    tgn.load_state_dict(sd)
+    tgn.eval()
+    if not quiet:
+        print(f"[bench] graph+finder {t1 - t0:.1f}s, plan {t2 - t1:.1f}s, model {time.time() - t2:.1f}s",
+              file=sys.stderr)
+    return g, neg, plan, tgn
+
+
+def pick_window(n_batches, steps, warmup):
+    """First batch index of the warm-up so that the timed batches sit mid-stream."""
+    total = steps + warmup
+    if total > n_batches:
+        raise SystemExit(f"--steps + --warmup = {total} exceeds the {n_batches} batches of the stream")
+    first = max(0, min(n_batches // 2 - warmup, n_batches - total))
+    return first
+
+
+def batch_arrays(g, neg, b):
+    bs = g.spec.bs
+    s, e = b * bs, min(g.n_edges, (b + 1) * bs)
+    return g.sources[s:e], g.destinations[s:e], neg[s:e], g.timestamps[s:e], g.edge_idxs[s:e]
+
+
+def reset_state(tgn, plan, first):
+    tgn.memory.__init_memory__()
+    if tgn.n_layers > 1:
+        tgn.embedding_module.reset_history()
+        h = tgn.embedding_module.histories[0]
+        h.cache_flag_dev.zero_()
+        h.n_prev[0] = -1
+        if first > 0:
+            h.update_flag(plan[first - 1], None)
+    tgn.test_mode = True
+
+
+def algorithmic_bytes(b, k, n1, n2, p):
+    """Bytes one batch must move, every gathered row counted once, weights excluded:
+    sampling Q*(28K+80), attention rows (N1+N2)*(R*(2K+2)+12K), scoring 3B*R+8B, message + GRU per
+    unique positive P*(13R+8)."""
+    q = n1 + n2
+    R = ROW_BYTES
+    return q * (28 * k + 80) + (n1 + n2) * (R * (2 * k + 2) + 12 * k) + 3 * b * R + 8 * b + p * (13 * R + 8)
+
+
+def run_ours(a):
+    import torch
+    import torch.distributed as dist
+
+    from orca_b200 import _lib
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if world != a.gpus:
+        raise SystemExit(f"--gpus {a.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    L = _lib.lib()
+    g, neg, plan, tgn = build_setup(a, device, quiet=rank != 0)
+    spec = g.spec
+    K, W = a.steps, a.warmup
+    nb_avail = len(plan)
+    first = pick_window(nb_avail, K, W)
+    k = spec.n_degree
+    stream = _lib.stream_ptr(device)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn_warm, fn_step):
+        for i in range(W):
+            fn_warm(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler = ClockSampler(local)
+        sampler.start()
+        e0.record()
+        for i in range(K):
+            fn_step(i)
+        e1.record()
+        barrier()
+        clocks = sampler.result()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), clocks
+
+    # ---------------- end to end: public API, host inputs, pinned H2D + D2H of the scores per step
+    bs = spec.bs
+    host_out = torch.empty((K, 2 * bs), dtype=torch.float32, pin_memory=True)
+    h2d = d2h = 0
+
+    def api_step(b, slot=None):
+        nonlocal h2d, d2h
+        src, dst, ng, ts, eidx = batch_arrays(g, neg, b)
+        p, q = tgn.compute_edge_probabilities(src, dst, ng, ts, eidx, k, True, False, plan[b])
+        if slot is not None:
+            n = len(src)
+            host_out[slot, :n].copy_(p.view(-1), non_blocking=True)
+            host_out[slot, bs:bs + n].copy_(q.view(-1), non_blocking=True)
+            h2d += 16 * n + 8 * n + 4 * len(plan[b])
+            d2h += 8 * n
+
+    reset_state(tgn, plan, first)
+    ms_e2e, _ = timed(lambda i: api_step(first + i), lambda i: api_step(first + W + i, i))
+    tgn.check_status()
+    edges = sum(len(batch_arrays(g, neg, first + W + i)[0]) for i in range(K))
+    e2e = {"value": edges * world / (ms_e2e / 1e3) if world == 1 else edges / (ms_e2e / 1e3), "unit": "edges/s",
+           "h2d_bytes_per_step": h2d // K, "d2h_bytes_per_step": d2h // K, "ms_per_step": ms_e2e / K}
+
+    # ---------------- device-resident inputs: packed batches preloaded, the C ABI called directly
+    packed = []
+    for i in range(W + K):
+        src, dst, ng, ts, eidx = batch_arrays(g, neg, first + i)
+        pl = plan[first + i]
+        ints = torch.from_numpy(np.concatenate([src, dst, ng, eidx, pl]).astype(np.int32)).to(device)
+        packed.append((ints, torch.from_numpy(np.ascontiguousarray(ts)).to(device), len(src), len(pl)))
+    probs = torch.empty((W + K, 2 * bs), device=device)
+    reset_state(tgn, plan, first)
+    desc = tgn._descriptor(k)
+    ws, u_cap = tgn._workspace(bs, k)
+
+    def abi_step(i):
+        ints, ts, n, n_plan = packed[i]
+        _lib.check(L.orca_tgn_eval_batch(desc, ints.data_ptr(), ts.data_ptr(), n, ints.data_ptr() + 16 * n, n_plan,
+                                         u_cap, ws.data_ptr(), ws.numel(), probs[i].data_ptr(), None,
+                                         tgn._status.data_ptr(), stream))
+
+    ms_dev, clocks = timed(lambda i: abi_step(i), lambda i: abi_step(W + i))
+    counts = tgn.check_status()
+    launches_per_batch = counts[2]
+
+    # ---------------- roofline pass: same batches, CUDA events around every gather-attention launch
+    reset_state(tgn, plan, first)
+    desc = tgn._descriptor(k)
+    counters = torch.zeros(2, dtype=torch.int64, device=device)
+    for i in range(W):
+        abi_step(i)
+    torch.cuda.synchronize()
+    _lib.check(L.orca_attn_gather_profile(1, counters.data_ptr()))
+    step_bytes = 0
+    for i in range(K):
+        abi_step(W + i)
+        n1, p, _ = tgn.check_status()
+        n = packed[W + i][2]
+        step_bytes += algorithmic_bytes(n, k, n1 if spec.n_layers == 2 else 3 * n,
+                                        3 * n if spec.n_layers == 2 else 0, p)
+    gms = np.zeros(1, dtype=np.float64)
+    gl = np.zeros(1, dtype=np.int64)
+    _lib.check(L.orca_attn_gather_profile_read(gms.ctypes.data, gl.ctypes.data))
+    _lib.check(L.orca_attn_gather_profile(0, None))
+    rows_g, slots_g = (int(x) for x in counters.cpu().numpy())
+    peak, peak_kind = load_peaks()
+    gather_bytes = rows_g * (2 * ROW_BYTES + 12 * k) + slots_g * 2 * ROW_BYTES
+    achieved = gather_bytes / (gms[0] / 1e3) / 1e9 if gms[0] > 0 else 0.0
+    roofline = {"bound": "hbm", "kernel": "attn_gather_kernel", "achieved": achieved, "peak": peak,
+                "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind + " copy bandwidth",
+                "traffic": GATHER_TRAFFIC_PER_LAUNCH, "launches": int(gl[0]),
+                "avg_launch_us": gms[0] * 1e3 / max(int(gl[0]), 1),
+                "algorithmic_bytes_per_launch": gather_bytes / max(int(gl[0]), 1)}
+    step_frac = step_bytes / (ms_dev / 1e3) / 1e9 / peak
+
+    value = edges / (ms_dev / 1e3)
+    line = {"metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_dev / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": workload_config(g, spec, first + W, {"whole_step_hbm_frac": step_frac,
+                                                           "algorithmic_bytes_per_edge": step_bytes / edges}),
+            "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches_per_batch * K), "clocks": clocks}
+    if rank == 0 and world == 1 and not a.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(a, g, neg, plan, first + W)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_gather_kernel launch from the ncu capture
+# summarised under profiles/ (null until a capture of the current kernel exists)
+GATHER_TRAFFIC_PER_LAUNCH = None
+
+
+def oracle_sample(g, neg, plan, first, n_batches, sub_bs, threads):
+    """Times the CPU oracle (the restatement of the reference's PyTorch + numba path) on
+    `n_batches` consecutive batches starting at `first`, each cut to its first `sub_bs` edges.
+    Returns (edges, seconds)."""
+    import torch
+
+    from oracle import tgn_oracle
+    from orca_b200 import params
+    torch.set_num_threads(threads)
+    spec = g.spec
+    adj = tgn_oracle.Adjacency(g.sources, g.destinations, g.edge_idxs, g.timestamps, g.n_nodes)
+    orc = tgn_oracle.OracleTGN(adj, g.edge_features, params.random_state_dict(spec.n_layers, seed=0), g.n_nodes,
+                               n_layers=spec.n_layers, budget=spec.budget)
+    if spec.n_layers > 1 and first > 0:
+        orc.cache_flag[0][np.asarray(plan[first - 1], dtype=np.int64)] = 1
+    # one untimed batch warms the thread pools and the page cache of the big tables
+    src, dst, ng, ts, eidx = (x[:sub_bs] for x in batch_arrays(g, neg, max(first - 1, 0)))
+    orc.compute_edge_probabilities(src, dst, ng, ts, eidx, spec.n_degree, plan[max(first - 1, 0)])
+    edges = 0
+    t0 = time.perf_counter()
+    for i in range(n_batches):
+        src, dst, ng, ts, eidx = (x[:sub_bs] for x in batch_arrays(g, neg, first + i))
+        orc.compute_edge_probabilities(src, dst, ng, ts, eidx, spec.n_degree, plan[first + i])
+        edges += len(src)
+    return edges, time.perf_counter() - t0
+
+
+def cpu_baseline(a, g, neg, plan, first):
+    threads = os.cpu_count() or 1
+    sub_bs = min(g.spec.bs, 500)
+    nb = a.cpu_batches or 8
+    nb = min(nb, len(plan) - first)
+    edges, sec = oracle_sample(g, neg, plan, first, nb, sub_bs, threads)
+    return {"value": edges / sec, "unit": "edges/s", "cores": threads, "kind": "port",
+            "sample": f"{nb} consecutive batches from batch {first}, first {sub_bs} edges of each, "
+                      f"CPU oracle (numpy + fp32 torch), {sec:.1f}s"}
+
+
+def run_reference(a):
+    """The reference arm: the CPU restatement of the reference's own path on the host cores (the
+    reference is Python + numba and is not installed on the GPU box; the oracle is its port)."""
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    import contextlib
+
+    from orca_b200 import synthetic
+    from oracle import planner, tgn_oracle
+    g = synthetic.make_graph(a.workload)
+    spec = g.spec
+    neg = synthetic.negative_destinations(g, seed=0)
+    K, W = a.steps, a.warmup
+    threads = os.cpu_count() or 1
+    # the plan only steers which neighbours count as cached; it is computed by the CPU planner on a
+    # prefix of the stream that covers the timed window
+    first = pick_window(g.n_batches, K, W)
+    # bounded: every step is the first `sub_bs` edges of one stream batch
+    sub_bs = min(spec.bs, 250)
+    adj = tgn_oracle.Adjacency(g.sources, g.destinations, g.edge_idxs, g.timestamps, g.n_nodes)
+    m = min(g.n_edges, (first + W + K) * spec.bs)
+    t0 = time.time()
+    plan = planner.get_cache_plan(g.sources[:m], g.destinations[:m], g.timestamps[:m], spec.bs, spec.n_degree,
+                                  spec.budget, adj, g.n_nodes, spec.strategy)
+    print(f"[bench] reference arm: CPU plan over {len(plan)} batches {time.time() - t0:.1f}s", file=sys.stderr)
+    del adj
+    edges, sec = oracle_sample(g, neg, plan, first + W, K, sub_bs, threads)
+    value = edges / sec
+    sample = f"{K} consecutive batches from batch {first + W}, first {sub_bs} edges of each"
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": a.gpus, "steps": K,
+            "warmup": W, "ms_per_step": sec * 1e3 / K, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(g, spec, first + W),
+            "cpu_baseline": {"value": value, "unit": "edges/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)

@@ -143,6 +143,13 @@ int orca_attn_gather(const float *d_qt, const float *d_nbr_table, const float *d
                      const float *d_delta, int32_t k, int32_t n_rows_cap, const int32_t *d_n_rows,
                      float *d_ctx, uint8_t *d_valid, int32_t *d_status, void *stream);
 
+/* Benchmark support for the kernel above (no counterpart in the reference): while enabled, every
+ * orca_attn_gather launch is bracketed by CUDA events on its stream and adds {rows that gathered,
+ * neighbour slots gathered} to the two uint64 device counters.  _read synchronises on the recorded
+ * events, returns their summed duration and count, and forgets them. */
+int orca_attn_gather_profile(int32_t enable, void *d_counters);
+int orca_attn_gather_profile_read(double *h_ms_total, int64_t *h_launches);
+
 /* Step 3 (out-projection, merger and LayerNorm, model/temporal_attention.py:48-55 and
  * utils/util.py:21-24): d_out[r] = LN(fc2(relu(fc1([attn | h_src])))).  If d_push_table is
  * non-NULL the row is also written to d_push_table[d_push_ids[r]] when d_push_win[r] != 0, which

@@ -67,6 +67,8 @@ SYMBOLS = {
     "orca_last_occurrence": (C.c_int, [_V, _I32, _V, _I64, _V, _I64, _V, _V, _V, _V]),
     "orca_attn_query": (C.c_int, [C.POINTER(AttnWeights), _V, _V, _I32, _V, _V, _V]),
     "orca_attn_gather": (C.c_int, [_V, _V, _V, _V, _V, _V, _V, _I32, _I32, _V, _V, _V, _V, _V]),
+    "orca_attn_gather_profile": (C.c_int, [_I32, _V]),
+    "orca_attn_gather_profile_read": (C.c_int, [_V, _V]),
     "orca_attn_output": (C.c_int, [C.POINTER(AttnWeights), _V, _V, _V, _V, _I32, _V, _V, _V, _V, _V, _V]),
     "orca_history_pull": (C.c_int, [_V, _V, _I64, _V, _V]),
     "orca_history_push": (C.c_int, [_V, _V, _V, _V, _I32, _V, _V]),

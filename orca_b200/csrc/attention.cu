@@ -6,6 +6,7 @@
 //   in : qt row (4128 B) + up to K * (688 + 688) B of gathered rows + K * 12 B of indices
 //   out: ctx row (4128 B) + 1 flag
 #include <algorithm>
+#include <vector>
 
 #include "common.cuh"
 
@@ -55,7 +56,8 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
                    const float *__restrict__ edge_table, const float *__restrict__ time_w,
                    const int32_t *__restrict__ nbr, const int32_t *__restrict__ eid,
                    const float *__restrict__ delta, int k, int n_cap, const int32_t *__restrict__ d_n,
-                   float *__restrict__ ctx, uint8_t *__restrict__ valid_out, int32_t *status) {
+                   float *__restrict__ ctx, uint8_t *__restrict__ valid_out, int32_t *status,
+                   unsigned long long *__restrict__ prof) {
   extern __shared__ __align__(128) float smem[];
   __shared__ __align__(8) uint64_t bar;
   __shared__ int s_nbr[ORCA_MAX_K];
@@ -94,6 +96,10 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
       continue;
     }
 
+    if (tid == 0 && prof != nullptr) {
+      atomicAdd(&prof[0], 1ull);                            // rows that gathered
+      atomicAdd(&prof[1], (unsigned long long)n_valid);     // gathered neighbour slots
+    }
     if (tid == 0) {
       // the previous row's reads of the staging area are ordered before these writes
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -180,6 +186,39 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
 
 using namespace orca;
 
+// optional in-situ timing of this kernel (benchmark support): CUDA events around every launch
+namespace {
+struct GatherProfile {
+  bool on = false;
+  unsigned long long *d_counters = nullptr;
+  std::vector<cudaEvent_t> ev;   // pairs (start, stop)
+  size_t used = 0;
+};
+GatherProfile g_prof;
+}  // namespace
+
+extern "C" int orca_attn_gather_profile(int32_t enable, void *d_counters) {
+  g_prof.on = enable != 0;
+  g_prof.d_counters = (unsigned long long *)d_counters;
+  g_prof.used = 0;
+  return ORCA_OK;
+}
+
+extern "C" int orca_attn_gather_profile_read(double *h_ms_total, int64_t *h_launches) {
+  ORCA_CHECK_ARG(h_ms_total && h_launches);
+  double total = 0.0;
+  for (size_t i = 0; i + 1 < g_prof.used; i += 2) {
+    ORCA_CUDA(cudaEventSynchronize(g_prof.ev[i + 1]));
+    float ms = 0.f;
+    ORCA_CUDA(cudaEventElapsedTime(&ms, g_prof.ev[i], g_prof.ev[i + 1]));
+    total += ms;
+  }
+  *h_ms_total = total;
+  *h_launches = (int64_t)(g_prof.used / 2);
+  g_prof.used = 0;
+  return ORCA_OK;
+}
+
 extern "C" int orca_attn_gather(const float *d_qt, const float *d_nbr_table, const float *d_edge_table,
                                 const float *d_time_w, const int32_t *d_nbr, const int32_t *d_eid,
                                 const float *d_delta, int32_t k, int32_t n_rows_cap,
@@ -200,9 +239,23 @@ extern "C" int orca_attn_gather(const float *d_qt, const float *d_nbr_table, con
                                    (QT + ORCA_MAX_K * KEY) * (int)sizeof(float)));
     configured_device = dev;
   }
+  if (g_prof.on) {
+    if (g_prof.used + 2 > g_prof.ev.size()) {
+      cudaEvent_t a, b;
+      ORCA_CUDA(cudaEventCreate(&a));
+      ORCA_CUDA(cudaEventCreate(&b));
+      g_prof.ev.push_back(a);
+      g_prof.ev.push_back(b);
+    }
+    ORCA_CUDA(cudaEventRecord(g_prof.ev[g_prof.used], (cudaStream_t)stream));
+  }
   attn_gather_kernel<<<std::min(n_rows_cap, 148 * 8), GA_THREADS, smem, (cudaStream_t)stream>>>(
       d_qt, d_nbr_table, d_edge_table, d_time_w, d_nbr, d_eid, d_delta, k, n_rows_cap, d_n_rows, d_ctx,
-      d_valid, d_status);
+      d_valid, d_status, g_prof.on ? g_prof.d_counters : nullptr);
+  if (g_prof.on) {
+    ORCA_CUDA(cudaEventRecord(g_prof.ev[g_prof.used + 1], (cudaStream_t)stream));
+    g_prof.used += 2;
+  }
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;
