@@ -1,6 +1,6 @@
 """Kernel-level parity on the GPU: every entry point of the C ABI against the CPU oracle on the
 same seeded inputs.  Integer outputs must be identical; floating-point outputs within the stated
-tolerance (fp32 kernels: 2e-5 relative to a 0.05 floor)."""
+tolerance (fp32 kernels: 1e-4 relative to a 0.05 floor)."""
 import numpy as np
 import pytest
 import torch
@@ -11,7 +11,7 @@ from oracle import tgn_oracle
 pytestmark = pytest.mark.gpu
 
 D = 172
-TOL = 2e-5
+TOL = 1e-4
 
 
 @pytest.fixture(scope="module")
