@@ -41,6 +41,7 @@ extern "C" {
 #define ORCA_MSG_DIM (4 * ORCA_DIM)          /* [mem_src | mem_dst | edge feat | time enc] */
 #define ORCA_KEY_DIM (3 * ORCA_DIM)          /* [neighbour | edge feat | time enc]         */
 #define ORCA_QT_DIM (ORCA_HEADS * ORCA_KEY_DIM)
+#define ORCA_QT_LD 1056                      /* row stride of the projected query: 2 heads x 528 */
 
 const char *orca_last_error(void);
 int orca_version(void);
@@ -108,14 +109,17 @@ int orca_last_occurrence(const int32_t *d_ids, int32_t n_cap, const int32_t *d_n
 /* ------------------------------------------------------------------------------------------
  * Prepared weights of one attention layer (host side composes them once per weight update from
  * the reference's parameters; see orca_b200/weights.py for the algebra):
- *   qt   = h_src . Mq + cq                                  [*, 1032]  (scaled, K-projected query)
+ *   qt   = h_src . Mq + cq                                  [*, 2 x 528] (scaled, K-projected query;
+ *                                                            516 used per head, stride ORCA_QT_LD)
  *   hid  = relu([ctx | h_src] . G + b1 + valid * g)         [*, 172]
  *   out  = LayerNorm(hid . W2t + b2) * ln_w + ln_b          [*, 172]
- * All matrices are row-major [in, out] float32.
+ * All matrices are row-major [in, out] float32.  The *_tc members hold the same matrices split into
+ * TF32 head and tail and packed into the stage images of the tensor-core kernel
+ * (orca_b200/weights.py: pack_tc).
  */
 typedef struct {
-  const float *Mq;   /* [172, 1032]  */
-  const float *cq;   /* [1032]       */
+  const float *Mq;   /* [172, 1056]  */
+  const float *cq;   /* [1056]       */
   const float *G;    /* [1204, 172]  */
   const float *b1;   /* [172]        */
   const float *g;    /* [172]        */
@@ -123,10 +127,19 @@ typedef struct {
   const float *b2;   /* [172]        */
   const float *ln_w; /* [172]        */
   const float *ln_b; /* [172]        */
+  const float *Mq_tc, *G_tc, *W2t_tc;
 } orca_attn_weights_t;
 
 /* Step 1 of TemporalAttentionLayer.forward (model/temporal_attention.py:41-48, the query side of
  * nn.MultiheadAttention): qt[r] = feat[idx ? idx[r] : r] . Mq + cq. */
+/* Projection kernels: 0 (default) = tcgen05 tensor cores with split-TF32 operands (error ~1e-6),
+ * 1 = plain fp32 SIMT tiles (debug reference for the tensor-core path). Process-wide. */
+int orca_set_projection_mode(int32_t mode);
+/* Device status word (int32[4], see orca_read_status) to which the projection kernels report a
+ * bounded wait that gave up; NULL (default) = not reported.  orca_tgn_eval_batch sets it to its own
+ * d_status.  Process-wide. */
+int orca_set_status_word(int32_t *d_status);
+
 int orca_attn_query(const orca_attn_weights_t *w, const float *d_feat, const int32_t *d_idx,
                     int32_t n_rows_cap, const int32_t *d_n_rows, float *d_qt, void *stream);
 
@@ -134,6 +147,7 @@ int orca_attn_query(const orca_attn_weights_t *w, const float *d_feat, const int
  * model/time_encoding.py:23-28 and the gathers of modules/embedding_module.py:262-270 and
  * modules/history.py:32-36): per row, gather the k neighbour rows of d_nbr_table and edge-feature
  * rows, encode cos(delta * w_time), masked 2-head softmax over the slots, weighted key sum.
+ *   d_qt    [n_rows_cap, ORCA_QT_LD]
  *   d_ctx   [n_rows_cap, 1032]   sum_j a_hj * [nbr_j | efeat_j | tenc_j] per head
  *   d_valid [n_rows_cap]         0 where every slot is padding (the layer output of such a row
  *                                ignores the attention term, model/temporal_attention.py:46,52)
@@ -153,11 +167,13 @@ int orca_attn_gather_profile_read(double *h_ms_total, int64_t *h_launches);
 /* Step 3 (out-projection, merger and LayerNorm, model/temporal_attention.py:48-55 and
  * utils/util.py:21-24): d_out[r] = LN(fc2(relu(fc1([attn | h_src])))).  If d_push_table is
  * non-NULL the row is also written to d_push_table[d_push_ids[r]] when d_push_win[r] != 0, which
- * is History.push (modules/history.py:38-40) with the last occurrence of an id winning. */
+ * is History.push (modules/history.py:38-40) with the last occurrence of an id winning.
+ * d_scratch_hidden: [n_rows_cap, 172] floats for the merger's hidden layer. */
 int orca_attn_output(const orca_attn_weights_t *w, const float *d_ctx, const uint8_t *d_valid,
                      const float *d_feat, const int32_t *d_idx, int32_t n_rows_cap,
                      const int32_t *d_n_rows, float *d_out, float *d_push_table,
-                     const int32_t *d_push_ids, const uint8_t *d_push_win, void *stream);
+                     const int32_t *d_push_ids, const uint8_t *d_push_win, float *d_scratch_hidden,
+                     void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Historical-embedding cache.  Replace History.pull / push / update_flag
@@ -183,6 +199,7 @@ typedef struct {
   const float *b1;  /* [172]      */
   const float *w2;  /* [172]      */
   float b2;
+  const float *W1t_tc;
 } orca_score_weights_t;
 int orca_score(const orca_score_weights_t *w, const float *d_emb, int32_t b, float *d_prob, void *stream);
 
@@ -214,7 +231,8 @@ int orca_message_store(const orca_memory_t *mem, const float *d_edge_table, cons
  * (r, z, n_input, n_hidden) interleaved], bg [688] likewise. */
 typedef struct {
   const float *Wg;
-  const float *bg;
+  const float *bg;     /* padded to 704 entries */
+  const float *Wg_tc;
 } orca_gru_weights_t;
 
 /* Replaces SequenceMemoryUpdater.update_memory / update_memory_in_test with nn.GRUCell

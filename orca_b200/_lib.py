@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "liborca_b200.so")
 
 DIM = 172
 QT_DIM = 1032
+QT_LD = 1056
 MSG_DIM = 688
 
 c_f32p = C.c_void_p
@@ -22,15 +23,17 @@ c_i32p = C.c_void_p
 
 
 class AttnWeights(C.Structure):
-    _fields_ = [(n, C.c_void_p) for n in ("Mq", "cq", "G", "b1", "g", "W2t", "b2", "ln_w", "ln_b")]
+    _fields_ = [(n, C.c_void_p) for n in ("Mq", "cq", "G", "b1", "g", "W2t", "b2", "ln_w", "ln_b",
+                                          "Mq_tc", "G_tc", "W2t_tc")]
 
 
 class ScoreWeights(C.Structure):
-    _fields_ = [("W1t", C.c_void_p), ("b1", C.c_void_p), ("w2", C.c_void_p), ("b2", C.c_float)]
+    _fields_ = [("W1t", C.c_void_p), ("b1", C.c_void_p), ("w2", C.c_void_p), ("b2", C.c_float),
+                ("W1t_tc", C.c_void_p)]
 
 
 class GruWeights(C.Structure):
-    _fields_ = [("Wg", C.c_void_p), ("bg", C.c_void_p)]
+    _fields_ = [("Wg", C.c_void_p), ("bg", C.c_void_p), ("Wg_tc", C.c_void_p)]
 
 
 class MemoryT(C.Structure):
@@ -69,7 +72,9 @@ SYMBOLS = {
     "orca_attn_gather": (C.c_int, [_V, _V, _V, _V, _V, _V, _V, _I32, _I32, _V, _V, _V, _V, _V]),
     "orca_attn_gather_profile": (C.c_int, [_I32, _V]),
     "orca_attn_gather_profile_read": (C.c_int, [_V, _V]),
-    "orca_attn_output": (C.c_int, [C.POINTER(AttnWeights), _V, _V, _V, _V, _I32, _V, _V, _V, _V, _V, _V]),
+    "orca_attn_output": (C.c_int, [C.POINTER(AttnWeights), _V, _V, _V, _V, _I32, _V, _V, _V, _V, _V, _V, _V]),
+    "orca_set_projection_mode": (C.c_int, [_I32]),
+    "orca_set_status_word": (C.c_int, [_V]),
     "orca_history_pull": (C.c_int, [_V, _V, _I64, _V, _V]),
     "orca_history_push": (C.c_int, [_V, _V, _V, _V, _I32, _V, _V]),
     "orca_history_set_flags": (C.c_int, [_V, _I64, _V, _I32, _V, _I32, _V]),
@@ -122,6 +127,14 @@ def ptr(t):
     if isinstance(t, np.ndarray):
         return t.ctypes.data
     raise TypeError(type(t))
+
+
+ATTN_FIELDS = ("Mq", "cq", "G", "b1", "g", "W2t", "b2", "ln_w", "ln_b", "Mq_tc", "G_tc", "W2t_tc")
+
+
+def attn_struct(w):
+    """AttnWeights from a dict of device tensors (weights.prepare_attention uploaded)."""
+    return AttnWeights(*[w[k].data_ptr() for k in ATTN_FIELDS])
 
 
 def stream_ptr(device=None):

@@ -104,7 +104,8 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
       // the previous row's reads of the staging area are ordered before these writes
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_expect_tx(&bar, (uint32_t)(QT * 4 + n_valid * 2 * ROW_BYTES));
-      bulk_g2s(s_qt, qt + (size_t)row * QT, QT * 4, &bar);
+      bulk_g2s(s_qt, qt + (size_t)row * QT_LD, KEY * 4, &bar);
+      bulk_g2s(s_qt + KEY, qt + (size_t)row * QT_LD + QT_HEAD, KEY * 4, &bar);
       for (int j = 0; j < k; ++j) {
         if (s_nbr[j] != 0) {
           bulk_g2s(s_key + j * KEY, nbr_table + (size_t)s_nbr[j] * D, ROW_BYTES, &bar);

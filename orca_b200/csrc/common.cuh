@@ -13,6 +13,8 @@ constexpr int D = ORCA_DIM;          // 172 floats = 688 bytes = 43 x 16 bytes
 constexpr int H = ORCA_HEADS;        // 2
 constexpr int KEY = ORCA_KEY_DIM;    // 516
 constexpr int QT = ORCA_QT_DIM;      // 1032
+constexpr int QT_LD = ORCA_QT_LD;    // 1056: head h of a projected query starts at h * 528
+constexpr int QT_HEAD = QT_LD / H;   // 528
 constexpr int MSG = ORCA_MSG_DIM;    // 688
 constexpr int ROW_BYTES = D * 4;     // 688
 

@@ -6,6 +6,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "tc_gemm.cuh"
 
 namespace orca {
 
@@ -380,6 +381,9 @@ __global__ void gru_clear_kernel(orca_memory_t mem, const int32_t *__restrict__ 
 
 using namespace orca;
 
+static int g_projection_mode = 0;  // 0 = tensor cores (split TF32), 1 = fp32 SIMT tiles
+static int32_t *g_status_word = nullptr;  // where the projection kernels report bounded-wait time-outs
+
 static int ensure_f2_smem() {
   static thread_local int configured_device = -1;
   int dev = 0;
@@ -394,23 +398,51 @@ static int ensure_f2_smem() {
   return ORCA_OK;
 }
 
+static inline int kblocks(int k) { return (k + tc::BK - 1) / tc::BK; }
+
 extern "C" {
+
+int orca_set_status_word(int32_t *d_status) {
+  g_status_word = d_status;
+  return ORCA_OK;
+}
+
+int orca_set_projection_mode(int32_t mode) {
+  ORCA_CHECK_ARG(mode == 0 || mode == 1);
+  g_projection_mode = mode;
+  return ORCA_OK;
+}
 
 int orca_attn_query(const orca_attn_weights_t *w, const float *d_feat, const int32_t *d_idx,
                     int32_t n_rows_cap, const int32_t *d_n_rows, float *d_qt, void *stream) {
   ORCA_CHECK_ARG(w && w->Mq && w->cq && d_feat && d_qt && n_rows_cap >= 0);
   if (n_rows_cap == 0) return ORCA_OK;
+  if (g_projection_mode == 0) {
+    ORCA_CHECK_ARG(w->Mq_tc != nullptr);
+    tc::Args a{};
+    a.status = g_status_word;
+    a.a0 = tc::RowSrc{d_feat, d_idx, D, 0, 0};
+    a.Kd = D;
+    a.w_packed = w->Mq_tc;
+    a.n_kblocks = kblocks(D);
+    a.m_cap = n_rows_cap;
+    a.d_m = d_n_rows;
+    a.bias = w->cq;
+    a.out = d_qt;
+    a.out_ld = QT_LD;
+    return tc::launch(tc::EPI_BIAS, a, QT_LD / tc::BN, (cudaStream_t)stream);
+  }
   F1Args g{};
   g.a0 = RowSrc{d_feat, d_idx, D, 0, 0};
   g.a1 = RowSrc{nullptr, nullptr, 0, 0, 0};
   g.Kd = D;
   g.B = w->Mq;
-  g.Nc = QT;
+  g.Nc = QT_LD;
   g.bias = w->cq;
   g.m_cap = n_rows_cap;
   g.d_m = d_n_rows;
   g.C = d_qt;
-  dim3 grid(ceil_div(QT, F1_BN), std::min(ceil_div(n_rows_cap, F1_BM), 148));
+  dim3 grid(ceil_div(QT_LD, F1_BN), std::min(ceil_div(n_rows_cap, F1_BM), 148));
   f1_gemm_kernel<EPI_BIAS><<<grid, F1_THREADS, 0, (cudaStream_t)stream>>>(g);
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
@@ -420,11 +452,47 @@ int orca_attn_query(const orca_attn_weights_t *w, const float *d_feat, const int
 int orca_attn_output(const orca_attn_weights_t *w, const float *d_ctx, const uint8_t *d_valid,
                      const float *d_feat, const int32_t *d_idx, int32_t n_rows_cap,
                      const int32_t *d_n_rows, float *d_out, float *d_push_table,
-                     const int32_t *d_push_ids, const uint8_t *d_push_win, void *stream) {
+                     const int32_t *d_push_ids, const uint8_t *d_push_win, float *d_scratch_hidden,
+                     void *stream) {
   ORCA_CHECK_ARG(w && w->G && w->b1 && w->g && w->W2t && w->b2 && w->ln_w && w->ln_b);
   ORCA_CHECK_ARG(d_ctx && d_valid && d_feat && d_out && n_rows_cap >= 0);
   ORCA_CHECK_ARG(d_push_table == nullptr || (d_push_ids && d_push_win));
   if (n_rows_cap == 0) return ORCA_OK;
+  if (g_projection_mode == 0) {
+    ORCA_CHECK_ARG(w->G_tc && w->W2t_tc && d_scratch_hidden);
+    tc::Args a{};
+    a.status = g_status_word;
+    a.a0 = tc::RowSrc{d_ctx, nullptr, QT, 0, 0};
+    a.a1 = tc::RowSrc{d_feat, d_idx, D, 0, 0};
+    a.Kd = QT + D;
+    a.row_valid = d_valid;
+    a.zero_cols = QT;
+    a.w_packed = w->G_tc;
+    a.n_kblocks = kblocks(QT + D);
+    a.m_cap = n_rows_cap;
+    a.d_m = d_n_rows;
+    a.bias = w->b1;
+    a.bias2 = w->g;
+    a.out = d_scratch_hidden;
+    int rc = tc::launch(tc::EPI_HIDDEN, a, 1, (cudaStream_t)stream);
+    if (rc) return rc;
+    tc::Args b{};
+    b.status = g_status_word;
+    b.a0 = tc::RowSrc{d_scratch_hidden, nullptr, D, 0, 0};
+    b.Kd = D;
+    b.w_packed = w->W2t_tc;
+    b.n_kblocks = kblocks(D);
+    b.m_cap = n_rows_cap;
+    b.d_m = d_n_rows;
+    b.bias = w->b2;
+    b.ln_w = w->ln_w;
+    b.ln_b = w->ln_b;
+    b.out = d_out;
+    b.push_table = d_push_table;
+    b.push_ids = d_push_ids;
+    b.push_win = d_push_win;
+    return tc::launch(tc::EPI_LAYERNORM, b, 1, (cudaStream_t)stream);
+  }
   int rc = ensure_f2_smem();
   if (rc) return rc;
   OutArgs g{};
@@ -447,6 +515,23 @@ int orca_attn_output(const orca_attn_weights_t *w, const float *d_ctx, const uin
 int orca_score(const orca_score_weights_t *w, const float *d_emb, int32_t b, float *d_prob, void *stream) {
   ORCA_CHECK_ARG(w && w->W1t && w->b1 && w->w2 && d_emb && d_prob && b >= 0);
   if (b == 0) return ORCA_OK;
+  if (g_projection_mode == 0) {
+    ORCA_CHECK_ARG(w->W1t_tc != nullptr);
+    tc::Args a{};
+    a.status = g_status_word;
+    // row m < b pairs (src m, dst m); row m >= b pairs (src m-b, neg m-b): table rows m % b and b + m
+    a.a0 = tc::RowSrc{d_emb, nullptr, D, b, 0};
+    a.a1 = tc::RowSrc{d_emb, nullptr, D, 0, b};
+    a.Kd = 2 * D;
+    a.w_packed = w->W1t_tc;
+    a.n_kblocks = kblocks(2 * D);
+    a.m_cap = 2 * b;
+    a.bias = w->b1;
+    a.w2 = w->w2;
+    a.b2 = w->b2;
+    a.out = d_prob;
+    return tc::launch(tc::EPI_SCORE, a, 1, (cudaStream_t)stream);
+  }
   int rc = ensure_f2_smem();
   if (rc) return rc;
   ScoreArgs g{*w, d_emb, b, d_prob};
@@ -465,21 +550,40 @@ int orca_gru_update(const orca_gru_weights_t *w, const orca_memory_t *mem, const
                  mem->msg_ts && mem->msg_flag && d_nodes && d_scratch_h && n_cap >= 0);
   if (n_cap == 0) return ORCA_OK;
   cudaStream_t s = (cudaStream_t)stream;
-  F1Args g{};
-  g.a0 = RowSrc{mem->messages, d_nodes, MSG, 0, 0};
-  g.a1 = RowSrc{mem->memory, d_nodes, D, 0, 0};
-  g.Kd = MSG + D;
-  g.B = w->Wg;
-  g.Nc = 4 * D;
-  g.bias = w->bg;
-  g.m_cap = n_cap;
-  g.d_m = d_n;
-  g.C = d_scratch_h;
-  g.memory = mem->memory;
-  g.nodes = d_nodes;
-  dim3 grid(ceil_div(4 * D, F1_BN), std::min(ceil_div(n_cap, F1_BM), 148));
-  f1_gemm_kernel<EPI_GRU><<<grid, F1_THREADS, 0, s>>>(g);
-  ORCA_COUNT_LAUNCH();
+  if (g_projection_mode == 0) {
+    ORCA_CHECK_ARG(w->Wg_tc != nullptr);
+    tc::Args a{};
+    a.status = g_status_word;
+    a.a0 = tc::RowSrc{mem->messages, d_nodes, MSG, 0, 0};
+    a.a1 = tc::RowSrc{mem->memory, d_nodes, D, 0, 0};
+    a.Kd = MSG + D;
+    a.w_packed = w->Wg_tc;
+    a.n_kblocks = kblocks(MSG + D);
+    a.m_cap = n_cap;
+    a.d_m = d_n;
+    a.bias = w->bg;
+    a.out = d_scratch_h;
+    a.memory = mem->memory;
+    a.nodes = d_nodes;
+    int rc = tc::launch(tc::EPI_GRU, a, 4, s);
+    if (rc) return rc;
+  } else {
+    F1Args g{};
+    g.a0 = RowSrc{mem->messages, d_nodes, MSG, 0, 0};
+    g.a1 = RowSrc{mem->memory, d_nodes, D, 0, 0};
+    g.Kd = MSG + D;
+    g.B = w->Wg;
+    g.Nc = 4 * D;
+    g.bias = w->bg;
+    g.m_cap = n_cap;
+    g.d_m = d_n;
+    g.C = d_scratch_h;
+    g.memory = mem->memory;
+    g.nodes = d_nodes;
+    dim3 grid(ceil_div(4 * D, F1_BN), std::min(ceil_div(n_cap, F1_BM), 148));
+    f1_gemm_kernel<EPI_GRU><<<grid, F1_THREADS, 0, s>>>(g);
+    ORCA_COUNT_LAUNCH();
+  }
   gru_scatter_kernel<<<ceil_div(n_cap, 4), 256, 0, s>>>(d_scratch_h, *mem, d_nodes, n_cap, d_n, clear_flags);
   ORCA_COUNT_LAUNCH();
   if (clear_flags) {

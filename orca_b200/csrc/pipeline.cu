@@ -17,6 +17,7 @@ struct Workspace {
   float *qt, *ctx, *emb1, *emb2;
   int32_t *cat_dst; uint8_t *is_last2; int32_t *win_pos; int32_t *n_win; int32_t *win_nodes;
   float *gru_h;
+  float *hidden;
   void *bitmap;
   size_t bytes;
 };
@@ -38,7 +39,7 @@ static Workspace carve(void *base, int b_cap, int u_cap, int k, int64_t n_nodes)
   w.dt1 = (float *)take(R1 * k * 4);
   w.win1 = (uint8_t *)take(R1);
   w.valid = (uint8_t *)take(R1);
-  w.qt = (float *)take(R1 * QT * 4);
+  w.qt = (float *)take(R1 * QT_LD * 4);
   w.ctx = (float *)take(R1 * QT * 4);
   w.emb1 = (float *)take(R1 * D * 4);
   w.emb2 = (float *)take(N * D * 4);
@@ -48,6 +49,7 @@ static Workspace carve(void *base, int b_cap, int u_cap, int k, int64_t n_nodes)
   w.n_win = (int32_t *)take(4);
   w.win_nodes = (int32_t *)take(2 * (size_t)b_cap * 4);
   w.gru_h = (float *)take(2 * (size_t)b_cap * D * 4);
+  w.hidden = (float *)take(R1 * D * 4);
   w.bitmap = take((size_t)orca_find_uncached_scratch_bytes(n_nodes));
   w.bytes = off;
   return w;
@@ -122,6 +124,7 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     return set_error(ORCA_E_CAPACITY, "orca_tgn_eval_batch: workspace of %lld bytes, %lld needed",
                      (long long)workspace_bytes, (long long)w.bytes);
   cudaStream_t s = (cudaStream_t)stream;
+  orca_set_status_word(d_status);
   launch_counter() = 0;
   const int N = 3 * b, R1 = N + u_cap;
 
@@ -137,7 +140,7 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     ORCA_TRY(orca_attn_gather(w.qt, m->mem.memory, m->edge_table, m->time_w, w.nbr1, w.eid1, w.dt1, k, N,
                               nullptr, w.ctx, w.valid, d_status, s));
     ORCA_TRY(orca_attn_output(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.nodes1, N, nullptr, emb_top,
-                              nullptr, nullptr, nullptr, s));
+                              nullptr, nullptr, nullptr, w.hidden, s));
   } else {
     // top-level neighbour table, then the uncached out-of-batch neighbours join the row list
     ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
@@ -154,7 +157,7 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     ORCA_TRY(orca_attn_gather(w.qt, m->mem.memory, m->edge_table, m->time_w, w.nbr1, w.eid1, w.dt1, k, R1,
                               w.n1, w.ctx, w.valid, d_status, s));
     ORCA_TRY(orca_attn_output(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.nodes1, R1, w.n1, w.emb1,
-                              m->hist_emb, w.nodes1, w.win1, s));
+                              m->hist_emb, w.nodes1, w.win1, w.hidden, s));
     // cache flags follow the plan of this batch (History.update_flag)
     if (d_plan != nullptr) {
       const bool know_prev = *m->n_prev_plan >= 0;
@@ -177,7 +180,7 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     ORCA_TRY(orca_attn_gather(w.qt, m->hist_emb, m->edge_table, m->time_w, w.nbr2, w.eid2, w.dt2, k, N,
                               nullptr, w.ctx, w.valid, d_status, s));
     ORCA_TRY(orca_attn_output(&m->attn[1], w.ctx, w.valid, w.emb1, nullptr, N, nullptr, emb_top, nullptr,
-                              nullptr, nullptr, s));
+                              nullptr, nullptr, w.hidden, s));
   }
 
   ORCA_TRY(orca_score(&m->score, emb_top, b, d_prob, s));

@@ -1,0 +1,68 @@
+// Interface of the tensor-core projection kernel (tc_gemm.cu).
+#pragma once
+
+#include "common.cuh"
+
+namespace orca {
+namespace tc {
+
+constexpr int BM = 128;      // tile rows (accumulator lanes)
+constexpr int BN = 176;      // tile columns (172 padded to a multiple of 16)
+constexpr int BK = 16;       // floats of K per stage = 4 chunks of 16 bytes = 2 MMA steps of K = 8
+constexpr int STAGES = 4;
+constexpr int THREADS = 192;
+constexpr int A_LBO = BM * 16 + 16;   // chunk stride of the A image; +16 keeps the row-per-thread stores conflict free
+constexpr int A_SBO = 128;
+constexpr int A_BYTES = (BK / 4) * A_LBO;
+constexpr int B_LBO = BN * 16;
+constexpr int B_SBO = 128;
+constexpr int B_BYTES = (BK / 4) * B_LBO;
+constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;   // A head, A tail, W head, W tail
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int TMEM_COLS = 512;   // main accumulator at column 0, cross-term accumulator at column 256
+constexpr int TMEM_SMALL = 256;
+
+// A logical A row is the concatenation of up to two gathered table rows
+struct RowSrc {
+  const float *p;      // table base, row stride = width floats
+  const int32_t *idx;  // row m reads table row idx[m]; nullptr: (mod > 0 ? m % mod : m) + add
+  int width;
+  int mod;
+  int add;
+};
+
+enum Epilogue { EPI_BIAS = 0, EPI_HIDDEN = 1, EPI_LAYERNORM = 2, EPI_GRU = 3, EPI_SCORE = 4 };
+
+struct Args {
+  RowSrc a0, a1;             // a1.width == 0 when unused
+  int Kd;                    // a0.width + a1.width
+  const uint8_t *row_valid;  // optional: rows with 0 read zeros for the first zero_cols columns
+  int zero_cols;
+  const float *w_packed;     // [n_tiles][n_kblocks][head | tail] stage images (weights.pack_tc)
+  int n_kblocks;
+  int m_cap;
+  const int32_t *d_m;
+  const float *bias;         // [n_tiles * BN]
+  float *out;                // BIAS: [m, out_ld]; HIDDEN / LAYERNORM: [m, 172]; GRU: [m, 172]; SCORE: [m]
+  int out_ld;
+  // HIDDEN: + valid * bias2
+  const float *bias2;
+  // LAYERNORM
+  const float *ln_w, *ln_b;
+  float *push_table;
+  const int32_t *push_ids;
+  const uint8_t *push_win;
+  // GRU
+  const float *memory;
+  const int32_t *nodes;
+  // SCORE
+  const float *w2;
+  float b2;
+  int32_t *status;
+};
+
+// enqueues the kernel: grid = (n_tiles, ceil(m_cap / 128))
+int launch(int epilogue, const Args &a, int n_tiles, cudaStream_t stream);
+
+}  // namespace tc
+}  // namespace orca

@@ -114,7 +114,7 @@ class GRUMemoryUpdater(nn.Module):
 
     def c_struct(self):
         p = self.prepared()
-        return _lib.GruWeights(p["Wg"].data_ptr(), p["bg"].data_ptr())
+        return _lib.GruWeights(p["Wg"].data_ptr(), p["bg"].data_ptr(), p["Wg_tc"].data_ptr())
 
     def _run(self, memory: Memory, ids: torch.Tensor, clear: bool):
         n = ids.numel()

@@ -220,11 +220,12 @@ class TGN(nn.Module):
 
     def attn_struct(self, layer):
         a = self._weights()["attn"][layer]
-        return _lib.AttnWeights(*[a[k].data_ptr() for k in ("Mq", "cq", "G", "b1", "g", "W2t", "b2", "ln_w", "ln_b")])
+        return _lib.attn_struct(a)
 
     def score_struct(self):
         s = self._weights()["score"]
-        return _lib.ScoreWeights(s["W1t"].data_ptr(), s["b1"].data_ptr(), s["w2"].data_ptr(), s["b2"])
+        return _lib.ScoreWeights(s["W1t"].data_ptr(), s["b1"].data_ptr(), s["w2"].data_ptr(), s["b2"],
+                                 s["W1t_tc"].data_ptr())
 
     def set_neighbor_finder(self, neighbor_finder):
         self.neighbor_finder = neighbor_finder

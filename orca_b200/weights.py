@@ -21,6 +21,31 @@ import numpy as np
 
 D = 172
 HEADS = 2
+QT_HEAD = 528     # column stride of one head of the projected query (516 used)
+TC_BN, TC_BK = 176, 16
+
+
+def pack_tc(W):
+    """Packs a row-major [K, N] matrix for the tensor-core kernel (csrc/tc_gemm.cu).
+
+    N is cut into tiles of 176 columns and K into blocks of 16 rows (both zero padded).  One
+    (tile, block) stage image is [head | tail], each [4 chunks][176 columns][4 floats]: element
+    (k, n) of the block sits at chunk k // 4, column n, float k % 4 -- the K-major, no-swizzle
+    core-matrix layout the MMA reads from shared memory -- so that a stage is one contiguous bulk copy.
+    head = the value with the 13 low mantissa bits cleared (exact in TF32), tail = the remainder,
+    cleared the same way."""
+    W = np.asarray(W, dtype=np.float32)
+    K, N = W.shape
+    nkb, nt = -(-K // TC_BK), -(-N // TC_BN)
+    P = np.zeros((nkb * TC_BK, nt * TC_BN), dtype=np.float32)
+    P[:K, :N] = W
+    head = (P.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+    tail = ((P - head).astype(np.float32).view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+
+    def image(X):  # [nkb*16, nt*176] -> [nt, nkb, 4, 176, 4]
+        return X.reshape(nkb, 4, 4, nt, TC_BN).transpose(3, 0, 1, 4, 2)
+
+    return np.ascontiguousarray(np.stack([image(head), image(tail)], axis=2))  # [nt, nkb, 2, 4, 176, 4]
 
 
 def _f64(x):
@@ -46,14 +71,14 @@ def prepare_attention(sd, layer: int, dim: int = D, heads: int = HEADS):
     A = Wq[:, :dim]                                             # [344, 172]
     a = Wq[:, dim:] @ src_t + bq                                # [344]
     s = 1.0 / math.sqrt(hd)
-    Mq = np.zeros((dim, heads * kd))
-    cq = np.zeros(heads * kd)
+    Mq = np.zeros((dim, heads * QT_HEAD))
+    cq = np.zeros(heads * QT_HEAD)
     G = np.zeros((heads * kd + dim, dim))
     W1a, W1b = W1[:, :E], W1[:, E:]
     for h in range(heads):
         rows = slice(h * hd, (h + 1) * hd)
-        Mq[:, h * kd:(h + 1) * kd] = s * (A[rows].T @ Wk[rows])          # [172, 516]
-        cq[h * kd:(h + 1) * kd] = s * (Wk[rows].T @ a[rows])
+        Mq[:, h * QT_HEAD:h * QT_HEAD + kd] = s * (A[rows].T @ Wk[rows])  # [172, 516]
+        cq[h * QT_HEAD:h * QT_HEAD + kd] = s * (Wk[rows].T @ a[rows])
         P_h = Wo[:, rows] @ Wv[rows]                                     # [344, 516]
         G[h * kd:(h + 1) * kd] = (W1a @ P_h).T                           # [516, 172]
     G[heads * kd:] = W1b.T
@@ -63,7 +88,10 @@ def prepare_attention(sd, layer: int, dim: int = D, heads: int = HEADS):
         "W2t": _f64(sd[p + "merger.fc2.weight"]).T, "b2": _f64(sd[p + "merger.fc2.bias"]),
         "ln_w": _f64(sd[p + "norm.weight"]), "ln_b": _f64(sd[p + "norm.bias"]),
     }
-    return {k: np.ascontiguousarray(v, dtype=np.float32) for k, v in out.items()}
+    out = {k: np.ascontiguousarray(v, dtype=np.float32) for k, v in out.items()}
+    for k in ("Mq", "G", "W2t"):
+        out[k + "_tc"] = pack_tc(out[k])
+    return out
 
 
 def prepare_gru(sd, dim: int = D):
@@ -85,12 +113,16 @@ def prepare_gru(sd, dim: int = D):
     bg[4 * j + 2] = bih[2 * dim + j]
     Wg[msg:, 4 * j + 3] = Whh[2 * dim + j].T
     bg[4 * j + 3] = bhh[2 * dim + j]
-    return {"Wg": np.ascontiguousarray(Wg, dtype=np.float32), "bg": bg.astype(np.float32)}
+    Wg = np.ascontiguousarray(Wg, dtype=np.float32)
+    bg_pad = np.zeros(4 * TC_BN, dtype=np.float32)
+    bg_pad[:4 * dim] = bg
+    return {"Wg": Wg, "bg": bg_pad, "Wg_tc": pack_tc(Wg)}
 
 
 def prepare_score(sd):
+    W1t = np.ascontiguousarray(_f64(sd["affinity_score.fc1.weight"]).T, dtype=np.float32)
     return {
-        "W1t": np.ascontiguousarray(_f64(sd["affinity_score.fc1.weight"]).T, dtype=np.float32),
+        "W1t": W1t, "W1t_tc": pack_tc(W1t),
         "b1": np.asarray(sd["affinity_score.fc1.bias"], dtype=np.float32),
         "w2": np.ascontiguousarray(np.asarray(sd["affinity_score.fc2.weight"], dtype=np.float32).reshape(-1)),
         "b2": float(np.asarray(sd["affinity_score.fc2.bias"]).reshape(-1)[0]),

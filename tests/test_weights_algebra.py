@@ -29,6 +29,7 @@ def test_attention_reassociation():
         want = tgn_oracle.attention_layer(p, layer, torch.as_tensor(h_src), torch.as_tensor(h_nbr),
                                           torch.as_tensor(ef), torch.as_tensor(dt), nbr).numpy()
         w = {k: v.astype(np.float64) for k, v in weights.prepare_attention(sd, layer).items()}
+        assert w["Mq"].shape == (172, 1056) and not w["Mq"][:, 516:528].any()
         tw = weights.prepare_time(sd).astype(np.float32)
         qt = h_src.astype(np.float64) @ w["Mq"] + w["cq"]                      # [n, 1032]
         tenc = np.cos((dt[..., None] * tw).astype(np.float32)).astype(np.float64)
@@ -37,7 +38,7 @@ def test_attention_reassociation():
         valid = ~mask.all(axis=1)
         ctx = np.zeros((len(h_src), 2 * 516))
         for h in range(2):
-            logit = np.einsum("nc,nkc->nk", qt[:, h * 516:(h + 1) * 516], key)
+            logit = np.einsum("nc,nkc->nk", qt[:, h * 528:h * 528 + 516], key)
             logit[mask] = -np.inf
             logit[~valid] = 0
             a = np.exp(logit - logit.max(axis=1, keepdims=True))
@@ -58,7 +59,7 @@ def test_gru_and_score_layout():
     h = rs.randn(9, D).astype(np.float32)
     want = tgn_oracle.gru_cell(p, torch.as_tensor(x), torch.as_tensor(h)).numpy()
     g = weights.prepare_gru(sd)
-    acc = np.concatenate([x, h], 1).astype(np.float64) @ g["Wg"].astype(np.float64) + g["bg"]
+    acc = np.concatenate([x, h], 1).astype(np.float64) @ g["Wg"].astype(np.float64) + g["bg"][:4 * D]
     acc = acc.reshape(9, D, 4)
     sig = lambda v: 1 / (1 + np.exp(-v))
     r, z = sig(acc[..., 0]), sig(acc[..., 1])
@@ -70,3 +71,20 @@ def test_gru_and_score_layout():
     s = weights.prepare_score(sd)
     hid = np.maximum(np.concatenate([a, b], 1).astype(np.float64) @ s["W1t"] + s["b1"], 0)
     assert np.max(np.abs(sig(hid @ s["w2"] + s["b2"]) - want)) < 1e-6
+
+
+def test_tensor_core_weight_packing():
+    """head + tail reproduces the matrix to ~2^-21 and the stage image puts element (k, n) at
+    [tile n // 176][block k // 16][part][chunk (k % 16) // 4][column n % 176][k % 4]."""
+    rs = np.random.RandomState(0)
+    W = rs.randn(1204, 172).astype(np.float32)
+    P = weights.pack_tc(W)
+    assert P.shape == (1, 76, 2, 4, 176, 4) and P.dtype == np.float32
+    assert not (P.view(np.uint32) & 0x1FFF).any()                      # both parts are exact TF32 values
+    rec = (P[:, :, 0] + P[:, :, 1]).transpose(1, 2, 4, 0, 3).reshape(76 * 16, 176)   # [k, n]
+    assert np.max(np.abs(rec[:1204, :172] - W) / np.maximum(np.abs(W), 1e-30)) < 2 ** -20
+    assert not rec[1204:].any() and not rec[:, 172:].any()
+    k, n = 1000, 37
+    assert P[0, k // 16, 0, (k % 16) // 4, n, k % 4] + P[0, k // 16, 1, (k % 16) // 4, n, k % 4] == rec[k, n]
+    Wq = rs.randn(172, 1056).astype(np.float32)
+    assert weights.pack_tc(Wq).shape == (6, 11, 2, 4, 176, 4)
