@@ -286,6 +286,7 @@ def run_ours(a):
         abi_step(i)
     torch.cuda.synchronize()
     _lib.check(L.orca_attn_gather_profile(1, counters.data_ptr()))
+    _lib.check(L.orca_trace(1))
     step_bytes = 0
     for i in range(K):
         abi_step(W + i)
@@ -297,6 +298,11 @@ def run_ours(a):
     gl = np.zeros(1, dtype=np.int64)
     _lib.check(L.orca_attn_gather_profile_read(gms.ctypes.data, gl.ctypes.data))
     _lib.check(L.orca_attn_gather_profile(0, None))
+    n_ph = L.orca_trace_phases()
+    ph_ms = np.zeros(n_ph, dtype=np.float64)
+    _lib.check(L.orca_trace_read(ph_ms.ctypes.data))
+    _lib.check(L.orca_trace(0))
+    phases = {L.orca_trace_phase_name(i).decode(): round(float(ph_ms[i]) * 1e3 / K, 2) for i in range(n_ph)}
     rows_g, slots_g = (int(x) for x in counters.cpu().numpy())
     peak, peak_kind = load_peaks()
     gather_bytes = rows_g * (2 * ROW_BYTES + 12 * k) + slots_g * 2 * ROW_BYTES
@@ -314,7 +320,8 @@ def run_ours(a):
             "dtype": "f32", "data": "synthetic",
             "config": workload_config(g, spec, first + W, {"whole_step_hbm_frac": step_frac,
                                                            "algorithmic_bytes_per_edge": step_bytes / edges}),
-            "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches_per_batch * K), "clocks": clocks}
+            "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches_per_batch * K), "clocks": clocks,
+            "phases_us_per_step": phases}
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(a, g, neg, plan, first + W)
     if rank == 0:

@@ -304,6 +304,15 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
                         void *d_workspace, int64_t workspace_bytes, float *d_prob,
                         float *d_emb_out, int32_t *d_status, void *stream);
 
+/* Phase tracing of orca_tgn_eval_batch (the reference only has wall-clock deltas around whole
+ * epochs, train.py:189-341): while enabled, CUDA events are recorded at the phase boundaries of every
+ * batch; orca_trace_read synchronises on them, returns the summed milliseconds per phase
+ * (orca_trace_phases() entries, names from orca_trace_phase_name) and forgets them. */
+int orca_trace(int32_t enable);
+int orca_trace_phases(void);
+const char *orca_trace_phase_name(int32_t phase);
+int orca_trace_read(double *h_ms_per_phase);
+
 /* Copies the device status words to the host (synchronises `stream`), returns the first nonzero
  * code and resets the device words. h_counts (may be NULL) receives {status, n_layer1_rows,
  * n_unique_positives, kernels launched by the last batch}. */

@@ -2,6 +2,7 @@
 // sample -> find uncached -> sample -> attention layer 1 (memory rows) -> history push / flags ->
 // attention layer 2 (history rows) -> link scores -> raw messages -> GRU memory update.
 #include <algorithm>
+#include <vector>
 
 #include "common.cuh"
 
@@ -89,6 +90,34 @@ __global__ void publish_counts_kernel(const int32_t *n1, const int32_t *n_win, i
 
 static thread_local int g_last_batch_launches = 0;
 
+// Optional per-phase timing of the eval batch: CUDA events at the phase boundaries, summed per phase.
+enum Phase { PH_PREP, PH_SAMPLE_TOP, PH_UNCACHED, PH_SAMPLE_L1, PH_LAST_OCC_L1, PH_QUERY_L1, PH_GATHER_L1,
+             PH_OUTPUT_L1, PH_FLAGS, PH_QUERY_L2, PH_GATHER_L2, PH_OUTPUT_L2, PH_SCORE, PH_LAST_OCC_MSG,
+             PH_MESSAGE, PH_GRU, PH_COUNT };
+static const char *kPhaseNames[PH_COUNT] = {"prep", "sample_top", "find_uncached", "sample_l1", "last_occurrence_l1",
+                                            "attn_query_l1", "attn_gather_l1", "attn_output_l1", "set_flags",
+                                            "attn_query_l2", "attn_gather_l2", "attn_output_l2", "score",
+                                            "last_occurrence_msg", "message_store", "gru_update"};
+struct Tracer {
+  bool on = false;
+  std::vector<cudaEvent_t> ev;        // PH_COUNT + 1 events per traced batch
+  std::vector<int> phase_of;          // phase that ENDS at event i (or -1 for a batch's first event)
+  size_t used = 0;
+  int mark(int phase, cudaStream_t s) {
+    if (!on) return ORCA_OK;
+    if (used == ev.size()) {
+      cudaEvent_t e;
+      ORCA_CUDA(cudaEventCreate(&e));
+      ev.push_back(e);
+      phase_of.push_back(-1);
+    }
+    phase_of[used] = phase;
+    ORCA_CUDA(cudaEventRecord(ev[used++], s));
+    return ORCA_OK;
+  }
+};
+static Tracer g_trace;
+
 }  // namespace orca
 
 using namespace orca;
@@ -128,36 +157,49 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
   launch_counter() = 0;
   const int N = 3 * b, R1 = N + u_cap;
 
+  ORCA_TRY(g_trace.mark(-1, s));
   batch_prep_kernel<<<ceil_div(N, 256), 256, 0, s>>>(d_batch_i32, d_batch_ts, b, w.nodes1, w.ts1, w.cat_dst, w.n1);
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
+  ORCA_TRY(g_trace.mark(PH_PREP, s));
 
   float *emb_top = d_emb_out ? d_emb_out : w.emb2;
   if (m->n_layers == 1) {
     ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
                               nullptr, k, w.nbr1, w.eid1, nullptr, w.dt1, d_status, s));
+    ORCA_TRY(g_trace.mark(PH_SAMPLE_TOP, s));
     ORCA_TRY(orca_attn_query(&m->attn[0], m->mem.memory, w.nodes1, N, nullptr, w.qt, s));
+    ORCA_TRY(g_trace.mark(PH_QUERY_L2, s));
     ORCA_TRY(orca_attn_gather(w.qt, m->mem.memory, m->edge_table, m->time_w, w.nbr1, w.eid1, w.dt1, k, N,
                               nullptr, w.ctx, w.valid, d_status, s));
+    ORCA_TRY(g_trace.mark(PH_GATHER_L2, s));
     ORCA_TRY(orca_attn_output(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.nodes1, N, nullptr, emb_top,
                               nullptr, nullptr, nullptr, w.hidden, s));
+    ORCA_TRY(g_trace.mark(PH_OUTPUT_L2, s));
   } else {
     // top-level neighbour table, then the uncached out-of-batch neighbours join the row list
     ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
                               nullptr, k, w.nbr2, w.eid2, nullptr, w.dt2, d_status, s));
+    ORCA_TRY(g_trace.mark(PH_SAMPLE_TOP, s));
     ORCA_TRY(orca_find_uncached(w.nbr2, N, k, m->cache_flag, m->n_nodes, w.nodes1, w.ts1, u_cap, w.n1,
                                 w.bitmap, d_status, s));
+    ORCA_TRY(g_trace.mark(PH_UNCACHED, s));
     ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, R1,
                               w.n1, k, w.nbr1, w.eid1, nullptr, w.dt1, d_status, s));
+    ORCA_TRY(g_trace.mark(PH_SAMPLE_L1, s));
     ORCA_TRY(orca_last_occurrence(w.nodes1, R1, w.n1, m->n_nodes, m->last_pos, *m->epoch_base, w.win1,
                                   nullptr, nullptr, s));
     *m->epoch_base += R1;
+    ORCA_TRY(g_trace.mark(PH_LAST_OCC_L1, s));
     // layer 1 over memory rows; its output rows are pushed into the history table
     ORCA_TRY(orca_attn_query(&m->attn[0], m->mem.memory, w.nodes1, R1, w.n1, w.qt, s));
+    ORCA_TRY(g_trace.mark(PH_QUERY_L1, s));
     ORCA_TRY(orca_attn_gather(w.qt, m->mem.memory, m->edge_table, m->time_w, w.nbr1, w.eid1, w.dt1, k, R1,
                               w.n1, w.ctx, w.valid, d_status, s));
+    ORCA_TRY(g_trace.mark(PH_GATHER_L1, s));
     ORCA_TRY(orca_attn_output(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.nodes1, R1, w.n1, w.emb1,
                               m->hist_emb, w.nodes1, w.win1, w.hidden, s));
+    ORCA_TRY(g_trace.mark(PH_OUTPUT_L1, s));
     // cache flags follow the plan of this batch (History.update_flag)
     if (d_plan != nullptr) {
       const bool know_prev = *m->n_prev_plan >= 0;
@@ -175,28 +217,62 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
       ORCA_COUNT_LAUNCH();
       *m->n_prev_plan = -1;
     }
+    ORCA_TRY(g_trace.mark(PH_FLAGS, s));
     // layer 2 over the history rows of the top-level neighbours
     ORCA_TRY(orca_attn_query(&m->attn[1], w.emb1, nullptr, N, nullptr, w.qt, s));
+    ORCA_TRY(g_trace.mark(PH_QUERY_L2, s));
     ORCA_TRY(orca_attn_gather(w.qt, m->hist_emb, m->edge_table, m->time_w, w.nbr2, w.eid2, w.dt2, k, N,
                               nullptr, w.ctx, w.valid, d_status, s));
+    ORCA_TRY(g_trace.mark(PH_GATHER_L2, s));
     ORCA_TRY(orca_attn_output(&m->attn[1], w.ctx, w.valid, w.emb1, nullptr, N, nullptr, emb_top, nullptr,
                               nullptr, nullptr, w.hidden, s));
+    ORCA_TRY(g_trace.mark(PH_OUTPUT_L2, s));
   }
 
   ORCA_TRY(orca_score(&m->score, emb_top, b, d_prob, s));
+  ORCA_TRY(g_trace.mark(PH_SCORE, s));
 
   // raw messages of the batch (last occurrence per node in [src|dst]) and the memory update
   ORCA_TRY(orca_last_occurrence(d_batch_i32, 2 * b, nullptr, m->n_nodes, m->last_pos, *m->epoch_base,
                                 w.is_last2, w.win_pos, w.n_win, s));
   *m->epoch_base += 2 * b;
+  ORCA_TRY(g_trace.mark(PH_LAST_OCC_MSG, s));
   ORCA_TRY(orca_message_store(&m->mem, m->edge_table, m->time_w, d_batch_i32, w.cat_dst, d_batch_ts,
                               d_batch_i32 + 3 * b, b, w.win_pos, 2 * b, w.n_win, w.win_nodes, s));
+  ORCA_TRY(g_trace.mark(PH_MESSAGE, s));
   ORCA_TRY(orca_gru_update(&m->gru, &m->mem, w.win_nodes, 2 * b, w.n_win, 1, w.gru_h, s));
+  ORCA_TRY(g_trace.mark(PH_GRU, s));
 
   publish_counts_kernel<<<1, 1, 0, s>>>(w.n1, w.n_win, d_status);
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   g_last_batch_launches = launch_counter();
+  return ORCA_OK;
+}
+
+int orca_trace(int32_t enable) {
+  g_trace.on = enable != 0;
+  g_trace.used = 0;
+  return ORCA_OK;
+}
+
+int orca_trace_phases(void) { return PH_COUNT; }
+const char *orca_trace_phase_name(int32_t phase) {
+  return (phase >= 0 && phase < PH_COUNT) ? kPhaseNames[phase] : "";
+}
+
+int orca_trace_read(double *h_ms_per_phase) {
+  ORCA_CHECK_ARG(h_ms_per_phase);
+  for (int i = 0; i < PH_COUNT; ++i) h_ms_per_phase[i] = 0.0;
+  for (size_t i = 1; i < g_trace.used; ++i) {
+    const int ph = g_trace.phase_of[i];
+    if (ph < 0) continue;  // first event of a batch
+    ORCA_CUDA(cudaEventSynchronize(g_trace.ev[i]));
+    float ms = 0.f;
+    ORCA_CUDA(cudaEventElapsedTime(&ms, g_trace.ev[i - 1], g_trace.ev[i]));
+    h_ms_per_phase[ph] += ms;
+  }
+  g_trace.used = 0;
   return ORCA_OK;
 }
 

@@ -202,26 +202,34 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
         v[kc] = x;
       }
     };
-    float4 cur[4], nxt[4];
-    fetch(0, cur);
+    // register ring of PREFETCH k-blocks: the loads of block kb + PREFETCH are issued before the
+    // stores of block kb, so a thread keeps 4 * PREFETCH 16-byte loads in flight
+    constexpr int PREFETCH = 4;
+    float4 ring[PREFETCH][4];
+#pragma unroll
+    for (int i = 0; i < PREFETCH; ++i) fetch(i, ring[i]);   // blocks beyond K read zeros
     const uint32_t row_off = (uint32_t)(tid >> 3) * A_SBO + (uint32_t)(tid & 7) * 16u;
-    for (int kb = 0; kb < nkb; ++kb) {
-      const int s = kb % STAGES;
-      if (kb + 1 < nkb) fetch(kb + 1, nxt);
-      mbar_wait(empty(s), ((kb / STAGES) & 1) ^ 1, g.status, 100 + s, alive);
+    for (int kb0 = 0; kb0 < nkb; kb0 += PREFETCH) {
 #pragma unroll
-      for (int kc = 0; kc < 4; ++kc) {
-        const float4 x = cur[kc];
-        const float4 hi = make_float4(tf32_head(x.x), tf32_head(x.y), tf32_head(x.z), tf32_head(x.w));
-        const float4 lo = make_float4(tf32_head(x.x - hi.x), tf32_head(x.y - hi.y), tf32_head(x.z - hi.z),
-                                      tf32_head(x.w - hi.w));
-        st_shared_v4(sm.a_hi(s) + kc * A_LBO + row_off, hi);
-        st_shared_v4(sm.a_lo(s) + kc * A_LBO + row_off, lo);
+      for (int i = 0; i < PREFETCH; ++i) {
+        const int kb = kb0 + i;
+        if (kb < nkb) {
+          const int s = kb % STAGES;
+          mbar_wait(empty(s), ((kb / STAGES) & 1) ^ 1, g.status, 100 + s, alive);
+#pragma unroll
+          for (int kc = 0; kc < 4; ++kc) {
+            const float4 x = ring[i][kc];
+            const float4 hi = make_float4(tf32_head(x.x), tf32_head(x.y), tf32_head(x.z), tf32_head(x.w));
+            const float4 lo = make_float4(tf32_head(x.x - hi.x), tf32_head(x.y - hi.y), tf32_head(x.z - hi.z),
+                                          tf32_head(x.w - hi.w));
+            st_shared_v4(sm.a_hi(s) + kc * A_LBO + row_off, hi);
+            st_shared_v4(sm.a_lo(s) + kc * A_LBO + row_off, lo);
+          }
+          fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async-proxy reads
+          mbar_arrive(full(s));
+          if (kb + PREFETCH < nkb) fetch(kb + PREFETCH, ring[i]);
+        }
       }
-      fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async-proxy reads
-      mbar_arrive(full(s));
-#pragma unroll
-      for (int kc = 0; kc < 4; ++kc) cur[kc] = nxt[kc];
     }
   } else if (warp == 4) {
     // ------------------------------------------------------------------ weight stages
