@@ -459,6 +459,7 @@ int orca_attn_output(const orca_attn_weights_t *w, const float *d_ctx, const uin
   ORCA_CHECK_ARG(d_push_table == nullptr || (d_push_ids && d_push_win));
   if (n_rows_cap == 0) return ORCA_OK;
   if (g_projection_mode == 0) {
+    // (the tensor-core kernel zeroes the whole first source of an invalid row: zero_cols == its width)
     ORCA_CHECK_ARG(w->G_tc && w->W2t_tc && d_scratch_hidden);
     tc::Args a{};
     a.status = g_status_word;

@@ -2,23 +2,36 @@
 //
 //   C[M, n_tiles*176] = A[M, K] . W[K, N]  (+ fused epilogue), fp32 in / fp32 out
 //
-// Precision: one TF32 pass loses 13 mantissa bits of each operand, which costs ~2e-3 on the link
-// scores (the path is specified to 1e-3).  Each operand is therefore split into a TF32 head and a
-// TF32 tail, x = hi + lo, and three MMAs accumulate hi*hi + lo*hi + hi*lo in fp32 in tensor memory,
-// which restores ~2^-21 relative accuracy.  The weight heads/tails are split once on the host; the
-// activation heads/tails are split by the producer warps on their way into shared memory.
+// Precision: a single reduced-precision pass (TF32 or bf16) costs 2e-3 or more on the link scores
+// (the path is specified to 1e-3).  Each fp32 operand is therefore split into a bf16 head and a bf16
+// tail, x ~ hi + lo (16 significant bits), and three MMAs accumulate hi*hi + lo*hi + hi*lo in fp32 in
+// tensor memory; emulating exactly this arithmetic over whole eval runs gives 3e-5 on the scores.
+// The tensor core truncates when it adds into the fp32 accumulator, so the error grows with the
+// number of accumulation steps at full magnitude: the two cross terms (2^-8 smaller) get an
+// accumulator of their own and are added once, in the epilogue.  The weight heads/tails are split
+// once on the host; the activation heads/tails are split by the producer warps on their way into
+// shared memory.
 //
-// Tile: 128 rows x 176 columns per CTA, K consumed 16 floats per stage through a 4-stage ring.
-// Warp roles (192 threads): warps 0-3 gather A rows (one row per thread: table rows picked by an
-// index array, up to two tables concatenated along K), split them and store them in the
-// no-swizzle K-major core-matrix layout the MMA reads; afterwards they are the epilogue warps
-// (warp w owns accumulator lanes 32w..32w+31 = tile rows).  Warp 4 streams the packed weight
-// stage (one 22.5 KB bulk copy per stage).  Warp 5 allocates tensor memory and issues the MMAs
-// (one thread), releasing each stage with tcgen05.commit.
+// Tile: 128 rows x 176 columns per CTA, K consumed 64 elements per stage (4 MMA steps of K = 16,
+// 12 MMAs), two stages.  Every hop over an mbarrier costs ~250-300 cycles and a thread that arrives
+// on one stalls until its outstanding global loads have landed, so stages are large and the A side
+// is produced by two warp groups that alternate stages: while one group waits for its loads, the
+// other converts and the tensor core works on the stage before.
+// Warp roles (320 threads):
+//   warps 0-3, 6-9  producer groups 0 / 1: group g fills stage g for every k-block kb = g (mod 2).
+//              A lane loads 16-byte pieces of the gathered rows (16 lanes cover the 256 contiguous
+//              bytes a row contributes to the stage; table rows picked by an index array, up to two
+//              tables concatenated along K), splits them and stores head and tail in the no-swizzle
+//              K-major core-matrix layout the MMA reads.  Group 0 later runs the epilogue (warp w
+//              owns accumulator lanes 32w..32w+31 = tile rows).
+//   warp 4     streams the packed weight stage (one 44 KB bulk copy per stage).
+//   warp 5     allocates tensor memory and issues the MMAs (one thread), releasing each stage with
+//              tcgen05.commit.
 //
 // Every wait on an mbarrier is bounded; a wait that gives up records ORCA_E_TIMEOUT and the kernel
 // runs to its end (tensor memory is always released).
 #include <algorithm>
+#include <cuda_bf16.h>
 
 #include "common.cuh"
 #include "tc_gemm.cuh"
@@ -46,11 +59,12 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// bounded wait (about a second of SM clocks); returns false and records the failure if the barrier
-// never flipped.  `alive` makes the failure sticky: a thread that gave up once does not wait again,
-// so a broken pipeline drains in about a second instead of one time-out per stage.
+// bounded wait (about a second of SM clocks); records the failure if the barrier never flipped.
+// `alive` makes the failure sticky: a thread that gave up once does not wait again, so a broken
+// pipeline drains in about a second instead of one time-out per stage.
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int32_t *status, int where, bool &alive) {
   if (!alive) return;
+  if (mbar_try(bar, parity)) return;
   const long long t0 = clock64();
   while (!mbar_try(bar, parity)) {
     if (clock64() - t0 > 2000000000ll) {
@@ -81,12 +95,12 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo, uint3
   return d;
 }
 
-// D[tmem] (+)= A[smem] . B[smem]^T, 128 x 176 x 8, TF32 inputs, fp32 accumulate
-__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+// D[tmem] (+)= A[smem] . B[smem]^T, 128 x 176 x 16, bf16 inputs, fp32 accumulate
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                          uint32_t accumulate) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem_d),
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem_d),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
@@ -115,7 +129,19 @@ __device__ __forceinline__ void tmem_ld16_sum(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] += w[i];
 }
 
-__device__ __forceinline__ float tf32_head(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
+// x ~ head + tail, both bf16 (round to nearest even); returns the two pairs packed for an 8-byte store
+__device__ __forceinline__ void split_bf16(const float4 x, uint2 &hi, uint2 &lo) {
+  const __nv_bfloat16 h0 = __float2bfloat16_rn(x.x), h1 = __float2bfloat16_rn(x.y), h2 = __float2bfloat16_rn(x.z),
+                      h3 = __float2bfloat16_rn(x.w);
+  const __nv_bfloat16 l0 = __float2bfloat16_rn(x.x - __bfloat162float(h0)),
+                      l1 = __float2bfloat16_rn(x.y - __bfloat162float(h1)),
+                      l2 = __float2bfloat16_rn(x.z - __bfloat162float(h2)),
+                      l3 = __float2bfloat16_rn(x.w - __bfloat162float(h3));
+  hi.x = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+  hi.y = (uint32_t)__bfloat16_as_ushort(h2) | ((uint32_t)__bfloat16_as_ushort(h3) << 16);
+  lo.x = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
+  lo.y = (uint32_t)__bfloat16_as_ushort(l2) | ((uint32_t)__bfloat16_as_ushort(l3) << 16);
+}
 
 struct Smem {
   uint32_t base;  // shared-window address of the (1024-byte aligned) stage ring
@@ -125,21 +151,16 @@ struct Smem {
   __device__ uint32_t b_lo(int s) const { return base + s * STAGE_BYTES + 2 * A_BYTES + B_BYTES; }
 };
 
-}  // namespace tc
-}  // namespace orca
-
-namespace orca {
-namespace tc {
-
 __device__ __forceinline__ const float *src_row(const RowSrc &s, int m) {
   const int r = s.idx ? s.idx[m] : (s.mod > 0 ? m % s.mod : m) + s.add;
   return s.p + (size_t)r * s.width;
 }
 
-__device__ __forceinline__ void st_shared_v4(uint32_t addr, float4 v) {
-  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
-               : "memory");
+__device__ __forceinline__ void st_shared_v2(uint32_t addr, uint2 v) {
+  asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(v.x), "r"(v.y) : "memory");
 }
+
+__device__ __align__(16) float g_zero16[4] = {0.f, 0.f, 0.f, 0.f};
 
 template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
@@ -162,8 +183,8 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full(s), BM + 1);  // 128 row producers + the weight loader's expect_tx arrival
-      mbar_init(empty(s), 1);      // one tcgen05.commit
+      mbar_init(full(s), 4 + 1);  // one elected lane per producer warp of the group + the weight loader
+      mbar_init(empty(s), 1);     // one tcgen05.commit
     }
     mbar_init(accbar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -173,6 +194,25 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  // per-row source pointers of the tile, resolved once (index arrays, validity)
+  __shared__ const float *s_p0[BM];
+  __shared__ const float *s_p1[BM];
+  if (tid < BM) {
+    const int m = m0 + tid;
+    const float *q0 = g_zero16, *q1 = g_zero16;
+    if (m < M) {
+      q0 = src_row(g.a0, m);
+      if (g.a1.width) q1 = src_row(g.a1, m);
+      // an invalid row reads zeros for its first zero_cols columns: with zero_cols == a0.width (the
+      // only use) that is the whole first source
+      if (g.row_valid != nullptr && g.row_valid[m] == 0 && g.zero_cols > 0) q0 = nullptr;
+    } else {
+      q0 = nullptr;
+      q1 = nullptr;
+    }
+    s_p0[tid] = q0;
+    s_p1[tid] = q1;
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -180,64 +220,51 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   const int nkb = g.n_kblocks;
   bool alive = true;
 
-  if (warp < 4) {
-    // ------------------------------------------------------------------ A producers, one row each
-    const int m = m0 + tid;
-    const bool live = m < M;
-    const bool rv = live && (g.row_valid == nullptr || g.row_valid[m] != 0);
-    const float *p0 = live ? src_row(g.a0, m) : nullptr;
-    const float *p1 = (live && g.a1.width) ? src_row(g.a1, m) : nullptr;
-    auto fetch = [&](int kb, float4(&v)[4]) {
+  if (warp < 4 || warp >= 6) {
+    // ------------------------------------------------------------------ producer groups
+    const int grp = warp >= 6 ? 1 : 0;
+    const int pw = grp ? warp - 6 : warp;  // warp within the group: rows pw*32 .. pw*32+31
+    const int half = lane >> 4;            // which of the two rows of a load instruction
+    const int f = lane & 15;               // 16-byte piece of the row's 256-byte stage segment
+    const uint32_t piece_off = (uint32_t)(f >> 1) * A_LBO + (uint32_t)(f & 1) * 8u;
+    for (int kb = grp; kb < nkb; kb += 2) {
+      const int s = grp;
+      const int col = kb * BK + f * 4;
+      // issue the 16 loads of this lane (rows pw*32 + 2i + half), addresses selected up front so
+      // that nothing consumes a loaded register before all loads are in flight
+      float4 x[16];
 #pragma unroll
-      for (int kc = 0; kc < 4; ++kc) {
-        const int col = kb * BK + kc * 4;
-        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (live && col < g.Kd) {
-          if (col < g.a0.width) {
-            if (rv || col >= g.zero_cols) x = *reinterpret_cast<const float4 *>(p0 + col);
-          } else {
-            x = *reinterpret_cast<const float4 *>(p1 + (col - g.a0.width));
-          }
-        }
-        v[kc] = x;
+      for (int i = 0; i < 16; ++i) {
+        const int r = pw * 32 + 2 * i + half;
+        const float *rowp = nullptr;
+        int c = col;
+        if (col < g.a0.width) rowp = s_p0[r];
+        else if (col < g.Kd) { rowp = s_p1[r]; c = col - g.a0.width; }
+        const float4 *src = rowp ? reinterpret_cast<const float4 *>(rowp + c)
+                                 : reinterpret_cast<const float4 *>(g_zero16);
+        x[i] = *src;
       }
-    };
-    // register ring of PREFETCH k-blocks: the loads of block kb + PREFETCH are issued before the
-    // stores of block kb, so a thread keeps 4 * PREFETCH 16-byte loads in flight
-    constexpr int PREFETCH = 4;
-    float4 ring[PREFETCH][4];
+      mbar_wait(empty(s), ((kb >> 1) & 1) ^ 1, g.status, 100 + s, alive);
 #pragma unroll
-    for (int i = 0; i < PREFETCH; ++i) fetch(i, ring[i]);   // blocks beyond K read zeros
-    const uint32_t row_off = (uint32_t)(tid >> 3) * A_SBO + (uint32_t)(tid & 7) * 16u;
-    for (int kb0 = 0; kb0 < nkb; kb0 += PREFETCH) {
-#pragma unroll
-      for (int i = 0; i < PREFETCH; ++i) {
-        const int kb = kb0 + i;
-        if (kb < nkb) {
-          const int s = kb % STAGES;
-          mbar_wait(empty(s), ((kb / STAGES) & 1) ^ 1, g.status, 100 + s, alive);
-#pragma unroll
-          for (int kc = 0; kc < 4; ++kc) {
-            const float4 x = ring[i][kc];
-            const float4 hi = make_float4(tf32_head(x.x), tf32_head(x.y), tf32_head(x.z), tf32_head(x.w));
-            const float4 lo = make_float4(tf32_head(x.x - hi.x), tf32_head(x.y - hi.y), tf32_head(x.z - hi.z),
-                                          tf32_head(x.w - hi.w));
-            st_shared_v4(sm.a_hi(s) + kc * A_LBO + row_off, hi);
-            st_shared_v4(sm.a_lo(s) + kc * A_LBO + row_off, lo);
-          }
-          fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async-proxy reads
-          mbar_arrive(full(s));
-          if (kb + PREFETCH < nkb) fetch(kb + PREFETCH, ring[i]);
-        }
+      for (int i = 0; i < 16; ++i) {
+        const int r = pw * 32 + 2 * i + half;
+        uint2 hi, lo;
+        split_bf16(x[i], hi, lo);
+        const uint32_t off = piece_off + (uint32_t)(r >> 3) * A_SBO + (uint32_t)(r & 7) * 16u;
+        st_shared_v2(sm.a_hi(s) + off, hi);
+        st_shared_v2(sm.a_lo(s) + off, lo);
       }
+      fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async-proxy reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full(s));
     }
   } else if (warp == 4) {
     // ------------------------------------------------------------------ weight stages
     if (lane == 0) {
       const char *wsrc = reinterpret_cast<const char *>(g.w_packed) + (size_t)nt * nkb * (2 * B_BYTES);
       for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % STAGES;
-        mbar_wait(empty(s), ((kb / STAGES) & 1) ^ 1, g.status, 200 + s, alive);
+        const int s = kb & 1;
+        mbar_wait(empty(s), ((kb >> 1) & 1) ^ 1, g.status, 200 + s, alive);
         mbar_expect_tx(full(s), 2 * B_BYTES);
         bulk_g2s(sm.b_hi(s), wsrc + (size_t)kb * (2 * B_BYTES), 2 * B_BYTES, full(s));
       }
@@ -245,25 +272,23 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   } else {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
-      constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
+      // fp32 accumulate, bf16 x bf16, both K-major, N = 176, M = 128
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                  ((uint32_t)(BM >> 4) << 24);
       for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % STAGES;
-        mbar_wait(full(s), (kb / STAGES) & 1, g.status, 300 + s, alive);
+        const int s = kb & 1;
+        mbar_wait(full(s), (kb >> 1) & 1, g.status, 300 + s, alive);
         tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < BK / 8; ++ks) {
+        for (int ks = 0; ks < BK / 16; ++ks) {
           const uint64_t ah = make_desc(sm.a_hi(s) + ks * 2 * A_LBO, A_LBO, A_SBO);
           const uint64_t al = make_desc(sm.a_lo(s) + ks * 2 * A_LBO, A_LBO, A_SBO);
           const uint64_t bh = make_desc(sm.b_hi(s) + ks * 2 * B_LBO, B_LBO, B_SBO);
           const uint64_t bl = make_desc(sm.b_lo(s) + ks * 2 * B_LBO, B_LBO, B_SBO);
-          // the tensor core truncates when it adds into the fp32 accumulator, so the error grows with
-          // the number of accumulation steps at full magnitude: the two cross terms (2^-11 smaller)
-          // get an accumulator of their own and are added once, in the epilogue
           const uint32_t first = (kb > 0 || ks > 0) ? 1u : 0u;
-          mma_tf32(tmem, ah, bh, idesc, first);
-          mma_tf32(tmem + TMEM_SMALL, al, bh, idesc, first);
-          mma_tf32(tmem + TMEM_SMALL, ah, bl, idesc, 1u);
+          mma_bf16(tmem, ah, bh, idesc, first);
+          mma_bf16(tmem + TMEM_SMALL, al, bh, idesc, first);
+          mma_bf16(tmem + TMEM_SMALL, ah, bl, idesc, 1u);
         }
         mma_commit(empty(s));  // the stage may be refilled once these MMAs have read it
       }

@@ -8,15 +8,16 @@ namespace tc {
 
 constexpr int BM = 128;      // tile rows (accumulator lanes)
 constexpr int BN = 176;      // tile columns (172 padded to a multiple of 16)
-constexpr int BK = 16;       // floats of K per stage = 4 chunks of 16 bytes = 2 MMA steps of K = 8
-constexpr int STAGES = 4;
-constexpr int THREADS = 192;
-constexpr int A_LBO = BM * 16 + 16;   // chunk stride of the A image; +16 keeps the row-per-thread stores conflict free
+constexpr int BK = 64;       // K elements per stage = 8 chunks of 8 bf16 (16 bytes) = 4 MMA steps of K = 16
+constexpr int CHUNKS = BK / 8;
+constexpr int STAGES = 2;    // producer group g (warps 0-3 / 6-9) owns stage g
+constexpr int THREADS = 320;
+constexpr int A_LBO = BM * 16 + 16;   // chunk stride of an A image; +16 keeps the 8-byte stores conflict free
 constexpr int A_SBO = 128;
-constexpr int A_BYTES = (BK / 4) * A_LBO;
+constexpr int A_BYTES = CHUNKS * A_LBO;
 constexpr int B_LBO = BN * 16;
 constexpr int B_SBO = 128;
-constexpr int B_BYTES = (BK / 4) * B_LBO;
+constexpr int B_BYTES = CHUNKS * B_LBO;
 constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;   // A head, A tail, W head, W tail
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int TMEM_COLS = 512;   // main accumulator at column 0, cross-term accumulator at column 256
@@ -38,7 +39,7 @@ struct Args {
   int Kd;                    // a0.width + a1.width
   const uint8_t *row_valid;  // optional: rows with 0 read zeros for the first zero_cols columns
   int zero_cols;
-  const float *w_packed;     // [n_tiles][n_kblocks][head | tail] stage images (weights.pack_tc)
+  const void *w_packed;      // [n_tiles][n_kblocks][head | tail] bf16 stage images (weights.pack_tc)
   int n_kblocks;
   int m_cap;
   const int32_t *d_m;

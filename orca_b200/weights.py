@@ -22,30 +22,37 @@ import numpy as np
 D = 172
 HEADS = 2
 QT_HEAD = 528     # column stride of one head of the projected query (516 used)
-TC_BN, TC_BK = 176, 16
+TC_BN, TC_BK = 176, 64
+
+
+def _bf16_round(x):
+    """float32 -> nearest bfloat16 (ties to even), returned as float32 with the low 16 bits zero."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32).view(np.float32)
 
 
 def pack_tc(W):
     """Packs a row-major [K, N] matrix for the tensor-core kernel (csrc/tc_gemm.cu).
 
-    N is cut into tiles of 176 columns and K into blocks of 16 rows (both zero padded).  One
-    (tile, block) stage image is [head | tail], each [4 chunks][176 columns][4 floats]: element
-    (k, n) of the block sits at chunk k // 4, column n, float k % 4 -- the K-major, no-swizzle
-    core-matrix layout the MMA reads from shared memory -- so that a stage is one contiguous bulk copy.
-    head = the value with the 13 low mantissa bits cleared (exact in TF32), tail = the remainder,
-    cleared the same way."""
+    N is cut into tiles of 176 columns and K into blocks of 64 rows (both zero padded).  One
+    (tile, block) stage image is [head | tail], each [8 chunks][176 columns][8 bf16]: element
+    (k, n) of the block sits at chunk k // 8, column n, position k % 8 -- the K-major, no-swizzle
+    core-matrix layout the MMA reads from shared memory -- so that a stage is one contiguous bulk
+    copy.  head = the value rounded to bf16, tail = the remainder rounded to bf16 (16 significant
+    bits together).  Returned as uint16 [n_tiles, n_kblocks, 2, 8, 176, 8]."""
     W = np.asarray(W, dtype=np.float32)
     K, N = W.shape
     nkb, nt = -(-K // TC_BK), -(-N // TC_BN)
     P = np.zeros((nkb * TC_BK, nt * TC_BN), dtype=np.float32)
     P[:K, :N] = W
-    head = (P.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
-    tail = ((P - head).astype(np.float32).view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+    head = _bf16_round(P)
+    tail = _bf16_round(P - head)
 
-    def image(X):  # [nkb*16, nt*176] -> [nt, nkb, 4, 176, 4]
-        return X.reshape(nkb, 4, 4, nt, TC_BN).transpose(3, 0, 1, 4, 2)
+    def image(X):  # [nkb*64, nt*176] -> [nt, nkb, 8, 176, 8] of bf16 bit patterns
+        bits = (X.view(np.uint32) >> 16).astype(np.uint16)
+        return bits.reshape(nkb, TC_BK // 8, 8, nt, TC_BN).transpose(3, 0, 1, 4, 2)
 
-    return np.ascontiguousarray(np.stack([image(head), image(tail)], axis=2))  # [nt, nkb, 2, 4, 176, 4]
+    return np.ascontiguousarray(np.stack([image(head), image(tail)], axis=2))
 
 
 def _f64(x):

@@ -74,17 +74,17 @@ def test_gru_and_score_layout():
 
 
 def test_tensor_core_weight_packing():
-    """head + tail reproduces the matrix to ~2^-21 and the stage image puts element (k, n) at
-    [tile n // 176][block k // 16][part][chunk (k % 16) // 4][column n % 176][k % 4]."""
+    """head + tail reproduces the matrix to ~2^-16 and the stage image puts element (k, n) at
+    [tile n // 176][block k // 64][part][chunk (k % 64) // 8][column n % 176][k % 8]."""
     rs = np.random.RandomState(0)
     W = rs.randn(1204, 172).astype(np.float32)
     P = weights.pack_tc(W)
-    assert P.shape == (1, 76, 2, 4, 176, 4) and P.dtype == np.float32
-    assert not (P.view(np.uint32) & 0x1FFF).any()                      # both parts are exact TF32 values
-    rec = (P[:, :, 0] + P[:, :, 1]).transpose(1, 2, 4, 0, 3).reshape(76 * 16, 176)   # [k, n]
-    assert np.max(np.abs(rec[:1204, :172] - W) / np.maximum(np.abs(W), 1e-30)) < 2 ** -20
+    assert P.shape == (1, 19, 2, 8, 176, 8) and P.dtype == np.uint16
+    as_f32 = lambda bits: (bits.astype(np.uint32) << 16).view(np.float32)
+    rec = (as_f32(P[:, :, 0]) + as_f32(P[:, :, 1])).transpose(1, 2, 4, 0, 3).reshape(19 * 64, 176)   # [k, n]
+    assert np.max(np.abs(rec[:1204, :172] - W) / np.maximum(np.abs(W), 1e-30)) < 2 ** -15
     assert not rec[1204:].any() and not rec[:, 172:].any()
     k, n = 1000, 37
-    assert P[0, k // 16, 0, (k % 16) // 4, n, k % 4] + P[0, k // 16, 1, (k % 16) // 4, n, k % 4] == rec[k, n]
-    Wq = rs.randn(172, 1056).astype(np.float32)
-    assert weights.pack_tc(Wq).shape == (6, 11, 2, 4, 176, 4)
+    got = as_f32(P[0, k // 64, 0, (k % 64) // 8, n, k % 8]) + as_f32(P[0, k // 64, 1, (k % 64) // 8, n, k % 8])
+    assert got == rec[k, n]
+    assert weights.pack_tc(rs.randn(172, 1056).astype(np.float32)).shape == (6, 3, 2, 8, 176, 8)
