@@ -245,6 +245,16 @@ int orca_gru_update(const orca_gru_weights_t *w, const orca_memory_t *mem, const
                     void *stream);
 int64_t orca_gru_scratch_bytes(int32_t n_cap);
 
+/* The same update for callers that cannot allocate device memory (no counterpart in the reference,
+ * which allocates freely through PyTorch): the scratch is a fixed array inside the library, so the
+ * call takes no scratch pointer and is limited to ORCA_GRU_STATIC_MAX_ROWS listed nodes
+ * (ORCA_E_CAPACITY beyond that).  The first call on each device resolves the array's device address
+ * and should be made outside stream capture.  Calls share the array: do not let two of them overlap
+ * on the GPU. */
+#define ORCA_GRU_STATIC_MAX_ROWS 4096
+int orca_gru_update_static(const orca_gru_weights_t *w, const orca_memory_t *mem, const int32_t *d_nodes,
+                           int32_t n_cap, const int32_t *d_n, int32_t clear_flags, void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * Offline cache planning.  Replaces read_batches + MRD_numba / LRU_numba / TwoQ_numba
  * (utils/cache.py:19-89, 92-166, 338-403, 175-333).  The neighbour tables of ALL batches are

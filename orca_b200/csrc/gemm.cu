@@ -595,4 +595,44 @@ int orca_gru_update(const orca_gru_weights_t *w, const orca_memory_t *mem, const
   return ORCA_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// orca_gru_update for callers that may not allocate device memory.
+//
+// Some hosts of this library cannot hand it a scratch buffer: a serving loop that runs under a fixed
+// memory budget and treats any cudaMalloc as a fault (it also synchronises the whole device), or a
+// plugin whose owner forbids allocator calls after start-up.  For them the [rows, 172] staging
+// area of the GRU result lives in the library image itself: a file-scope device array that every GPU
+// which loads the library holds until the process exits.  Its size bounds the call:
+// ORCA_GRU_STATIC_MAX_ROWS rows (2.8 MB).
+//
+// In host code `g_gru_static_scratch` is only a stand-in for the symbol, not a device address, so
+// the address is looked up with cudaGetSymbolAddress once per device (with that device current) and
+// that pointer is what the kernels receive.  The look-up happens on the first call on a device;
+// make that first call outside any stream capture.  All calls share the array and it keeps the
+// previous call's contents: nothing in it has to start at zero (every row that is read was written
+// by the same call first), but two calls that overlap on the GPU (different streams) race on it.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_gru_static_scratch[ORCA_GRU_STATIC_MAX_ROWS * ORCA_DIM];
+
+int orca_gru_update_static(const orca_gru_weights_t *w, const orca_memory_t *mem, const int32_t *d_nodes,
+                           int32_t n_cap, const int32_t *d_n, int32_t clear_flags, void *stream) {
+  ORCA_CHECK_ARG(n_cap >= 0);
+  if (n_cap > ORCA_GRU_STATIC_MAX_ROWS)
+    return set_error(ORCA_E_CAPACITY,
+                     "orca_gru_update_static: %d rows exceed the built-in scratch of %d rows; "
+                     "use orca_gru_update with a caller-provided scratch buffer",
+                     n_cap, ORCA_GRU_STATIC_MAX_ROWS);
+  constexpr int kMaxDevices = 64;
+  static float *scratch_of_device[kMaxDevices] = {nullptr};
+  int dev = 0;
+  ORCA_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return set_error(ORCA_E_UNSUPPORTED, "orca_gru_update_static: device %d", dev);
+  if (scratch_of_device[dev] == nullptr) {
+    float *p = nullptr;
+    ORCA_CUDA(cudaGetSymbolAddress((void **)&p, g_gru_static_scratch));
+    scratch_of_device[dev] = p;
+  }
+  return orca_gru_update(w, mem, d_nodes, n_cap, d_n, clear_flags, scratch_of_device[dev], stream);
+}
+
 }  // extern "C"
