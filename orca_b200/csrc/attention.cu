@@ -14,7 +14,7 @@ namespace orca {
 
 constexpr int GA_THREADS = 256;
 constexpr int GA_WARPS = GA_THREADS / 32;
-constexpr unsigned GA_SPIN_LIMIT = 1u << 24;
+constexpr unsigned GA_SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -115,21 +115,30 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
     }
     // time encoding of the valid slots while the copies are in flight (cosf with full range
     // reduction: delta * w reaches 1e8)
-    for (int i = tid; i < k * D; i += GA_THREADS) {
-      const int j = i / D, d = i - j * D;
-      if (s_nbr[j] != 0) s_key[j * KEY + 2 * D + d] = cosf(s_dt[j] * __ldg(time_w + d));
-    }
-    // bounded wait for the gathered rows
     {
+      // element i = j * 172 + d walks in steps of 256 = 172 + 84 without a division
+      int j = tid >= D ? 1 : 0, d = tid - j * D;
+      while (j < k) {
+        if (s_nbr[j] != 0) s_key[j * KEY + 2 * D + d] = cos_any(s_dt[j] * __ldg(time_w + d));
+        d += GA_THREADS - D;
+        j += 1;
+        if (d >= D) { d -= D; j += 1; }
+      }
+    }
+    // bounded wait for the gathered rows: one warp polls the mbarrier (with a back-off, so that the
+    // polling does not eat the issue slots of the other resident blocks), the others sleep in the
+    // block barrier
+    if (warp == 0) {
       unsigned spins = 0;
       while (!mbar_try_wait(&bar, parity)) {
+        __nanosleep(64);
         if (++spins > GA_SPIN_LIMIT) {
           report(status, ORCA_E_TIMEOUT, row);
           break;
         }
       }
-      parity ^= 1u;
     }
+    parity ^= 1u;
     __syncthreads();
 
     // logits: one warp per slot, both heads
@@ -166,17 +175,25 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
     __syncthreads();
     // weighted key sum, both heads
     float *out = ctx + (size_t)row * QT;
-    for (int c = tid; c < KEY; c += GA_THREADS) {
-      float a0 = 0.f, a1 = 0.f;
+    {
+      // columns tid and tid + 256 (and tid + 512 for the first four threads) share the weight loads
+      const bool third = tid + 2 * GA_THREADS < KEY;
+      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f, c0 = 0.f, c1 = 0.f;
       for (int j = 0; j < k; ++j) {
-        if (s_nbr[j] != 0) {
-          const float x = s_key[j * KEY + c];
-          a0 += s_w[0][j] * x;
-          a1 += s_w[1][j] * x;
+        if (s_nbr[j] == 0) continue;   // padded slots carry weight zero
+        const float w0 = s_w[0][j], w1 = s_w[1][j];
+        const float *kr = s_key + j * KEY;
+        const float x = kr[tid], y = kr[tid + GA_THREADS];
+        a0 = fmaf(w0, x, a0); a1 = fmaf(w1, x, a1);
+        b0 = fmaf(w0, y, b0); b1 = fmaf(w1, y, b1);
+        if (third) {
+          const float z = kr[tid + 2 * GA_THREADS];
+          c0 = fmaf(w0, z, c0); c1 = fmaf(w1, z, c1);
         }
       }
-      out[c] = a0;
-      out[KEY + c] = a1;
+      out[tid] = a0; out[KEY + tid] = a1;
+      out[tid + GA_THREADS] = b0; out[KEY + tid + GA_THREADS] = b1;
+      if (third) { out[tid + 2 * GA_THREADS] = c0; out[KEY + tid + 2 * GA_THREADS] = c1; }
     }
     if (tid == 0) valid_out[row] = 1;
     __syncthreads();

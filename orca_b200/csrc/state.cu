@@ -63,7 +63,7 @@ message_store_kernel(orca_memory_t mem, const float *__restrict__ edge_table, co
     if (lane < ROW_F4) reinterpret_cast<float4 *>(dst)[lane] = reinterpret_cast<const float4 *>(src)[lane];
   } else {
     const float gap = t - mem.last_update[node];
-    for (int d = lane; d < D; d += 64) dst[d] = cosf(gap * __ldg(time_w + d));
+    for (int d = lane; d < D; d += 64) dst[d] = cos_any(gap * __ldg(time_w + d));
   }
   if (threadIdx.x == 0) {
     mem.msg_ts[node] = t;
