@@ -314,6 +314,12 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
                         void *d_workspace, int64_t workspace_bytes, float *d_prob,
                         float *d_emb_out, int32_t *d_status, void *stream);
 
+/* With overlap on (default) a two-layer batch runs its raw-message / GRU chain on an auxiliary
+ * stream of the library, next to the top attention layer and the scorer; `stream` waits for it
+ * before orca_tgn_eval_batch's work is complete, so callers see one stream-ordered operation.  The
+ * auxiliary stream and two events are created once per device on first use.  Off while tracing. */
+int orca_set_overlap(int32_t enable);
+
 /* Phase tracing of orca_tgn_eval_batch (the reference only has wall-clock deltas around whole
  * epochs, train.py:189-341): while enabled, CUDA events are recorded at the phase boundaries of every
  * batch; orca_trace_read synchronises on them, returns the summed milliseconds per phase

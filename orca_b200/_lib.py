@@ -86,6 +86,7 @@ SYMBOLS = {
     "orca_plan_host": (C.c_int, [_I32, _V, _V, _I64, _I32, _I32, _V, _I64, _I32, C.c_uint32, _V, _I64, _V, _V]),
     "orca_eval_workspace_bytes": (_I64, [_I32, _I32, _I32, _I64]),
     "orca_tgn_eval_batch": (C.c_int, [C.POINTER(TgnT), _V, _V, _I32, _V, _I32, _I32, _V, _I64, _V, _V, _V, _V]),
+    "orca_set_overlap": (C.c_int, [_I32]),
     "orca_trace": (C.c_int, [_I32]),
     "orca_trace_phases": (C.c_int, []),
     "orca_trace_phase_name": (C.c_char_p, [_I32]),

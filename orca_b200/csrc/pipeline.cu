@@ -118,6 +118,27 @@ struct Tracer {
 };
 static Tracer g_trace;
 
+// The raw-message / GRU chain of a batch only needs the memory table to be no longer read by the
+// batch's attention layers, so it runs on a second stream next to the top attention layer and the
+// scorer.  One auxiliary stream and two events per device, created on first use.
+struct Overlap {
+  bool enabled = true;
+  int device = -1;
+  cudaStream_t aux = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  int ensure() {
+    int dev = 0;
+    ORCA_CUDA(cudaGetDevice(&dev));
+    if (dev == device && aux != nullptr) return ORCA_OK;
+    ORCA_CUDA(cudaStreamCreateWithFlags(&aux, cudaStreamNonBlocking));
+    ORCA_CUDA(cudaEventCreateWithFlags(&fork, cudaEventDisableTiming));
+    ORCA_CUDA(cudaEventCreateWithFlags(&join, cudaEventDisableTiming));
+    device = dev;
+    return ORCA_OK;
+  }
+};
+static Overlap g_overlap;
+
 }  // namespace orca
 
 using namespace orca;
@@ -164,6 +185,7 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
   ORCA_TRY(g_trace.mark(PH_PREP, s));
 
   float *emb_top = d_emb_out ? d_emb_out : w.emb2;
+  bool forked = false;
   if (m->n_layers == 1) {
     ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
                               nullptr, k, w.nbr1, w.eid1, nullptr, w.dt1, d_status, s));
@@ -200,6 +222,12 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     ORCA_TRY(orca_attn_output(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.nodes1, R1, w.n1, w.emb1,
                               m->hist_emb, w.nodes1, w.win1, w.hidden, s));
     ORCA_TRY(g_trace.mark(PH_OUTPUT_L1, s));
+    if (g_overlap.enabled && !g_trace.on) {
+      ORCA_TRY(g_overlap.ensure());
+      ORCA_CUDA(cudaEventRecord(g_overlap.fork, s));
+      ORCA_CUDA(cudaStreamWaitEvent(g_overlap.aux, g_overlap.fork, 0));
+      forked = true;
+    }
     // cache flags follow the plan of this batch (History.update_flag)
     if (d_plan != nullptr) {
       const bool know_prev = *m->n_prev_plan >= 0;
@@ -232,21 +260,32 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
   ORCA_TRY(orca_score(&m->score, emb_top, b, d_prob, s));
   ORCA_TRY(g_trace.mark(PH_SCORE, s));
 
-  // raw messages of the batch (last occurrence per node in [src|dst]) and the memory update
+  // raw messages of the batch (last occurrence per node in [src|dst]) and the memory update; on the
+  // auxiliary stream when the fork event was recorded after the last reader of the memory table
+  cudaStream_t ms = forked ? g_overlap.aux : s;
   ORCA_TRY(orca_last_occurrence(d_batch_i32, 2 * b, nullptr, m->n_nodes, m->last_pos, *m->epoch_base,
-                                w.is_last2, w.win_pos, w.n_win, s));
+                                w.is_last2, w.win_pos, w.n_win, ms));
   *m->epoch_base += 2 * b;
   ORCA_TRY(g_trace.mark(PH_LAST_OCC_MSG, s));
   ORCA_TRY(orca_message_store(&m->mem, m->edge_table, m->time_w, d_batch_i32, w.cat_dst, d_batch_ts,
-                              d_batch_i32 + 3 * b, b, w.win_pos, 2 * b, w.n_win, w.win_nodes, s));
+                              d_batch_i32 + 3 * b, b, w.win_pos, 2 * b, w.n_win, w.win_nodes, ms));
   ORCA_TRY(g_trace.mark(PH_MESSAGE, s));
-  ORCA_TRY(orca_gru_update(&m->gru, &m->mem, w.win_nodes, 2 * b, w.n_win, 1, w.gru_h, s));
+  ORCA_TRY(orca_gru_update(&m->gru, &m->mem, w.win_nodes, 2 * b, w.n_win, 1, w.gru_h, ms));
   ORCA_TRY(g_trace.mark(PH_GRU, s));
+  if (forked) {
+    ORCA_CUDA(cudaEventRecord(g_overlap.join, g_overlap.aux));
+    ORCA_CUDA(cudaStreamWaitEvent(s, g_overlap.join, 0));
+  }
 
   publish_counts_kernel<<<1, 1, 0, s>>>(w.n1, w.n_win, d_status);
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   g_last_batch_launches = launch_counter();
+  return ORCA_OK;
+}
+
+int orca_set_overlap(int32_t enable) {
+  g_overlap.enabled = enable != 0;
   return ORCA_OK;
 }
 

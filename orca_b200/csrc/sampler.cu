@@ -135,12 +135,22 @@ find_uncached_kernel(const int32_t *__restrict__ nbr, int n_query, int k, const 
   for (int w = tid; w < n_words; w += FU_THREADS) bm[w] = 0u;
   __syncthreads();
   const int n_slots = n_query * k;
-  for (int i = tid; i < n_slots; i += FU_THREADS) {
-    const int v = nbr[i];
-    if (v >= 0 && v < n_nodes) {
-      if (flag[v] == 0) atomicOr(&bm[v >> 5], 1u << (v & 31));
-    } else {
-      report(status, ORCA_E_BOUNDS, i);
+  // eight ids and then their eight cache flags are loaded before any of them is used, so the
+  // dependent (id -> flag) global loads of a thread overlap instead of queueing behind each other
+  for (int i0 = tid; i0 < n_slots; i0 += 8 * FU_THREADS) {
+    int v[8];
+    uint8_t fl[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * FU_THREADS;
+      v[u] = i < n_slots ? nbr[i] : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) fl[u] = (v[u] >= 0 && v[u] < n_nodes) ? flag[v[u]] : (uint8_t)1;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (fl[u] == 0) atomicOr(&bm[v[u] >> 5], 1u << (v[u] & 31));
+      if (i0 + u * FU_THREADS < n_slots && (v[u] < 0 || v[u] >= n_nodes)) report(status, ORCA_E_BOUNDS, i0);
     }
   }
   // max query time (modules/embedding_module.py:254), fused here: one pass over n_query doubles
