@@ -202,6 +202,8 @@ def run_ours(a):
         dist.init_process_group("nccl", device_id=device)
     L = _lib.lib()
     g, neg, plan, tgn = build_setup(a, device, quiet=rank != 0)
+    if world > 1:
+        tgn.set_distributed(rank, world)
     spec = g.spec
     K, W = a.steps, a.warmup
     nb_avail = len(plan)
@@ -253,7 +255,7 @@ def run_ours(a):
     ms_e2e, _ = timed(lambda i: api_step(first + i), lambda i: api_step(first + W + i, i))
     tgn.check_status()
     edges = sum(len(batch_arrays(g, neg, first + W + i)[0]) for i in range(K))
-    e2e = {"value": edges * world / (ms_e2e / 1e3) if world == 1 else edges / (ms_e2e / 1e3), "unit": "edges/s",
+    e2e = {"value": edges / (ms_e2e / 1e3), "unit": "edges/s",
            "h2d_bytes_per_step": h2d // K, "d2h_bytes_per_step": d2h // K, "ms_per_step": ms_e2e / K}
 
     # ---------------- device-resident inputs: packed batches preloaded, the C ABI called directly
@@ -270,6 +272,22 @@ def run_ours(a):
 
     def abi_step(i):
         ints, ts, n, n_plan = packed[i]
+        if world > 1:
+            # sharded attention layers and scores, NCCL all-gather of the layer-1 rows in between;
+            # the scores stay sharded (every rank keeps those of its edges)
+            from orca_b200 import shard
+            rpr = shard.rows_per_rank(3 * n + u_cap, world)
+            emb1_local = torch.empty(rpr, 172, device=device)
+            _lib.check(L.orca_tgn_eval_batch_sharded(desc, 1, ints.data_ptr(), ts.data_ptr(), n,
+                                                     ints.data_ptr() + 16 * n, n_plan, u_cap, ws.data_ptr(),
+                                                     ws.numel(), emb1_local.data_ptr(), None, None, None,
+                                                     tgn._status.data_ptr(), stream))
+            emb1_all = shard.all_gather_rows(emb1_local)
+            _lib.check(L.orca_tgn_eval_batch_sharded(desc, 2, ints.data_ptr(), ts.data_ptr(), n,
+                                                     ints.data_ptr() + 16 * n, n_plan, u_cap, ws.data_ptr(),
+                                                     ws.numel(), None, emb1_all.data_ptr(), probs[i].data_ptr(),
+                                                     None, tgn._status.data_ptr(), stream))
+            return
         _lib.check(L.orca_tgn_eval_batch(desc, ints.data_ptr(), ts.data_ptr(), n, ints.data_ptr() + 16 * n, n_plan,
                                          u_cap, ws.data_ptr(), ws.numel(), probs[i].data_ptr(), None,
                                          tgn._status.data_ptr(), stream))
@@ -318,8 +336,10 @@ def run_ours(a):
     line = {"metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms_dev / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": workload_config(g, spec, first + W, {"whole_step_hbm_frac": step_frac,
-                                                           "algorithmic_bytes_per_edge": step_bytes / edges}),
+            "config": workload_config(g, spec, first + W, {
+                "whole_step_hbm_frac": step_frac / world, "algorithmic_bytes_per_edge": step_bytes / edges,
+                "sharding": "replicated tables; attention rows and scores split by row/edge % n_gpus; one NCCL "
+                            "all-gather of the layer-1 rows per batch" if world > 1 else "single GPU"}),
             "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches_per_batch * K), "clocks": clocks,
             "phases_us_per_step": phases}
     if rank == 0 and world == 1 and not a.no_cpu_baseline:

@@ -299,6 +299,7 @@ typedef struct {
   int32_t plan_cap;
   int64_t *last_pos;        /* [n_nodes] scratch of orca_last_occurrence              */
   int64_t *epoch_base;      /* host-resident counter owned by the caller              */
+  int32_t rank, world;      /* orca_tgn_eval_batch_sharded only; world <= 1 means one GPU */
 } orca_tgn_t;
 
 /* Workspace sizing: bytes needed for batches of up to b_cap edges with at most u_cap uncached
@@ -313,6 +314,29 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
                         int32_t b, const int32_t *d_plan, int32_t n_plan, int32_t u_cap,
                         void *d_workspace, int64_t workspace_bytes, float *d_prob,
                         float *d_emb_out, int32_t *d_status, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * The same batch with its rows split over `world` GPUs of one node (no counterpart in the reference,
+ * which is single-device).  Every rank holds a full replica of the graph, the tables and the weights
+ * and receives the full batch.  Index work (top-level sampling, uncached set, last occurrences) and the
+ * raw-message / GRU chain are replicated -- they are cheap and keep every replica identical -- while
+ * the two attention layers and the scorer are sharded:
+ *   phase 1: layer-1 row i of [src|dst|neg|U] belongs to rank i % world; a rank computes its rows
+ *            into d_emb1_local [rows_per_rank, 172], rows_per_rank = ceil((3b + u_cap) / world),
+ *            local slot i / world.
+ *   -- the caller all-gathers d_emb1_local into d_emb1_all [world, rows_per_rank, 172] (NCCL) --
+ *   phase 2: every rank pushes ALL layer-1 rows into its history replica, sets the cache flags, then
+ *            computes the top layer and the link scores of its edges (edge e belongs to rank
+ *            e % world, local slot e / world): d_prob_local [2 * b_local] = [pos | neg] and, if
+ *            non-NULL, d_emb2_local [3 * b_local, 172] = [src | dst | neg], b_local = number of local
+ *            edges = (b - rank + world - 1) / world.
+ * Workspace: orca_eval_workspace_bytes (same size as the single-GPU call).
+ */
+int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_t *d_batch_i32,
+                                const double *d_batch_ts, int32_t b, const int32_t *d_plan, int32_t n_plan,
+                                int32_t u_cap, void *d_workspace, int64_t workspace_bytes,
+                                float *d_emb1_local, const float *d_emb1_all, float *d_prob_local,
+                                float *d_emb2_local, int32_t *d_status, void *stream);
 
 /* With overlap on (default) a two-layer batch runs its raw-message / GRU chain on an auxiliary
  * stream of the library, next to the top attention layer and the scorer; `stream` waits for it

@@ -54,6 +54,7 @@ class TgnT(C.Structure):
         ("hist_emb", C.c_void_p), ("cache_flag", C.c_void_p),
         ("prev_plan", C.c_void_p), ("n_prev_plan", C.POINTER(C.c_int32)), ("plan_cap", C.c_int32),
         ("last_pos", C.c_void_p), ("epoch_base", C.POINTER(C.c_int64)),
+        ("rank", C.c_int32), ("world", C.c_int32),
     ]
 
 
@@ -86,6 +87,8 @@ SYMBOLS = {
     "orca_plan_host": (C.c_int, [_I32, _V, _V, _I64, _I32, _I32, _V, _I64, _I32, C.c_uint32, _V, _I64, _V, _V]),
     "orca_eval_workspace_bytes": (_I64, [_I32, _I32, _I32, _I64]),
     "orca_tgn_eval_batch": (C.c_int, [C.POINTER(TgnT), _V, _V, _I32, _V, _I32, _I32, _V, _I64, _V, _V, _V, _V]),
+    "orca_tgn_eval_batch_sharded": (C.c_int, [C.POINTER(TgnT), _I32, _V, _V, _I32, _V, _I32, _I32, _V, _I64, _V, _V,
+                                              _V, _V, _V, _V]),
     "orca_set_overlap": (C.c_int, [_I32]),
     "orca_trace": (C.c_int, [_I32]),
     "orca_trace_phases": (C.c_int, []),

@@ -19,6 +19,8 @@ struct Workspace {
   int32_t *cat_dst; uint8_t *is_last2; int32_t *win_pos; int32_t *n_win; int32_t *win_nodes;
   float *gru_h;
   float *hidden;
+  int32_t *loc_nodes; double *loc_ts; int32_t *n1_loc;      // sharded layer 1
+  int32_t *feat_idx; int32_t *nbr2_loc, *eid2_loc; float *dt2_loc;  // sharded layer 2
   void *bitmap;
   size_t bytes;
 };
@@ -51,6 +53,13 @@ static Workspace carve(void *base, int b_cap, int u_cap, int k, int64_t n_nodes)
   w.win_nodes = (int32_t *)take(2 * (size_t)b_cap * 4);
   w.gru_h = (float *)take(2 * (size_t)b_cap * D * 4);
   w.hidden = (float *)take(R1 * D * 4);
+  w.loc_nodes = (int32_t *)take(R1 * 4);
+  w.loc_ts = (double *)take(R1 * 8);
+  w.n1_loc = (int32_t *)take(4);
+  w.feat_idx = (int32_t *)take(N * 4);
+  w.nbr2_loc = (int32_t *)take(N * k * 4);
+  w.eid2_loc = (int32_t *)take(N * k * 4);
+  w.dt2_loc = (float *)take(N * k * 4);
   w.bitmap = take((size_t)orca_find_uncached_scratch_bytes(n_nodes));
   w.bytes = off;
   return w;
@@ -80,6 +89,52 @@ __global__ void set_flags_counted_kernel(uint8_t *__restrict__ flag, int64_t n_n
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     const int v = ids[i];
     if (v >= 0 && v < n_nodes) flag[v] = 1;
+  }
+}
+
+// ---- row sharding over `world` ranks: layer-1 row i -> rank i % world, slot i / world
+__global__ void shard_l1_kernel(const int32_t *__restrict__ nodes1, const double *__restrict__ ts1,
+                                const int32_t *__restrict__ n1, int rank, int world, int rpr,
+                                int32_t *__restrict__ loc_nodes, double *__restrict__ loc_ts,
+                                int32_t *__restrict__ n1_loc) {
+  const int n = *n1;
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j == 0) *n1_loc = n > rank ? (n - rank + world - 1) / world : 0;
+  if (j >= rpr) return;
+  const int i = rank + j * world;
+  loc_nodes[j] = i < n ? nodes1[i] : 0;
+  loc_ts[j] = i < n ? ts1[i] : 0.0;
+}
+
+// History.push of ALL layer-1 rows from the all-gathered buffer: row i sits at slot
+// (i % world) * rpr + i / world
+__global__ void push_gathered_kernel(float *__restrict__ table, const float *__restrict__ emb_all,
+                                     const int32_t *__restrict__ ids, const uint8_t *__restrict__ win,
+                                     const int32_t *__restrict__ n1, int world, int rpr) {
+  const int n = *n1;
+  const int i = blockIdx.x * 4 + threadIdx.x / 64;
+  const int t = threadIdx.x % 64;
+  if (i >= n || t >= D / 4 || win[i] == 0) return;
+  const size_t slot = (size_t)(i % world) * rpr + i / world;
+  reinterpret_cast<float4 *>(table + (size_t)ids[i] * D)[t] =
+      reinterpret_cast<const float4 *>(emb_all + slot * D)[t];
+}
+
+// top-layer rows of the local edges e = rank + j * world: local row p * b_loc + j <- batch row p * b + e
+__global__ void shard_l2_kernel(const int32_t *__restrict__ nbr2, const int32_t *__restrict__ eid2,
+                                const float *__restrict__ dt2, int b, int k, int rank, int world, int rpr,
+                                int b_loc, int32_t *__restrict__ feat_idx, int32_t *__restrict__ nbr_loc,
+                                int32_t *__restrict__ eid_loc, float *__restrict__ dt_loc) {
+  const int lr = blockIdx.x * blockDim.x / 32 + threadIdx.x / 32;   // one warp per local row
+  const int lane = threadIdx.x % 32;
+  if (lr >= 3 * b_loc) return;
+  const int p = lr / b_loc, j = lr - p * b_loc;
+  const int row = p * b + rank + j * world;
+  if (lane == 0) feat_idx[lr] = (row % world) * rpr + row / world;
+  if (lane < k) {
+    nbr_loc[(size_t)lr * k + lane] = nbr2[(size_t)row * k + lane];
+    eid_loc[(size_t)lr * k + lane] = eid2[(size_t)row * k + lane];
+    dt_loc[(size_t)lr * k + lane] = dt2[(size_t)row * k + lane];
   }
 }
 
@@ -277,6 +332,115 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     ORCA_CUDA(cudaStreamWaitEvent(s, g_overlap.join, 0));
   }
 
+  publish_counts_kernel<<<1, 1, 0, s>>>(w.n1, w.n_win, d_status);
+  ORCA_COUNT_LAUNCH();
+  ORCA_LAUNCH_CHECK();
+  g_last_batch_launches = launch_counter();
+  return ORCA_OK;
+}
+
+int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_t *d_batch_i32,
+                                const double *d_batch_ts, int32_t b, const int32_t *d_plan, int32_t n_plan,
+                                int32_t u_cap, void *d_workspace, int64_t workspace_bytes,
+                                float *d_emb1_local, const float *d_emb1_all, float *d_prob_local,
+                                float *d_emb2_local, int32_t *d_status, void *stream) {
+  ORCA_CHECK_ARG(m && d_batch_i32 && d_batch_ts && d_workspace && d_status);
+  ORCA_CHECK_ARG(phase == 1 || phase == 2);
+  ORCA_CHECK_ARG(b > 0 && u_cap >= 0 && n_plan >= 0 && m->n_layers == 2);
+  ORCA_CHECK_ARG(m->world >= 1 && m->rank >= 0 && m->rank < m->world);
+  ORCA_CHECK_ARG(m->k >= 1 && m->k <= ORCA_MAX_K && m->last_pos && m->epoch_base && *m->epoch_base > 0);
+  ORCA_CHECK_ARG(m->hist_emb && m->cache_flag && m->n_prev_plan && (n_plan == 0 || m->prev_plan) && n_plan <= m->plan_cap);
+  const int k = m->k, world = m->world, rank = m->rank;
+  Workspace w = carve(d_workspace, b, u_cap, k, m->n_nodes);
+  if ((int64_t)w.bytes > workspace_bytes)
+    return set_error(ORCA_E_CAPACITY, "orca_tgn_eval_batch_sharded: workspace of %lld bytes, %lld needed",
+                     (long long)workspace_bytes, (long long)w.bytes);
+  cudaStream_t s = (cudaStream_t)stream;
+  orca_set_status_word(d_status);
+  const int N = 3 * b, R1 = N + u_cap;
+  const int rpr = ceil_div(R1, world);
+  const int b_loc = (b - rank + world - 1) / world;
+
+  if (phase == 1) {
+    ORCA_CHECK_ARG(d_emb1_local != nullptr);
+    launch_counter() = 0;
+    batch_prep_kernel<<<ceil_div(N, 256), 256, 0, s>>>(d_batch_i32, d_batch_ts, b, w.nodes1, w.ts1, w.cat_dst, w.n1);
+    ORCA_COUNT_LAUNCH();
+    // replicated index work: every rank must find the same uncached set and the same winners
+    ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
+                              nullptr, k, w.nbr2, w.eid2, nullptr, w.dt2, d_status, s));
+    ORCA_TRY(orca_find_uncached(w.nbr2, N, k, m->cache_flag, m->n_nodes, w.nodes1, w.ts1, u_cap, w.n1,
+                                w.bitmap, d_status, s));
+    ORCA_TRY(orca_last_occurrence(w.nodes1, R1, w.n1, m->n_nodes, m->last_pos, *m->epoch_base, w.win1,
+                                  nullptr, nullptr, s));
+    *m->epoch_base += R1;
+    // this rank's layer-1 rows
+    shard_l1_kernel<<<ceil_div(rpr, 256), 256, 0, s>>>(w.nodes1, w.ts1, w.n1, rank, world, rpr, w.loc_nodes,
+                                                       w.loc_ts, w.n1_loc);
+    ORCA_COUNT_LAUNCH();
+    ORCA_LAUNCH_CHECK();
+    ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.loc_nodes, w.loc_ts,
+                              rpr, w.n1_loc, k, w.nbr1, w.eid1, nullptr, w.dt1, d_status, s));
+    ORCA_TRY(orca_attn_query(&m->attn[0], m->mem.memory, w.loc_nodes, rpr, w.n1_loc, w.qt, s));
+    ORCA_TRY(orca_attn_gather(w.qt, m->mem.memory, m->edge_table, m->time_w, w.nbr1, w.eid1, w.dt1, k, rpr,
+                              w.n1_loc, w.ctx, w.valid, d_status, s));
+    ORCA_TRY(orca_attn_output(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.loc_nodes, rpr, w.n1_loc,
+                              d_emb1_local, nullptr, nullptr, nullptr, w.hidden, s));
+    return ORCA_OK;
+  }
+
+  ORCA_CHECK_ARG(d_emb1_all != nullptr && d_prob_local != nullptr);
+  // every replica of the history table receives every layer-1 row
+  push_gathered_kernel<<<ceil_div(R1, 4), 256, 0, s>>>(m->hist_emb, d_emb1_all, w.nodes1, w.win1, w.n1, world, rpr);
+  ORCA_COUNT_LAUNCH();
+  if (d_plan != nullptr) {
+    const bool know_prev = *m->n_prev_plan >= 0;
+    ORCA_TRY(orca_history_set_flags(m->cache_flag, m->n_nodes, know_prev ? m->prev_plan : nullptr,
+                                    know_prev ? *m->n_prev_plan : 0, d_plan, n_plan, s));
+    if (n_plan > 0) {
+      copy_i32_kernel<<<ceil_div(n_plan, 256), 256, 0, s>>>(d_plan, m->prev_plan, n_plan);
+      ORCA_COUNT_LAUNCH();
+    }
+    *m->n_prev_plan = n_plan;
+  } else {
+    set_flags_counted_kernel<<<std::min(ceil_div(R1, 256), 1024), 256, 0, s>>>(m->cache_flag, m->n_nodes,
+                                                                               w.nodes1, R1, w.n1);
+    ORCA_COUNT_LAUNCH();
+    *m->n_prev_plan = -1;
+  }
+  // the memory table was last read in phase 1: the replicated raw-message / GRU chain can run aside
+  bool forked = false;
+  if (g_overlap.enabled) {
+    ORCA_TRY(g_overlap.ensure());
+    ORCA_CUDA(cudaEventRecord(g_overlap.fork, s));
+    ORCA_CUDA(cudaStreamWaitEvent(g_overlap.aux, g_overlap.fork, 0));
+    forked = true;
+  }
+  cudaStream_t ms = forked ? g_overlap.aux : s;
+  ORCA_TRY(orca_last_occurrence(d_batch_i32, 2 * b, nullptr, m->n_nodes, m->last_pos, *m->epoch_base,
+                                w.is_last2, w.win_pos, w.n_win, ms));
+  *m->epoch_base += 2 * b;
+  ORCA_TRY(orca_message_store(&m->mem, m->edge_table, m->time_w, d_batch_i32, w.cat_dst, d_batch_ts,
+                              d_batch_i32 + 3 * b, b, w.win_pos, 2 * b, w.n_win, w.win_nodes, ms));
+  ORCA_TRY(orca_gru_update(&m->gru, &m->mem, w.win_nodes, 2 * b, w.n_win, 1, w.gru_h, ms));
+  if (b_loc > 0) {
+    // top layer and scores of this rank's edges
+    shard_l2_kernel<<<ceil_div(3 * b_loc, 8), 256, 0, s>>>(w.nbr2, w.eid2, w.dt2, b, k, rank, world, rpr, b_loc,
+                                                           w.feat_idx, w.nbr2_loc, w.eid2_loc, w.dt2_loc);
+    ORCA_COUNT_LAUNCH();
+    ORCA_LAUNCH_CHECK();
+    float *emb2 = d_emb2_local ? d_emb2_local : w.emb2;
+    ORCA_TRY(orca_attn_query(&m->attn[1], d_emb1_all, w.feat_idx, 3 * b_loc, nullptr, w.qt, s));
+    ORCA_TRY(orca_attn_gather(w.qt, m->hist_emb, m->edge_table, m->time_w, w.nbr2_loc, w.eid2_loc, w.dt2_loc, k,
+                              3 * b_loc, nullptr, w.ctx, w.valid, d_status, s));
+    ORCA_TRY(orca_attn_output(&m->attn[1], w.ctx, w.valid, d_emb1_all, w.feat_idx, 3 * b_loc, nullptr, emb2,
+                              nullptr, nullptr, nullptr, w.hidden, s));
+    ORCA_TRY(orca_score(&m->score, emb2, b_loc, d_prob_local, s));
+  }
+  if (forked) {
+    ORCA_CUDA(cudaEventRecord(g_overlap.join, g_overlap.aux));
+    ORCA_CUDA(cudaStreamWaitEvent(s, g_overlap.join, 0));
+  }
   publish_counts_kernel<<<1, 1, 0, s>>>(w.n1, w.n_win, d_status);
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();

@@ -15,7 +15,7 @@ import numpy as np
 import torch
 from torch import nn
 
-from . import _lib, weights
+from . import _lib, shard, weights
 from .history import History
 from .memory import Memory, get_memory_updater
 
@@ -194,6 +194,14 @@ class TGN(nn.Module):
         self._epoch = np.ones(1, dtype=np.int64)
         self._dummy_prev = np.full(1, -1, dtype=np.int32)
         self.last_counts = None
+        self._rank, self._world, self._group = 0, 1, None
+
+    def set_distributed(self, rank, world, group=None):
+        """Shard every batch's attention rows and link scores over `world` GPUs of one node (one
+        process per GPU, torch.distributed initialised by the caller, NCCL).  Every rank keeps full
+        replicas and must be fed the same batches; results are identical on all ranks."""
+        self._rank, self._world, self._group = int(rank), int(world), group
+        self._ws_key = None
 
     # ---- weights ------------------------------------------------------------------------------
     def load_state_dict(self, state_dict, strict=True, **kw):
@@ -260,10 +268,13 @@ class TGN(nn.Module):
             t.n_prev_plan = self._dummy_prev.ctypes.data_as(C.POINTER(C.c_int32))
         t.last_pos = self._last_pos.data_ptr()
         t.epoch_base = self._epoch.ctypes.data_as(C.POINTER(C.c_int64))
+        t.rank, t.world = self._rank, self._world
         return t
 
     def _workspace(self, b, k):
         u_cap = min(3 * b * k, self.n_nodes) if self.n_layers == 2 else 0
+        if self._world > 1:
+            u_cap = min(u_cap, 3 * b)   # bounds the all-gather; a larger uncached set is reported as an error
         key = (b, u_cap, k)
         if self._ws_key is None or self._ws_key[0] < b or self._ws_key[2] != k:
             nbytes = _lib.lib().orca_eval_workspace_bytes(b, u_cap, k, self.n_nodes)
@@ -307,9 +318,33 @@ class TGN(nn.Module):
         desc = self._descriptor(k)
         base = dev.data_ptr()
         d_plan = base + 16 * b if cache_plan is not None else None
+        if self._world > 1:
+            return self._eval_batch_sharded(desc, base, base + off_ts, b, d_plan, n_plan, u_cap, ws, want_emb)
         _lib.check(L.orca_tgn_eval_batch(desc, base, base + off_ts, b, d_plan, n_plan, u_cap, ws.data_ptr(),
                                          ws.numel(), prob.data_ptr(), _lib.ptr(emb), self._status.data_ptr(),
                                          _lib.stream_ptr(self.device)))
+        return prob, emb
+
+    def _eval_batch_sharded(self, desc, d_i32, d_ts, b, d_plan, n_plan, u_cap, ws, want_emb):
+        if self.n_layers != 2:
+            raise NotImplementedError("the multi-GPU split is built for the two-layer model")
+        L = _lib.lib()
+        world = self._world
+        rpr = shard.rows_per_rank(3 * b + u_cap, world)
+        b_max = shard.rows_per_rank(b, world)
+        s = _lib.stream_ptr(self.device)
+        emb1_local = torch.empty(rpr, _lib.DIM, device=self.device)
+        _lib.check(L.orca_tgn_eval_batch_sharded(desc, 1, d_i32, d_ts, b, d_plan, n_plan, u_cap, ws.data_ptr(),
+                                                 ws.numel(), emb1_local.data_ptr(), None, None, None,
+                                                 self._status.data_ptr(), s))
+        emb1_all = shard.all_gather_rows(emb1_local, self._group)
+        prob_local = torch.zeros(2 * b_max, device=self.device)
+        emb2_local = torch.zeros(3 * b_max, _lib.DIM, device=self.device) if want_emb else None
+        _lib.check(L.orca_tgn_eval_batch_sharded(desc, 2, d_i32, d_ts, b, d_plan, n_plan, u_cap, ws.data_ptr(),
+                                                 ws.numel(), None, emb1_all.data_ptr(), prob_local.data_ptr(),
+                                                 _lib.ptr(emb2_local), self._status.data_ptr(), s))
+        prob = shard.assemble_edges(shard.all_gather_rows(prob_local, self._group), b, 2)
+        emb = shard.assemble_edges(shard.all_gather_rows(emb2_local, self._group), b, 3) if want_emb else None
         return prob, emb
 
     def check_status(self):
