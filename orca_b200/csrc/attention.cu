@@ -1,9 +1,9 @@
-// The fused gather-attention kernel: for one query row, gather the K neighbour rows and K
-// edge-feature rows (688 B each) with bulk asynchronous copies into shared memory, compute the
-// time encoding cos(delta * w) while the copies fly, and run the masked two-head attention over
-// the K staged keys entirely on chip.  No weight matrix is touched: the K and V projections are
-// folded into the query (qt) and into the output GEMM, so this kernel is pure HBM traffic:
-//   in : qt row (4128 B) + up to K * (688 + 688) B of gathered rows + K * 12 B of indices
+// The fused gather-attention kernel: per query row, gather the valid neighbour rows and edge-feature
+// rows (688 B each) with bulk asynchronous copies into shared memory, compute the time encoding
+// cos(delta * w) in registers, and run the masked two-head attention over the slots on chip.  No
+// weight matrix is touched: the K and V projections are folded into the query (qt) and into the
+// output GEMM, so the memory side of this kernel is pure HBM traffic:
+//   in : qt row (2 x 2064 B) + valid slots x (688 + 688) B of gathered rows + K * 12 B of indices
 //   out: ctx row (4128 B) + 1 flag
 #include <algorithm>
 #include <vector>
@@ -14,7 +14,6 @@ namespace orca {
 
 constexpr int GA_THREADS = 256;
 constexpr int GA_WARPS = GA_THREADS / 32;
-constexpr unsigned GA_SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -50,8 +49,30 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
       : "memory");
 }
 
-// Shared memory layout (floats): qt[1032] | keys[K][516] | score[2][32] | weight[2][32]
-__global__ void __launch_bounds__(GA_THREADS)
+// One warp per query row, two passes over its valid neighbour slots:
+//   pass 1  every lane owns a fixed set of key columns -- 16-byte pieces l, l+32, l+64 of the
+//           gathered [neighbour | edge feature] part, loaded straight from the tables into registers
+//           with 128-bit loads (the next slot's pieces are requested before the current slot is
+//           processed), and columns l, l+32, ... of the time-encoding part, which is computed
+//           (cos of delta * w) and parked in shared memory.  The lane's partial dot products with
+//           the two query heads are parked too; no cross-lane work happens inside the slot loop.
+//   softmax the 2 * slots partial-sum rows are reduced by 2 * slots lanes at once, the two heads'
+//           softmax runs across lanes;
+//   pass 2  the gathered pieces are loaded again (they sit in L2 now), the time encodings come back
+//           from shared memory, and the weighted key sum is accumulated in registers.
+// Keeping the reductions and the exponentials out of the slot loops matters: with one row per warp
+// the kernel is bound by the length of each warp's dependent instruction chain, not by bandwidth.
+// (The 688-byte rows are not moved by cp.async.bulk: an SM retires only about one small bulk copy
+// per ~130 cycles, which capped an earlier version at 1.5 TB/s whatever else it did.)
+// No block-level synchronisation; a block is eight independent warps.
+constexpr int GA_MEM_F4 = 2 * D / 4;            // 86 sixteen-byte pieces of [neighbour | edge feature]
+constexpr int GA_ROW_F4 = D / 4;                // 43 pieces per table row
+constexpr int GA_T_ITERS = (D + 31) / 32;       // 6 time columns per lane (the last one partial)
+constexpr int GA_TE_LD = 172;                   // floats per parked time encoding
+constexpr int GA_PART_LD = 33;                  // 32 partial sums + 1 pad (conflict-free column reads)
+__host__ __device__ constexpr int ga_warp_floats(int k) { return k * GA_TE_LD + 2 * k * GA_PART_LD; }
+
+__global__ void __launch_bounds__(GA_THREADS, 2)
 attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_table,
                    const float *__restrict__ edge_table, const float *__restrict__ time_w,
                    const int32_t *__restrict__ nbr, const int32_t *__restrict__ eid,
@@ -59,144 +80,187 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
                    float *__restrict__ ctx, uint8_t *__restrict__ valid_out, int32_t *status,
                    unsigned long long *__restrict__ prof) {
   extern __shared__ __align__(128) float smem[];
-  __shared__ __align__(8) uint64_t bar;
-  __shared__ int s_nbr[ORCA_MAX_K];
-  __shared__ int s_eid[ORCA_MAX_K];
-  __shared__ float s_dt[ORCA_MAX_K];
-  __shared__ float s_logit[H][ORCA_MAX_K];
-  __shared__ float s_w[H][ORCA_MAX_K];
-
   const int n = rows_of(n_cap, d_n);
-  float *s_qt = smem;
-  float *s_key = smem + QT;
-  const int tid = threadIdx.x;
-  const int warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) {
-    mbar_init(&bar, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  uint32_t parity = 0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float *s_te = smem + warp * ga_warp_floats(k);  // [k][176]
+  float *s_part = s_te + k * GA_TE_LD;            // [2k][33]
+  // this lane's time-encoding frequencies
+  float wt[GA_T_ITERS];
+#pragma unroll
+  for (int i = 0; i < GA_T_ITERS; ++i) wt[i] = (lane + 32 * i < D) ? __ldg(time_w + lane + 32 * i) : 0.f;
+  const bool third = lane + 64 < GA_MEM_F4;       // lanes 0..21 own a third 16-byte piece
+  unsigned long long prof_rows = 0, prof_slots = 0;
+  (void)status;
 
-  // persistent over rows: the grid is sized for the machine, not for the row capacity
-  for (int row = blockIdx.x; row < n; row += gridDim.x) {
-    if (tid < k) {
-      const size_t o = (size_t)row * k + tid;
-      s_nbr[tid] = nbr[o];
-      s_eid[tid] = eid[o];
-      s_dt[tid] = delta[o];
+  const int wpb = blockDim.x >> 5;   // 8 warps per block, 4 when k is large (shared memory)
+  const int warps_total = gridDim.x * wpb;
+  for (int row = blockIdx.x * wpb + warp; row < n; row += warps_total) {
+    int my_nbr = 0, my_eid = 0;
+    float my_dt = 0.f;
+    if (lane < k) {
+      const size_t o = (size_t)row * k + lane;
+      my_nbr = nbr[o];
+      my_eid = eid[o];
+      my_dt = delta[o];
     }
-    __syncthreads();
-
-    int n_valid = 0;
-    for (int j = 0; j < k; ++j) n_valid += (s_nbr[j] != 0);
-    if (n_valid == 0) {
+    const unsigned vmask = __ballot_sync(0xffffffffu, my_nbr != 0);
+    if (vmask == 0) {
       // every slot is padding: the layer ignores the attention term for this row
-      if (tid == 0) valid_out[row] = 0;
-      __syncthreads();
+      if (lane == 0) valid_out[row] = 0;
       continue;
     }
-
-    if (tid == 0 && prof != nullptr) {
-      atomicAdd(&prof[0], 1ull);                            // rows that gathered
-      atomicAdd(&prof[1], (unsigned long long)n_valid);     // gathered neighbour slots
-    }
-    if (tid == 0) {
-      // the previous row's reads of the staging area are ordered before these writes
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_expect_tx(&bar, (uint32_t)(QT * 4 + n_valid * 2 * ROW_BYTES));
-      bulk_g2s(s_qt, qt + (size_t)row * QT_LD, KEY * 4, &bar);
-      bulk_g2s(s_qt + KEY, qt + (size_t)row * QT_LD + QT_HEAD, KEY * 4, &bar);
-      for (int j = 0; j < k; ++j) {
-        if (s_nbr[j] != 0) {
-          bulk_g2s(s_key + j * KEY, nbr_table + (size_t)s_nbr[j] * D, ROW_BYTES, &bar);
-          bulk_g2s(s_key + j * KEY + D, edge_table + (size_t)s_eid[j] * D, ROW_BYTES, &bar);
-        }
-      }
-    }
-    // time encoding of the valid slots while the copies are in flight (cosf with full range
-    // reduction: delta * w reaches 1e8)
-    {
-      // element i = j * 172 + d walks in steps of 256 = 172 + 84 without a division
-      int j = tid >= D ? 1 : 0, d = tid - j * D;
-      while (j < k) {
-        if (s_nbr[j] != 0) s_key[j * KEY + 2 * D + d] = cos_any(s_dt[j] * __ldg(time_w + d));
-        d += GA_THREADS - D;
-        j += 1;
-        if (d >= D) { d -= D; j += 1; }
-      }
-    }
-    // bounded wait for the gathered rows: one warp polls the mbarrier (with a back-off, so that the
-    // polling does not eat the issue slots of the other resident blocks), the others sleep in the
-    // block barrier
-    if (warp == 0) {
-      unsigned spins = 0;
-      while (!mbar_try_wait(&bar, parity)) {
-        __nanosleep(64);
-        if (++spins > GA_SPIN_LIMIT) {
-          report(status, ORCA_E_TIMEOUT, row);
-          break;
-        }
-      }
-    }
-    parity ^= 1u;
-    __syncthreads();
-
-    // logits: one warp per slot, both heads
-    for (int j = warp; j < k; j += GA_WARPS) {
-      if (s_nbr[j] == 0) continue;
-      const float4 *kv = reinterpret_cast<const float4 *>(s_key + j * KEY);
-      const float4 *q0 = reinterpret_cast<const float4 *>(s_qt);
-      const float4 *q1 = reinterpret_cast<const float4 *>(s_qt + KEY);
-      float a0 = 0.f, a1 = 0.f;
-      for (int c = lane; c < KEY / 4; c += 32) {
-        const float4 x = kv[c], y0 = q0[c], y1 = q1[c];
-        a0 += x.x * y0.x + x.y * y0.y + x.z * y0.z + x.w * y0.w;
-        a1 += x.x * y1.x + x.y * y1.y + x.z * y1.z + x.w * y1.w;
-      }
-      a0 = warp_sum(a0);
-      a1 = warp_sum(a1);
-      if (lane == 0) {
-        s_logit[0][j] = a0;
-        s_logit[1][j] = a1;
-      }
-    }
-    __syncthreads();
-    // softmax over the valid slots, one warp per head
-    if (warp < H) {
-      const bool on = lane < k && s_nbr[lane] != 0;
-      const float v = on ? s_logit[warp][lane] : -INFINITY;
-      float m = v;
+    const int n_valid = __popc(vmask);
+    // this lane's pieces of a slot: piece l of the neighbour row; piece l+32 of the concatenation
+    // (neighbour row for l < 11, else edge row piece l-11); piece l+64 (edge row piece l+21, l < 22).
+    // Addresses are selected, loads are unconditional (lanes without a third piece re-read piece 0
+    // of the edge row; their third accumulator is never written out).
+    auto load_slot = [&](int j, float4(&x)[3]) {
+      const int nb = __shfl_sync(0xffffffffu, my_nbr, j), ei = __shfl_sync(0xffffffffu, my_eid, j);
+      const float4 *nrow = reinterpret_cast<const float4 *>(nbr_table + (size_t)nb * D);
+      const float4 *erow = reinterpret_cast<const float4 *>(edge_table + (size_t)ei * D);
+      const float4 *p1 = lane < GA_ROW_F4 - 32 ? nrow + lane + 32 : erow + lane - (GA_ROW_F4 - 32);
+      const float4 *p2 = third ? erow + lane + 64 - GA_ROW_F4 : erow;
+      x[0] = __ldg(nrow + lane);
+      x[1] = __ldg(p1);
+      x[2] = __ldg(p2);
+    };
+    float4 x[3], xn[3];
+    unsigned todo = vmask;
+    load_slot(__ffs(todo) - 1, x);
+    // the lane's pieces of the two query heads (head h starts at h * 528 in the projected query)
+    const float *qrow = qt + (size_t)row * QT_LD;
+    float4 qa[3], qb[3];
+    float qta[GA_T_ITERS], qtb[GA_T_ITERS];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-      const float e = on ? expf(v - m) : 0.f;
-      const float sum = warp_sum(e);
-      if (lane < k) s_w[warp][lane] = e / sum;
+    for (int i = 0; i < 3; ++i) {
+      const int f = (i < 2 || third) ? lane + 32 * i : 0;
+      qa[i] = __ldg(reinterpret_cast<const float4 *>(qrow) + f);
+      qb[i] = __ldg(reinterpret_cast<const float4 *>(qrow + QT_HEAD) + f);
     }
-    __syncthreads();
-    // weighted key sum, both heads
-    float *out = ctx + (size_t)row * QT;
-    {
-      // columns tid and tid + 256 (and tid + 512 for the first four threads) share the weight loads
-      const bool third = tid + 2 * GA_THREADS < KEY;
-      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f, c0 = 0.f, c1 = 0.f;
-      for (int j = 0; j < k; ++j) {
-        if (s_nbr[j] == 0) continue;   // padded slots carry weight zero
-        const float w0 = s_w[0][j], w1 = s_w[1][j];
-        const float *kr = s_key + j * KEY;
-        const float x = kr[tid], y = kr[tid + GA_THREADS];
-        a0 = fmaf(w0, x, a0); a1 = fmaf(w1, x, a1);
-        b0 = fmaf(w0, y, b0); b1 = fmaf(w1, y, b1);
-        if (third) {
-          const float z = kr[tid + 2 * GA_THREADS];
-          c0 = fmaf(w0, z, c0); c1 = fmaf(w1, z, c1);
+#pragma unroll
+    for (int i = 0; i < GA_T_ITERS; ++i) {
+      const int c = lane + 32 * i < D ? lane + 32 * i : 0;
+      qta[i] = __ldg(qrow + 2 * D + c);
+      qtb[i] = __ldg(qrow + QT_HEAD + 2 * D + c);
+    }
+
+    // ---- pass 1: time encodings and partial logits, slot by slot
+    for (int it = 0; it < n_valid; ++it) {
+      const int j = __ffs(todo) - 1;
+      todo &= todo - 1;
+      if (todo) load_slot(__ffs(todo) - 1, xn);   // request the next slot before working on this one
+      const float dt = __shfl_sync(0xffffffffu, my_dt, j);
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < GA_T_ITERS; ++i) {
+        if (lane + 32 * i < D) {
+          const float te = cos_any(dt * wt[i]);
+          s_te[it * GA_TE_LD + lane + 32 * i] = te;
+          s0 = fmaf(te, qta[i], s0);
+          s1 = fmaf(te, qtb[i], s1);
         }
       }
-      out[tid] = a0; out[KEY + tid] = a1;
-      out[tid + GA_THREADS] = b0; out[KEY + tid + GA_THREADS] = b1;
-      if (third) { out[tid + 2 * GA_THREADS] = c0; out[KEY + tid + 2 * GA_THREADS] = c1; }
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        if (i < 2 || third) {
+          s0 += x[i].x * qa[i].x + x[i].y * qa[i].y + x[i].z * qa[i].z + x[i].w * qa[i].w;
+          s1 += x[i].x * qb[i].x + x[i].y * qb[i].y + x[i].z * qb[i].z + x[i].w * qb[i].w;
+        }
+      }
+      s_part[(2 * it) * GA_PART_LD + lane] = s0;
+      s_part[(2 * it + 1) * GA_PART_LD + lane] = s1;
+#pragma unroll
+      for (int i = 0; i < 3; ++i) x[i] = xn[i];
     }
-    if (tid == 0) valid_out[row] = 1;
-    __syncthreads();
+    __syncwarp();
+
+    // ---- softmax: lane p reduces partial row p = 2 * slot + head; heads live on even / odd lanes
+    // (k <= 16 keeps all 2k rows on the 32 lanes; for larger k a lane takes rows p and p + 32)
+    float prob_lo = 0.f, prob_hi = 0.f;
+    {
+      float lg_lo = -INFINITY, lg_hi = -INFINITY;
+      if (lane < 2 * n_valid) {
+        float a = 0.f;
+#pragma unroll 8
+        for (int t = 0; t < 32; ++t) a += s_part[lane * GA_PART_LD + t];
+        lg_lo = a;
+      }
+      if (lane + 32 < 2 * n_valid) {
+        float a = 0.f;
+#pragma unroll 8
+        for (int t = 0; t < 32; ++t) a += s_part[(lane + 32) * GA_PART_LD + t];
+        lg_hi = a;
+      }
+      float m = fmaxf(lg_lo, lg_hi);               // lanes of equal parity hold the same head
+#pragma unroll
+      for (int o = 2; o < 32; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      const float e_lo = lane < 2 * n_valid ? expf(lg_lo - m) : 0.f;
+      const float e_hi = lane + 32 < 2 * n_valid ? expf(lg_hi - m) : 0.f;
+      float sum = e_lo + e_hi;
+#pragma unroll
+      for (int o = 2; o < 32; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      const float inv = 1.f / sum;
+      prob_lo = e_lo * inv;
+      prob_hi = e_hi * inv;
+    }
+
+    // ---- pass 2: weighted key sum
+    float4 am0[3], am1[3];                         // gathered part, heads 0 / 1
+    float at0[GA_T_ITERS], at1[GA_T_ITERS];        // time part
+#pragma unroll
+    for (int i = 0; i < 3; ++i) am0[i] = am1[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < GA_T_ITERS; ++i) at0[i] = at1[i] = 0.f;
+    todo = vmask;
+    load_slot(__ffs(todo) - 1, x);
+    for (int it = 0; it < n_valid; ++it) {
+      todo &= todo - 1;
+      if (todo) load_slot(__ffs(todo) - 1, xn);
+      const int p = 2 * it;
+      const float p0 = p < 32 ? __shfl_sync(0xffffffffu, prob_lo, p) : __shfl_sync(0xffffffffu, prob_hi, p - 32);
+      const float p1 = p < 32 ? __shfl_sync(0xffffffffu, prob_lo, p + 1) : __shfl_sync(0xffffffffu, prob_hi, p - 31);
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        am0[i].x = fmaf(p0, x[i].x, am0[i].x); am0[i].y = fmaf(p0, x[i].y, am0[i].y);
+        am0[i].z = fmaf(p0, x[i].z, am0[i].z); am0[i].w = fmaf(p0, x[i].w, am0[i].w);
+        am1[i].x = fmaf(p1, x[i].x, am1[i].x); am1[i].y = fmaf(p1, x[i].y, am1[i].y);
+        am1[i].z = fmaf(p1, x[i].z, am1[i].z); am1[i].w = fmaf(p1, x[i].w, am1[i].w);
+      }
+#pragma unroll
+      for (int i = 0; i < GA_T_ITERS; ++i) {
+        if (lane + 32 * i < D) {
+          const float te = s_te[it * GA_TE_LD + lane + 32 * i];
+          at0[i] = fmaf(p0, te, at0[i]);
+          at1[i] = fmaf(p1, te, at1[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 3; ++i) x[i] = xn[i];
+    }
+    // write the row: [head 0: gathered 344 | time 172][head 1: ...]
+    float *out = ctx + (size_t)row * QT;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      if (i < 2 || third) {
+        reinterpret_cast<float4 *>(out)[lane + 32 * i] = am0[i];
+        reinterpret_cast<float4 *>(out + KEY)[lane + 32 * i] = am1[i];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < GA_T_ITERS; ++i) {
+      if (lane + 32 * i < D) {
+        out[2 * D + lane + 32 * i] = at0[i];
+        out[KEY + 2 * D + lane + 32 * i] = at1[i];
+      }
+    }
+    if (lane == 0) valid_out[row] = 1;
+    prof_rows += 1;
+    prof_slots += (unsigned long long)n_valid;
+    __syncwarp();   // the parked values of this row are dead before the next row overwrites them
+  }
+  if (prof != nullptr && lane == 0 && prof_rows) {
+    atomicAdd(&prof[0], prof_rows);     // rows that gathered
+    atomicAdd(&prof[1], prof_slots);    // gathered neighbour slots
   }
 }
 
@@ -248,13 +312,14 @@ extern "C" int orca_attn_gather(const float *d_qt, const float *d_nbr_table, con
   ORCA_CHECK_ARG(((uintptr_t)d_qt % 16 == 0) && ((uintptr_t)d_nbr_table % 16 == 0) &&
                  ((uintptr_t)d_edge_table % 16 == 0));
   if (n_rows_cap == 0) return ORCA_OK;
-  const size_t smem = (size_t)(QT + k * KEY) * sizeof(float);
+  const int warps = k <= 28 ? GA_WARPS : GA_WARPS / 2;
+  const size_t smem = (size_t)warps * ga_warp_floats(k) * sizeof(float);
   static thread_local int configured_device = -1;
   int dev = 0;
   ORCA_CUDA(cudaGetDevice(&dev));
   if (configured_device != dev) {
     ORCA_CUDA(cudaFuncSetAttribute(attn_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (QT + ORCA_MAX_K * KEY) * (int)sizeof(float)));
+                                   GA_WARPS * ga_warp_floats(28) * (int)sizeof(float)));
     configured_device = dev;
   }
   if (g_prof.on) {
@@ -267,7 +332,7 @@ extern "C" int orca_attn_gather(const float *d_qt, const float *d_nbr_table, con
     }
     ORCA_CUDA(cudaEventRecord(g_prof.ev[g_prof.used], (cudaStream_t)stream));
   }
-  attn_gather_kernel<<<std::min(n_rows_cap, 148 * 8), GA_THREADS, smem, (cudaStream_t)stream>>>(
+  attn_gather_kernel<<<std::min(ceil_div(n_rows_cap, warps), 148 * 2), warps * 32, smem, (cudaStream_t)stream>>>(
       d_qt, d_nbr_table, d_edge_table, d_time_w, d_nbr, d_eid, d_delta, k, n_rows_cap, d_n_rows, d_ctx,
       d_valid, d_status, g_prof.on ? g_prof.d_counters : nullptr);
   if (g_prof.on) {

@@ -63,26 +63,19 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-// cos(x) for an fp32 argument of any magnitude up to 1e9, accurate to about 1e-7 absolute.
+// cos(x) for an fp32 argument of any magnitude up to 1e9, accurate to about 5e-7 absolute.
 // The arguments here are delta * w with delta up to 3e8 seconds and w down from 1, so most of them
-// are far outside the range where cosf() stays on its fast path; its slow path (Payne-Hanek) made
-// this kernel issue-bound.  The reduction is done in double precision instead: k = round(x * 2/pi),
-// r = x - k * pi/2 with pi/2 in two doubles (exact enough for k < 2^31), then degree-8 / degree-9
-// polynomials on |r| <= pi/4 in fp32 and the quadrant fix-up.
+// are far outside the range where cosf() stays on its fast path, and its slow path (Payne-Hanek)
+// costs a hundred instructions.  Here the argument is reduced in double precision --
+// r = x - round(x / 2pi) * 2pi with 2pi in two doubles, exact enough for |x| < 1e9 -- and the
+// hardware cosine approximation is applied to r in [-pi, pi], where its absolute error is 2^-21.
 __device__ __forceinline__ float cos_any(float x) {
   if (!(fabsf(x) < 1.0e9f)) return cosf(x);
   const double xd = (double)x;
-  const int ki = __double2int_rn(xd * 0.63661977236758134308);
-  const double k = (double)ki;
-  double r = fma(-k, 1.57079632679489655800e+00, xd);
-  r = fma(-k, 6.12323399573676603587e-17, r);
-  const float rf = (float)r;
-  const float r2 = rf * rf;
-  const float c = fmaf(r2, fmaf(r2, fmaf(r2, fmaf(r2, 2.4801587e-5f, -1.3888889e-3f), 4.1666668e-2f), -0.5f), 1.0f);
-  const float sn = rf * fmaf(r2, fmaf(r2, fmaf(r2, fmaf(r2, 2.7557319e-6f, -1.9841270e-4f), 8.3333333e-3f),
-                                      -1.6666667e-1f), 1.0f);
-  const float v = (ki & 1) ? sn : c;          // quadrants: cos r, -sin r, -cos r, sin r
-  return (((ki + 1) & 2) != 0) ? -v : v;
+  const double k = rint(xd * 0.15915494309189533577);          // 1 / 2pi
+  double r = fma(-k, 6.28318530717958623200e+00, xd);          // 2pi, high part
+  r = fma(-k, 2.44929359829470641435e-16, r);                  // 2pi, low part
+  return __cosf((float)r);
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

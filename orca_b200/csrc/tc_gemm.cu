@@ -120,13 +120,22 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
-// main accumulator + cross-term accumulator
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
+      "[%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+// main accumulator + cross-term accumulator: both loads in flight, one wait
 __device__ __forceinline__ void tmem_ld16_sum(uint32_t taddr, float (&v)[16]) {
-  float w[16];
-  tmem_ld16(taddr, v);
-  tmem_ld16(taddr + TMEM_SMALL, w);
+  uint32_t a[16], b[16];
+  tmem_ld16_nowait(taddr, a);
+  tmem_ld16_nowait(taddr + TMEM_SMALL, b);
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] += w[i];
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(a[i]) + __uint_as_float(b[i]);
 }
 
 // x ~ head + tail, both bf16 (round to nearest even); returns the two pairs packed for an 8-byte store
@@ -193,6 +202,19 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // epilogue vectors of this column tile, staged once (a global load per accumulator chunk would put
+  // an L2 round trip into every step of the epilogue)
+  __shared__ __align__(16) float s_bias[BN], s_v1[BN], s_v2[BN];
+  if (tid >= 192) {   // warps 6-9
+    const int lim = (EPI == EPI_BIAS || EPI == EPI_GRU) ? BN : D;
+    for (int i = tid - 192; i < BN; i += 128) {
+      const bool in = i < lim;
+      s_bias[i] = in ? g.bias[nt * BN + i] : 0.f;
+      const float *v1 = EPI == EPI_HIDDEN ? g.bias2 : EPI == EPI_LAYERNORM ? g.ln_w : EPI == EPI_SCORE ? g.w2 : nullptr;
+      s_v1[i] = (v1 != nullptr && in) ? v1[i] : 0.f;
+      s_v2[i] = (EPI == EPI_LAYERNORM && in) ? g.ln_b[i] : 0.f;
+    }
   }
   // per-row source pointers of the tile, resolved once (index arrays, validity)
   __shared__ const float *s_p0[BM];
@@ -312,7 +334,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
           float *o = g.out + (size_t)m * g.out_ld + c0 + ch * 16;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const float4 b = __ldg(reinterpret_cast<const float4 *>(g.bias + c0 + ch * 16 + q * 4));
+            const float4 b = *reinterpret_cast<const float4 *>(&s_bias[ch * 16 + q * 4]);
             *reinterpret_cast<float4 *>(o + q * 4) =
                 make_float4(v[q * 4] + b.x, v[q * 4 + 1] + b.y, v[q * 4 + 2] + b.z, v[q * 4 + 3] + b.w);
           }
@@ -327,8 +349,8 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
           for (int q = 0; q < 4; ++q) {
             const int c = ch * 16 + q * 4;
             if (c < D) {
-              const float4 b = __ldg(reinterpret_cast<const float4 *>(g.bias + c));
-              const float4 b2 = __ldg(reinterpret_cast<const float4 *>(g.bias2 + c));
+              const float4 b = *reinterpret_cast<const float4 *>(&s_bias[c]);
+              const float4 b2 = *reinterpret_cast<const float4 *>(&s_v1[c]);
               *reinterpret_cast<float4 *>(g.out + (size_t)m * D + c) =
                   make_float4(fmaxf(v[q * 4] + b.x + rvf * b2.x, 0.f), fmaxf(v[q * 4 + 1] + b.y + rvf * b2.y, 0.f),
                               fmaxf(v[q * 4 + 2] + b.z + rvf * b2.z, 0.f), fmaxf(v[q * 4 + 3] + b.w + rvf * b2.w, 0.f));
@@ -337,24 +359,21 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
         }
       }
     } else if (EPI == EPI_LAYERNORM) {
-      float sum = 0.f;
-      for (int ch = 0; ch < BN / 16; ++ch) {
-        tmem_ld16_sum(trow + ch * 16, v);
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-          if (ch * 16 + i < D) sum += v[i] + __ldg(g.bias + ch * 16 + i);
-      }
-      const float mean = sum * (1.f / D);
-      float sq = 0.f;
+      // one pass over the accumulator for both moments (the row is O(1) after the merger, so
+      // E[y^2] - mean^2 loses nothing that matters at the 1e-5 epsilon)
+      float sum = 0.f, sumsq = 0.f;
       for (int ch = 0; ch < BN / 16; ++ch) {
         tmem_ld16_sum(trow + ch * 16, v);
 #pragma unroll
         for (int i = 0; i < 16; ++i)
           if (ch * 16 + i < D) {
-            const float d = v[i] + __ldg(g.bias + ch * 16 + i) - mean;
-            sq += d * d;
+            const float y = v[i] + s_bias[ch * 16 + i];
+            sum += y;
+            sumsq = fmaf(y, y, sumsq);
           }
       }
+      const float mean = sum * (1.f / D);
+      const float sq = fmaxf(sumsq - sum * mean, 0.f);
       const float inv = 1.f / sqrtf(sq * (1.f / D) + 1e-5f);
       const bool push = live && g.push_table != nullptr && g.push_win[m] != 0;
       float *prow = push ? g.push_table + (size_t)g.push_ids[m] * D : nullptr;
@@ -365,9 +384,9 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
           for (int q = 0; q < 4; ++q) {
             const int c = ch * 16 + q * 4;
             if (c < D) {
-              const float4 b = __ldg(reinterpret_cast<const float4 *>(g.bias + c));
-              const float4 w = __ldg(reinterpret_cast<const float4 *>(g.ln_w + c));
-              const float4 lb = __ldg(reinterpret_cast<const float4 *>(g.ln_b + c));
+              const float4 b = *reinterpret_cast<const float4 *>(&s_bias[c]);
+              const float4 w = *reinterpret_cast<const float4 *>(&s_v1[c]);
+              const float4 lb = *reinterpret_cast<const float4 *>(&s_v2[c]);
               const float4 o = make_float4((v[q * 4] + b.x - mean) * inv * w.x + lb.x,
                                            (v[q * 4 + 1] + b.y - mean) * inv * w.y + lb.y,
                                            (v[q * 4 + 2] + b.z - mean) * inv * w.z + lb.z,
@@ -387,7 +406,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
           for (int q = 0; q < 4; ++q) {
             const int u = nt * (BN / 4) + ch * 4 + q;  // GRU unit of these four gate columns
             if (u < D) {
-              const float4 b = __ldg(reinterpret_cast<const float4 *>(g.bias + c0 + ch * 16 + q * 4));
+              const float4 b = *reinterpret_cast<const float4 *>(&s_bias[ch * 16 + q * 4]);
               const float r = 1.f / (1.f + expf(-(v[q * 4] + b.x)));
               const float z = 1.f / (1.f + expf(-(v[q * 4 + 1] + b.y)));
               const float nn = tanhf((v[q * 4 + 2] + b.z) + r * (v[q * 4 + 3] + b.w));
@@ -403,7 +422,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const int c = ch * 16 + i;
-          if (c < D) part += fmaxf(v[i] + __ldg(g.bias + c), 0.f) * __ldg(g.w2 + c);
+          if (c < D) part += fmaxf(v[i] + s_bias[c], 0.f) * s_v1[c];
         }
       }
       if (live) g.out[m] = 1.f / (1.f + expf(-(part + g.b2)));

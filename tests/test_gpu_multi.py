@@ -42,18 +42,18 @@ def _worker(rank, world, port, case, out_dir):
             n = len(src)
             ng = neg[b * spec.bs: b * spec.bs + n]
             if b == 3:
-                s_e, d_e, n_e = tgn.compute_temporal_embeddings(src, dst, ng, ts, eidx, spec.n_degree, True, False, plan[b])
-                assert s_e.shape == (n, 172) and n_e.shape == (n, 172)
-                continue_scores = False
-            p, q = tgn.compute_edge_probabilities(src, dst, ng, ts, eidx, spec.n_degree, True, False, plan[b]) \
-                if b != 3 else (None, None)
-            tgn.check_status()
-            if p is None:
+                # the embedding API advances the state exactly like the scoring API
+                s_e, d_e, n_e = tgn.compute_temporal_embeddings(src, dst, ng, ts, eidx, spec.n_degree, True, False,
+                                                                plan[b])
+                assert s_e.shape == (n, 172) and d_e.shape == (n, 172) and n_e.shape == (n, 172)
+                got.append(s_e.cpu().numpy().ravel())
+                tgn.check_status()
                 continue
+            p, q = tgn.compute_edge_probabilities(src, dst, ng, ts, eidx, spec.n_degree, True, False, plan[b])
+            tgn.check_status()
             p, q = p.cpu().numpy().ravel(), q.cpu().numpy().ravel()
             got.append(np.r_[p, q])
-            if b < 3:   # after batch 3 the state went through an extra-embedding call on both sides alike
-                worst = max(worst, max_rel(p, scores[b, 0, :n]), max_rel(q, scores[b, 1, :n]))
+            worst = max(worst, max_rel(p, scores[b, 0, :n]), max_rel(q, scores[b, 1, :n]))
         assert worst < 1e-3, worst
         np.save(os.path.join(out_dir, f"scores_{rank}.npy"), np.concatenate(got))
         np.save(os.path.join(out_dir, f"memory_{rank}.npy"), tgn.memory.memory.cpu().numpy())
