@@ -327,7 +327,7 @@ def run_ours(a):
     achieved = gather_bytes / (gms[0] / 1e3) / 1e9 if gms[0] > 0 else 0.0
     roofline = {"bound": "hbm", "kernel": "attn_gather_kernel", "achieved": achieved, "peak": peak,
                 "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind + " copy bandwidth",
-                "traffic": GATHER_TRAFFIC_PER_LAUNCH, "launches": int(gl[0]),
+                "traffic": GATHER_TRAFFIC_RATIO * gather_bytes / max(int(gl[0]), 1), "launches": int(gl[0]),
                 "avg_launch_us": gms[0] * 1e3 / max(int(gl[0]), 1),
                 "algorithmic_bytes_per_launch": gather_bytes / max(int(gl[0]), 1)}
     step_frac = step_bytes / (ms_dev / 1e3) / 1e9 / peak
@@ -350,9 +350,10 @@ def run_ours(a):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one attn_gather_kernel launch from the ncu capture
-# summarised under profiles/ (null until a capture of the current kernel exists)
-GATHER_TRAFFIC_PER_LAUNCH = None
+# DRAM traffic of attn_gather_kernel: dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic
+# bytes of the captured launch (profiles/attn_gather_kernel_c4_ncu.md: 15.23 MB read + 0 written for
+# 30.68 MB algorithmic, workload c4), applied to the algorithmic bytes of this run's launches
+GATHER_TRAFFIC_RATIO = 15.233536 / 30.683416
 
 
 def oracle_sample(g, neg, plan, first, n_batches, sub_bs, threads):
