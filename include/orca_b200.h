@@ -72,6 +72,17 @@ int orca_sample_topk(const int64_t *d_indptr, const int32_t *d_adj_nbr, const in
                      int32_t *d_nbr, int32_t *d_eid, float *d_edge_times, float *d_delta,
                      int32_t *d_status, void *stream);
 
+/* orca_sample_topk that also prepares find_uncached_out_of_batch_neighbors
+ * (modules/embedding_module.py:200-212): every sampled neighbour id (the padding node 0 for an empty
+ * slot) whose cache flag is 0 gets its bit set in d_cand_bitmap ((n_nodes+31)/32 words, all zero on
+ * entry); orca_find_uncached_marked turns the bitmap into the uncached set. */
+int orca_sample_topk_mark(const int64_t *d_indptr, const int32_t *d_adj_nbr, const int32_t *d_adj_eid,
+                          const double *d_adj_ts, int64_t n_nodes, const int32_t *d_nodes,
+                          const double *d_ts, int32_t n_query_cap, const int32_t *d_n_query, int32_t k,
+                          int32_t *d_nbr, int32_t *d_eid, float *d_edge_times, float *d_delta,
+                          int32_t *d_status, const uint8_t *d_cache_flag, uint32_t *d_cand_bitmap,
+                          void *stream);
+
 /* find_before (utils/util.py:129-131) on its own: the number of interactions of d_nodes[i]
  * strictly before d_ts[i]. */
 int orca_find_before(const int64_t *d_indptr, const double *d_adj_ts, int64_t n_nodes,
@@ -91,6 +102,12 @@ int64_t orca_find_uncached_scratch_bytes(int64_t n_nodes);
 int orca_find_uncached(const int32_t *d_nbr, int32_t n_query, int32_t k, const uint8_t *d_cache_flag,
                        int64_t n_nodes, int32_t *d_nodes_io, double *d_ts_io, int32_t u_cap,
                        int32_t *d_n_total, void *d_bitmap, int32_t *d_status, void *stream);
+
+/* orca_find_uncached on a bitmap filled by orca_sample_topk_mark: same outputs; the bitmap is all
+ * zero again when the kernel has run. */
+int orca_find_uncached_marked(uint32_t *d_cand_bitmap, int32_t n_query, int64_t n_nodes, int32_t *d_nodes_io,
+                              double *d_ts_io, int32_t u_cap, int32_t *d_n_total, int32_t *d_status,
+                              void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Last-occurrence selection.  Replaces the np.unique(np.flip(nodes), return_index=True) rule of
@@ -300,6 +317,7 @@ typedef struct {
   int64_t *last_pos;        /* [n_nodes] scratch of orca_last_occurrence              */
   int64_t *epoch_base;      /* host-resident counter owned by the caller              */
   int32_t rank, world;      /* orca_tgn_eval_batch_sharded only; world <= 1 means one GPU */
+  uint32_t *cand_bitmap;    /* (n_nodes+31)/32 words, zero-initialised once by the caller       */
 } orca_tgn_t;
 
 /* Workspace sizing: bytes needed for batches of up to b_cap edges with at most u_cap uncached

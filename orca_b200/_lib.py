@@ -55,6 +55,7 @@ class TgnT(C.Structure):
         ("prev_plan", C.c_void_p), ("n_prev_plan", C.POINTER(C.c_int32)), ("plan_cap", C.c_int32),
         ("last_pos", C.c_void_p), ("epoch_base", C.POINTER(C.c_int64)),
         ("rank", C.c_int32), ("world", C.c_int32),
+        ("cand_bitmap", C.c_void_p),
     ]
 
 
@@ -65,6 +66,8 @@ SYMBOLS = {
     "orca_version": (C.c_int, []),
     "orca_csr_build_host": (C.c_int, [_V, _V, _V, _V, _I64, _I64, _V, _V, _V, _V]),
     "orca_sample_topk": (C.c_int, [_V, _V, _V, _V, _I64, _V, _V, _I32, _V, _I32, _V, _V, _V, _V, _V, _V]),
+    "orca_sample_topk_mark": (C.c_int, [_V, _V, _V, _V, _I64, _V, _V, _I32, _V, _I32, _V, _V, _V, _V, _V, _V, _V, _V]),
+    "orca_find_uncached_marked": (C.c_int, [_V, _I32, _I64, _V, _V, _I32, _V, _V, _V]),
     "orca_find_before": (C.c_int, [_V, _V, _I64, _V, _V, _I32, _V, _V]),
     "orca_find_uncached_scratch_bytes": (_I64, [_I64]),
     "orca_find_uncached": (C.c_int, [_V, _I32, _I32, _V, _I64, _V, _V, _I32, _V, _V, _V, _V]),

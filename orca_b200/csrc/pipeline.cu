@@ -221,7 +221,7 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
   ORCA_CHECK_ARG(m->k >= 1 && m->k <= ORCA_MAX_K);
   ORCA_CHECK_ARG(m->last_pos && m->epoch_base && *m->epoch_base > 0);
   if (m->n_layers == 2) ORCA_CHECK_ARG(m->hist_emb && m->cache_flag && m->n_prev_plan && (n_plan == 0 || m->prev_plan));
-  if (m->n_layers == 2) ORCA_CHECK_ARG(n_plan <= m->plan_cap);
+  if (m->n_layers == 2) ORCA_CHECK_ARG(n_plan <= m->plan_cap && m->cand_bitmap);
   const int k = m->k;
   if (m->n_layers == 1) u_cap = 0;
   Workspace w = carve(d_workspace, b, u_cap, k, m->n_nodes);
@@ -255,11 +255,11 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     ORCA_TRY(g_trace.mark(PH_OUTPUT_L2, s));
   } else {
     // top-level neighbour table, then the uncached out-of-batch neighbours join the row list
-    ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
-                              nullptr, k, w.nbr2, w.eid2, nullptr, w.dt2, d_status, s));
+    ORCA_TRY(orca_sample_topk_mark(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
+                                   nullptr, k, w.nbr2, w.eid2, nullptr, w.dt2, d_status, m->cache_flag,
+                                   m->cand_bitmap, s));
     ORCA_TRY(g_trace.mark(PH_SAMPLE_TOP, s));
-    ORCA_TRY(orca_find_uncached(w.nbr2, N, k, m->cache_flag, m->n_nodes, w.nodes1, w.ts1, u_cap, w.n1,
-                                w.bitmap, d_status, s));
+    ORCA_TRY(orca_find_uncached_marked(m->cand_bitmap, N, m->n_nodes, w.nodes1, w.ts1, u_cap, w.n1, d_status, s));
     ORCA_TRY(g_trace.mark(PH_UNCACHED, s));
     ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, R1,
                               w.n1, k, w.nbr1, w.eid1, nullptr, w.dt1, d_status, s));
@@ -349,7 +349,7 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
   ORCA_CHECK_ARG(b > 0 && u_cap >= 0 && n_plan >= 0 && m->n_layers == 2);
   ORCA_CHECK_ARG(m->world >= 1 && m->rank >= 0 && m->rank < m->world);
   ORCA_CHECK_ARG(m->k >= 1 && m->k <= ORCA_MAX_K && m->last_pos && m->epoch_base && *m->epoch_base > 0);
-  ORCA_CHECK_ARG(m->hist_emb && m->cache_flag && m->n_prev_plan && (n_plan == 0 || m->prev_plan) && n_plan <= m->plan_cap);
+  ORCA_CHECK_ARG(m->hist_emb && m->cache_flag && m->n_prev_plan && (n_plan == 0 || m->prev_plan) && n_plan <= m->plan_cap && m->cand_bitmap);
   const int k = m->k, world = m->world, rank = m->rank;
   Workspace w = carve(d_workspace, b, u_cap, k, m->n_nodes);
   if ((int64_t)w.bytes > workspace_bytes)
@@ -367,10 +367,10 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
     batch_prep_kernel<<<ceil_div(N, 256), 256, 0, s>>>(d_batch_i32, d_batch_ts, b, w.nodes1, w.ts1, w.cat_dst, w.n1);
     ORCA_COUNT_LAUNCH();
     // replicated index work: every rank must find the same uncached set and the same winners
-    ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
-                              nullptr, k, w.nbr2, w.eid2, nullptr, w.dt2, d_status, s));
-    ORCA_TRY(orca_find_uncached(w.nbr2, N, k, m->cache_flag, m->n_nodes, w.nodes1, w.ts1, u_cap, w.n1,
-                                w.bitmap, d_status, s));
+    ORCA_TRY(orca_sample_topk_mark(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
+                                   nullptr, k, w.nbr2, w.eid2, nullptr, w.dt2, d_status, m->cache_flag,
+                                   m->cand_bitmap, s));
+    ORCA_TRY(orca_find_uncached_marked(m->cand_bitmap, N, m->n_nodes, w.nodes1, w.ts1, u_cap, w.n1, d_status, s));
     ORCA_TRY(orca_last_occurrence(w.nodes1, R1, w.n1, m->n_nodes, m->last_pos, *m->epoch_base, w.win1,
                                   nullptr, nullptr, s));
     *m->epoch_base += R1;

@@ -59,7 +59,7 @@ sample_topk_kernel(const int64_t *__restrict__ indptr, const int32_t *__restrict
                    int64_t n_nodes, const int32_t *__restrict__ nodes, const double *__restrict__ qts,
                    int n_cap, const int32_t *__restrict__ d_n, int k, int32_t *__restrict__ o_nbr,
                    int32_t *__restrict__ o_eid, float *__restrict__ o_et, float *__restrict__ o_dt,
-                   int32_t *status) {
+                   int32_t *status, const uint8_t *__restrict__ cache_flag, uint32_t *__restrict__ cand_bitmap) {
   const int n = rows_of(n_cap, d_n);
   const int groups_per_block = blockDim.x / G;
   const int lane = threadIdx.x % G;
@@ -90,6 +90,14 @@ sample_topk_kernel(const int64_t *__restrict__ indptr, const int32_t *__restrict
       o_eid[o] = ei;
       if (o_et) o_et[o] = et;
       if (o_dt) o_dt[o] = (float)(t - (double)et);
+      // optional: mark the neighbour (the padding node 0 for an empty slot) as a candidate of the
+      // uncached set when its cache flag is clear
+      // (hub nodes are sampled thousands of times per batch: the bit is tested first so that only the
+      // first few writers pay for an atomic on the same word)
+      if (cand_bitmap != nullptr && cache_flag[nb] == 0) {
+        const uint32_t bit = 1u << (nb & 31);
+        if ((__ldcg(&cand_bitmap[nb >> 5]) & bit) == 0) atomicOr(&cand_bitmap[nb >> 5], bit);
+      }
     }
   }
 }
@@ -149,7 +157,8 @@ find_uncached_kernel(const int32_t *__restrict__ nbr, int n_query, int k, const 
     for (int u = 0; u < 8; ++u) fl[u] = (v[u] >= 0 && v[u] < n_nodes) ? flag[v[u]] : (uint8_t)1;
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
-      if (fl[u] == 0) atomicOr(&bm[v[u] >> 5], 1u << (v[u] & 31));
+      if (fl[u] == 0 && (((volatile uint32_t *)bm)[v[u] >> 5] & (1u << (v[u] & 31))) == 0)
+        atomicOr(&bm[v[u] >> 5], 1u << (v[u] & 31));
       if (i0 + u * FU_THREADS < n_slots && (v[u] < 0 || v[u] >= n_nodes)) report(status, ORCA_E_BOUNDS, i0);
     }
   }
@@ -162,7 +171,8 @@ find_uncached_kernel(const int32_t *__restrict__ nbr, int n_query, int k, const 
   __syncthreads();
   for (int i = tid; i < n_query; i += FU_THREADS) {
     const int v = nodes_io[i];
-    if (v >= 0 && v < n_nodes) atomicAnd(&bm[v >> 5], ~(1u << (v & 31)));
+    if (v >= 0 && v < n_nodes && (((volatile uint32_t *)bm)[v >> 5] & (1u << (v & 31))) != 0)
+      atomicAnd(&bm[v >> 5], ~(1u << (v & 31)));
   }
   __syncthreads();
   tmax = s_tmax[0];
@@ -209,6 +219,107 @@ find_uncached_kernel(const int32_t *__restrict__ nbr, int n_query, int k, const 
         }
       }
       ++rank;
+    }
+  }
+  if (tid == 0) {
+    int u = s_total > 0 ? s_total - 1 : 0;
+    if (u > u_cap) {
+      report(status, ORCA_E_CAPACITY, u);
+      u = u_cap;
+    }
+    *d_n_total = n_query + u;
+  }
+}
+
+// The same set from a candidate bitmap that the sampling launch already filled
+// (orca_sample_topk_mark): only the cheap part is left for the single block -- clear the bits of the
+// query nodes, count, scan, emit -- and the words are zeroed on the way so that the bitmap is clean
+// for the next batch.
+__global__ void __launch_bounds__(FU_THREADS)
+find_uncached_marked_kernel(uint32_t *__restrict__ gbm, int n_query, int64_t n_nodes,
+                            int32_t *__restrict__ nodes_io, double *__restrict__ ts_io, int u_cap,
+                            int32_t *__restrict__ d_n_total, int32_t *status) {
+  extern __shared__ uint32_t s_bitmap[];
+  __shared__ int s_scan[FU_THREADS / 32];
+  __shared__ double s_tmax[FU_THREADS / 32];
+  __shared__ int s_total;
+  const int n_words = (int)((n_nodes + 31) / 32);
+  const bool staged = n_words <= FU_SMEM_WORDS;
+  uint32_t *bm = staged ? s_bitmap : gbm;
+  const int tid = threadIdx.x;
+  if (staged) {
+    // coalesced, unrolled copy of the bitmap into shared memory; the global words are zeroed on the
+    // way so that the bitmap is clean for the next batch
+    for (int w0 = tid; w0 < n_words; w0 += 8 * FU_THREADS) {
+      uint32_t x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) x[u] = (w0 + u * FU_THREADS < n_words) ? __ldcg(&gbm[w0 + u * FU_THREADS]) : 0u;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int w = w0 + u * FU_THREADS;
+        if (w < n_words) {
+          s_bitmap[w] = x[u];
+          if (x[u]) gbm[w] = 0u;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  double tmax = -1.0e300;
+  for (int i = tid; i < n_query; i += FU_THREADS) {
+    tmax = fmax(tmax, ts_io[i]);
+    const int v = nodes_io[i];
+    if (v >= 0 && v < n_nodes) {
+      const uint32_t bit = 1u << (v & 31);
+      if (((volatile uint32_t *)bm)[v >> 5] & bit) atomicAnd(&bm[v >> 5], ~bit);   // test first: repeated query nodes
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) tmax = fmax(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+  if ((tid & 31) == 0) s_tmax[tid >> 5] = tmax;
+  __threadfence_block();
+  __syncthreads();
+  tmax = s_tmax[0];
+  for (int i = 1; i < FU_THREADS / 32; ++i) tmax = fmax(tmax, s_tmax[i]);
+  // each thread owns a contiguous run of words (ascending order of the output)
+  const int per = (n_words + FU_THREADS - 1) / FU_THREADS;
+  const int w0 = tid * per, w1 = min(n_words, w0 + per);
+  int cnt = 0;
+  for (int w = w0; w < w1; ++w) cnt += __popc(bm[w]);
+  int incl = cnt;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int y = __shfl_up_sync(0xffffffffu, incl, o);
+    if ((tid & 31) >= o) incl += y;
+  }
+  if ((tid & 31) == 31) s_scan[tid >> 5] = incl;
+  __syncthreads();
+  if (tid < 32) {
+    int v = s_scan[tid], inc2 = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int y = __shfl_up_sync(0xffffffffu, inc2, o);
+      if (tid >= o) inc2 += y;
+    }
+    s_scan[tid] = inc2 - v;
+    if (tid == 31) s_total = inc2;
+  }
+  __syncthreads();
+  int rank = s_scan[tid >> 5] + incl - cnt;
+  if (cnt > 0) {
+    for (int w = w0; w < w1; ++w) {
+      uint32_t bits = bm[w];
+      if (bits == 0) continue;
+      if (!staged) bm[w] = 0u;
+      while (bits) {
+        const int bit = __ffs(bits) - 1;
+        bits &= bits - 1;
+        if (rank >= 1 && rank - 1 < u_cap) {   // rank 0 is dropped (modules/embedding_module.py:212)
+          nodes_io[n_query + rank - 1] = w * 32 + bit;
+          ts_io[n_query + rank - 1] = tmax;
+        }
+        ++rank;
+      }
     }
   }
   if (tid == 0) {
@@ -340,11 +451,11 @@ int orca_csr_build_host(const int64_t *h_src, const int64_t *h_dst, const int64_
   return ORCA_OK;
 }
 
-int orca_sample_topk(const int64_t *d_indptr, const int32_t *d_adj_nbr, const int32_t *d_adj_eid,
-                     const double *d_adj_ts, int64_t n_nodes, const int32_t *d_nodes,
-                     const double *d_ts, int32_t n_query_cap, const int32_t *d_n_query, int32_t k,
-                     int32_t *d_nbr, int32_t *d_eid, float *d_edge_times, float *d_delta,
-                     int32_t *d_status, void *stream) {
+static int orca_sample_topk_impl(const int64_t *d_indptr, const int32_t *d_adj_nbr, const int32_t *d_adj_eid,
+                            const double *d_adj_ts, int64_t n_nodes, const int32_t *d_nodes,
+                            const double *d_ts, int32_t n_query_cap, const int32_t *d_n_query, int32_t k,
+                            int32_t *d_nbr, int32_t *d_eid, float *d_edge_times, float *d_delta,
+                            int32_t *d_status, const uint8_t *d_cache_flag, uint32_t *d_cand_bitmap, void *stream) {
   ORCA_CHECK_ARG(d_indptr && d_adj_nbr && d_adj_eid && d_adj_ts && d_nodes && d_ts && d_nbr && d_eid);
   ORCA_CHECK_ARG(n_query_cap >= 0 && n_nodes > 0);
   ORCA_CHECK_ARG(k >= 1 && k <= ORCA_MAX_K);
@@ -356,17 +467,40 @@ int orca_sample_topk(const int64_t *d_indptr, const int32_t *d_adj_nbr, const in
     const int grid = std::min(ceil_div(n_query_cap, per), 148 * 16);
     sample_topk_kernel<16><<<grid, threads, 0, s>>>(d_indptr, d_adj_nbr, d_adj_eid, d_adj_ts, n_nodes,
                                                     d_nodes, d_ts, n_query_cap, d_n_query, k, d_nbr,
-                                                    d_eid, d_edge_times, d_delta, d_status);
+                                                    d_eid, d_edge_times, d_delta, d_status, d_cache_flag,
+                                                    d_cand_bitmap);
   } else {
     const int per = threads / 32;
     const int grid = std::min(ceil_div(n_query_cap, per), 148 * 16);
     sample_topk_kernel<32><<<grid, threads, 0, s>>>(d_indptr, d_adj_nbr, d_adj_eid, d_adj_ts, n_nodes,
                                                     d_nodes, d_ts, n_query_cap, d_n_query, k, d_nbr,
-                                                    d_eid, d_edge_times, d_delta, d_status);
+                                                    d_eid, d_edge_times, d_delta, d_status, d_cache_flag,
+                                                    d_cand_bitmap);
   }
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;
+}
+
+int orca_sample_topk(const int64_t *d_indptr, const int32_t *d_adj_nbr, const int32_t *d_adj_eid,
+                     const double *d_adj_ts, int64_t n_nodes, const int32_t *d_nodes,
+                     const double *d_ts, int32_t n_query_cap, const int32_t *d_n_query, int32_t k,
+                     int32_t *d_nbr, int32_t *d_eid, float *d_edge_times, float *d_delta,
+                     int32_t *d_status, void *stream) {
+  return orca_sample_topk_impl(d_indptr, d_adj_nbr, d_adj_eid, d_adj_ts, n_nodes, d_nodes, d_ts, n_query_cap,
+                          d_n_query, k, d_nbr, d_eid, d_edge_times, d_delta, d_status, nullptr, nullptr, stream);
+}
+
+int orca_sample_topk_mark(const int64_t *d_indptr, const int32_t *d_adj_nbr, const int32_t *d_adj_eid,
+                          const double *d_adj_ts, int64_t n_nodes, const int32_t *d_nodes,
+                          const double *d_ts, int32_t n_query_cap, const int32_t *d_n_query, int32_t k,
+                          int32_t *d_nbr, int32_t *d_eid, float *d_edge_times, float *d_delta,
+                          int32_t *d_status, const uint8_t *d_cache_flag, uint32_t *d_cand_bitmap,
+                          void *stream) {
+  ORCA_CHECK_ARG(d_cache_flag && d_cand_bitmap);
+  return orca_sample_topk_impl(d_indptr, d_adj_nbr, d_adj_eid, d_adj_ts, n_nodes, d_nodes, d_ts, n_query_cap,
+                          d_n_query, k, d_nbr, d_eid, d_edge_times, d_delta, d_status, d_cache_flag,
+                          d_cand_bitmap, stream);
 }
 
 int orca_find_before(const int64_t *d_indptr, const double *d_adj_ts, int64_t n_nodes,
@@ -411,6 +545,32 @@ int orca_find_uncached(const int32_t *d_nbr, int32_t n_query, int32_t k, const u
   find_uncached_kernel<<<1, FU_THREADS, smem, (cudaStream_t)stream>>>(
       d_nbr, n_query, k, d_cache_flag, n_nodes, d_nodes_io, d_ts_io, u_cap, d_n_total,
       (uint32_t *)d_bitmap, d_status);
+  ORCA_COUNT_LAUNCH();
+  ORCA_LAUNCH_CHECK();
+  return ORCA_OK;
+}
+
+int orca_find_uncached_marked(uint32_t *d_cand_bitmap, int32_t n_query, int64_t n_nodes, int32_t *d_nodes_io,
+                              double *d_ts_io, int32_t u_cap, int32_t *d_n_total, int32_t *d_status,
+                              void *stream) {
+  ORCA_CHECK_ARG(d_cand_bitmap && d_nodes_io && d_ts_io && d_n_total);
+  ORCA_CHECK_ARG(n_query >= 0 && u_cap >= 0 && n_nodes > 0 && (n_nodes + 31) / 32 < (1ll << 31));
+  const int64_t words = (n_nodes + 31) / 32;
+  size_t smem = 0;
+  if (words <= FU_SMEM_WORDS) {
+    smem = (size_t)words * 4;
+    static thread_local int configured_device = -1;
+    int dev = 0;
+    ORCA_CUDA(cudaGetDevice(&dev));
+    if (configured_device != dev) {
+      ORCA_CUDA(cudaFuncSetAttribute(find_uncached_marked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     FU_SMEM_WORDS * 4));
+      configured_device = dev;
+    }
+  }
+  find_uncached_marked_kernel<<<1, FU_THREADS, smem, (cudaStream_t)stream>>>(d_cand_bitmap, n_query, n_nodes,
+                                                                         d_nodes_io, d_ts_io, u_cap, d_n_total,
+                                                                         d_status);
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;

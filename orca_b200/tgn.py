@@ -191,6 +191,7 @@ class TGN(nn.Module):
         self._stage_dev = None
         self._status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._last_pos = torch.zeros(self.n_nodes, dtype=torch.int64, device=self.device)
+        self._cand_bitmap = torch.zeros((self.n_nodes + 31) // 32, dtype=torch.int32, device=self.device)
         self._epoch = np.ones(1, dtype=np.int64)
         self._dummy_prev = np.full(1, -1, dtype=np.int32)
         self.last_counts = None
@@ -269,6 +270,7 @@ class TGN(nn.Module):
         t.last_pos = self._last_pos.data_ptr()
         t.epoch_base = self._epoch.ctypes.data_as(C.POINTER(C.c_int64))
         t.rank, t.world = self._rank, self._world
+        t.cand_bitmap = self._cand_bitmap.data_ptr()
         return t
 
     def _workspace(self, b, k):

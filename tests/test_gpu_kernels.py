@@ -374,3 +374,54 @@ def test_message_store_and_gru(dev):
     upd.update_memory_in_test(mem)
     assert max_rel(mem.memory.cpu().numpy(), orc.memory.numpy(), floor=0.05) < TOL_TC
     assert mem.nodes.sum() == 0
+
+
+@pytest.mark.parametrize("n_nodes", [1501, 70000, 1700000])
+def test_find_uncached_marked_by_sampler(dev, n_nodes):
+    """The two-kernel form: the sampling launch marks the candidates, a light single block finishes."""
+    from orca_b200 import _lib
+    from orca_b200.neighbor_finder import get_neighbor_finder
+    L = _lib.lib()
+    rs = np.random.RandomState(n_nodes + 1)
+    E = 20000
+    hi = min(n_nodes, 4000)
+
+    class Data:
+        sources, destinations = rs.randint(1, hi, E).astype(np.int64), rs.randint(1, hi, E).astype(np.int64)
+        timestamps, edge_idxs = np.sort(rs.uniform(0, 1e5, E)), np.arange(1, E + 1)
+
+    nf = get_neighbor_finder(Data, max_node_idx=n_nodes - 1)
+    adj = tgn_oracle.Adjacency(Data.sources, Data.destinations, Data.edge_idxs, Data.timestamps, n_nodes)
+    bitmap = torch.zeros((n_nodes + 31) // 32, dtype=torch.int32, device=dev)
+    for trial in range(3):
+        nq, k = 600, 10
+        src = rs.randint(1, hi, nq).astype(np.int32)
+        ts = rs.uniform(0, 1.2e5, nq) if trial else np.full(nq, 2e5)     # trial 0: no padded slot at all? mostly
+        flag = (rs.rand(n_nodes) < 0.3).astype(np.uint8)
+        flag[0] = 0
+        nbr_want, _, _ = tgn_oracle.sample_neighbors(adj, src, ts, k)
+        want = tgn_oracle.find_uncached(src, nbr_want, flag.astype(np.float64))
+        u_cap = nq * k
+        nodes_io = torch.zeros(nq + u_cap, dtype=torch.int32, device=dev)
+        nodes_io[:nq] = _i32(src, dev)
+        ts_io = torch.zeros(nq + u_cap, dtype=torch.float64, device=dev)
+        ts_io[:nq] = torch.as_tensor(ts).to(dev)
+        nbr = torch.zeros(nq, k, dtype=torch.int32, device=dev)
+        eid = torch.zeros(nq, k, dtype=torch.int32, device=dev)
+        n_total = torch.zeros(1, dtype=torch.int32, device=dev)
+        status = torch.zeros(4, dtype=torch.int32, device=dev)
+        d_flag = torch.as_tensor(flag).to(dev)
+        s = _lib.stream_ptr(dev)
+        _lib.check(L.orca_sample_topk_mark(nf.indptr.data_ptr(), nf.adj_nbr.data_ptr(), nf.adj_eid.data_ptr(),
+                                           nf.adj_ts.data_ptr(), n_nodes, nodes_io.data_ptr(), ts_io.data_ptr(), nq,
+                                           None, k, nbr.data_ptr(), eid.data_ptr(), None, None, status.data_ptr(),
+                                           d_flag.data_ptr(), bitmap.data_ptr(), s))
+        _lib.check(L.orca_find_uncached_marked(bitmap.data_ptr(), nq, n_nodes, nodes_io.data_ptr(), ts_io.data_ptr(),
+                                               u_cap, n_total.data_ptr(), status.data_ptr(), s))
+        _lib.check(L.orca_read_status(status.data_ptr(), None, s))
+        n = int(n_total.item())
+        assert np.array_equal(nbr.cpu().numpy(), nbr_want)
+        assert n == nq + len(want)
+        assert np.array_equal(nodes_io[nq:n].cpu().numpy(), want)
+        assert np.all(ts_io[nq:n].cpu().numpy() == ts.max())
+        assert not bitmap.any()            # clean for the next batch
