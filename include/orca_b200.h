@@ -297,6 +297,21 @@ int orca_plan_host(int32_t strategy, const int64_t *h_src, const int64_t *h_dst,
  * with budget != 0 (model/tgn_model.py:95-157 over modules/embedding_module.py:215-285), enqueued
  * on `stream` without any host synchronisation.
  */
+/* The three recursions TGN.compute_temporal_embeddings chooses between (model/tgn_model.py:114-120),
+ * for the two-layer model; with one layer they coincide.
+ *   ORCA_MODE_BUDGET    reuse=True, budget != 0: compute_embedding_budget_reuse
+ *                       (modules/embedding_module.py:215-285) -- cached rows come from the history table,
+ *                       uncached out-of-batch neighbours join the layer-1 row list.
+ *   ORCA_MODE_REUSE_ALL reuse=True, budget == 0: compute_embedding_reuse
+ *                       (modules/embedding_module.py:154-182) -- layer 1 covers the 3b batch rows only,
+ *                       pushes them, and the top layer reads every neighbour from the history table.
+ *   ORCA_MODE_NO_REUSE  reuse=False: compute_embedding (modules/embedding_module.py:116-147) -- layer 1
+ *                       covers the 3b rows and each of their 3b*k neighbour slots; no table is written.
+ *                       The workspace must be sized with u_cap = 3*b*k. */
+#define ORCA_MODE_BUDGET 0
+#define ORCA_MODE_REUSE_ALL 1
+#define ORCA_MODE_NO_REUSE 2
+
 typedef struct {
   /* graph */
   const int64_t *indptr; const int32_t *adj_nbr; const int32_t *adj_eid; const double *adj_ts;
@@ -318,6 +333,7 @@ typedef struct {
   int64_t *epoch_base;      /* host-resident counter owned by the caller              */
   int32_t rank, world;      /* orca_tgn_eval_batch_sharded only; world <= 1 means one GPU */
   uint32_t *cand_bitmap;    /* (n_nodes+31)/32 words, zero-initialised once by the caller       */
+  int32_t mode;             /* ORCA_MODE_*: which recursion of the embedding module runs        */
 } orca_tgn_t;
 
 /* Workspace sizing: bytes needed for batches of up to b_cap edges with at most u_cap uncached

@@ -56,6 +56,7 @@ class TgnT(C.Structure):
         ("last_pos", C.c_void_p), ("epoch_base", C.POINTER(C.c_int64)),
         ("rank", C.c_int32), ("world", C.c_int32),
         ("cand_bitmap", C.c_void_p),
+        ("mode", C.c_int32),
     ]
 
 

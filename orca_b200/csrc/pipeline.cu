@@ -138,6 +138,19 @@ __global__ void shard_l2_kernel(const int32_t *__restrict__ nbr2, const int32_t 
   }
 }
 
+// recursion without reuse: every top-level neighbour slot becomes a layer-1 row of its own, queried at
+// the time of the row that sampled it; the top layer then gathers those rows by position
+__global__ void expand_rows_kernel(const int32_t *__restrict__ nbr2, int n, int k, int32_t *__restrict__ nodes1,
+                                   double *__restrict__ ts1, int32_t *__restrict__ idx2, int32_t *__restrict__ n1) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i == 0) *n1 = n * (1 + k);
+  if (i >= n * k) return;
+  const int v = nbr2[i];
+  nodes1[n + i] = v;
+  ts1[n + i] = ts1[i / k];
+  idx2[i] = v != 0 ? n + i : 0;
+}
+
 __global__ void publish_counts_kernel(const int32_t *n1, const int32_t *n_win, int32_t *status) {
   status[1] = *n1;
   status[2] = *n_win;
@@ -220,10 +233,16 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
   ORCA_CHECK_ARG(m->n_layers == 1 || m->n_layers == 2);
   ORCA_CHECK_ARG(m->k >= 1 && m->k <= ORCA_MAX_K);
   ORCA_CHECK_ARG(m->last_pos && m->epoch_base && *m->epoch_base > 0);
-  if (m->n_layers == 2) ORCA_CHECK_ARG(m->hist_emb && m->cache_flag && m->n_prev_plan && (n_plan == 0 || m->prev_plan));
-  if (m->n_layers == 2) ORCA_CHECK_ARG(n_plan <= m->plan_cap && m->cand_bitmap);
+  if (m->n_layers == 2 && m->mode == ORCA_MODE_BUDGET) {
+    ORCA_CHECK_ARG(m->hist_emb && m->cache_flag && m->n_prev_plan && (n_plan == 0 || m->prev_plan));
+    ORCA_CHECK_ARG(n_plan <= m->plan_cap && m->cand_bitmap);
+  }
+  if (m->n_layers == 2 && m->mode == ORCA_MODE_REUSE_ALL) ORCA_CHECK_ARG(m->hist_emb != nullptr);
   const int k = m->k;
-  if (m->n_layers == 1) u_cap = 0;
+  const int mode = m->n_layers == 2 ? m->mode : ORCA_MODE_BUDGET;
+  ORCA_CHECK_ARG(mode == ORCA_MODE_BUDGET || mode == ORCA_MODE_REUSE_ALL || mode == ORCA_MODE_NO_REUSE);
+  if (m->n_layers == 1 || mode == ORCA_MODE_REUSE_ALL) u_cap = 0;
+  if (m->n_layers == 2 && mode == ORCA_MODE_NO_REUSE) u_cap = 3 * b * k;
   Workspace w = carve(d_workspace, b, u_cap, k, m->n_nodes);
   if ((int64_t)w.bytes > workspace_bytes)
     return set_error(ORCA_E_CAPACITY, "orca_tgn_eval_batch: workspace of %lld bytes, %lld needed",
@@ -232,6 +251,7 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
   orca_set_status_word(d_status);
   launch_counter() = 0;
   const int N = 3 * b, R1 = N + u_cap;
+  const bool push1 = mode != ORCA_MODE_NO_REUSE;
 
   ORCA_TRY(g_trace.mark(-1, s));
   batch_prep_kernel<<<ceil_div(N, 256), 256, 0, s>>>(d_batch_i32, d_batch_ts, b, w.nodes1, w.ts1, w.cat_dst, w.n1);
@@ -254,28 +274,56 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
                               nullptr, nullptr, nullptr, w.hidden, s));
     ORCA_TRY(g_trace.mark(PH_OUTPUT_L2, s));
   } else {
-    // top-level neighbour table, then the uncached out-of-batch neighbours join the row list
-    ORCA_TRY(orca_sample_topk_mark(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
-                                   nullptr, k, w.nbr2, w.eid2, nullptr, w.dt2, d_status, m->cache_flag,
-                                   m->cand_bitmap, s));
-    ORCA_TRY(g_trace.mark(PH_SAMPLE_TOP, s));
-    ORCA_TRY(orca_find_uncached_marked(m->cand_bitmap, N, m->n_nodes, w.nodes1, w.ts1, u_cap, w.n1, d_status, s));
-    ORCA_TRY(g_trace.mark(PH_UNCACHED, s));
-    ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, R1,
-                              w.n1, k, w.nbr1, w.eid1, nullptr, w.dt1, d_status, s));
+    // top-level neighbour table; then the row list of layer 1 by recursion mode
+    const int32_t *nbr1 = w.nbr1, *eid1 = w.eid1, *gather2 = w.nbr2;
+    const float *dt1 = w.dt1;
+    const float *table2 = m->hist_emb;
+    const int32_t *d_n1 = w.n1;
+    if (mode == ORCA_MODE_BUDGET) {
+      // the uncached out-of-batch neighbours join the row list
+      ORCA_TRY(orca_sample_topk_mark(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
+                                     nullptr, k, w.nbr2, w.eid2, nullptr, w.dt2, d_status, m->cache_flag,
+                                     m->cand_bitmap, s));
+      ORCA_TRY(g_trace.mark(PH_SAMPLE_TOP, s));
+      ORCA_TRY(orca_find_uncached_marked(m->cand_bitmap, N, m->n_nodes, w.nodes1, w.ts1, u_cap, w.n1, d_status, s));
+      ORCA_TRY(g_trace.mark(PH_UNCACHED, s));
+    } else {
+      ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
+                                nullptr, k, w.nbr2, w.eid2, nullptr, w.dt2, d_status, s));
+      ORCA_TRY(g_trace.mark(PH_SAMPLE_TOP, s));
+      if (mode == ORCA_MODE_NO_REUSE) {
+        expand_rows_kernel<<<ceil_div(N * k, 256), 256, 0, s>>>(w.nbr2, N, k, w.nodes1, w.ts1, w.nbr2_loc, w.n1);
+        ORCA_COUNT_LAUNCH();
+        ORCA_LAUNCH_CHECK();
+        gather2 = w.nbr2_loc;
+        table2 = w.emb1;
+      }
+      ORCA_TRY(g_trace.mark(PH_UNCACHED, s));
+    }
+    if (mode == ORCA_MODE_REUSE_ALL) {
+      // layer 1 covers the batch rows only and shares the top-level neighbour table
+      nbr1 = w.nbr2, eid1 = w.eid2, dt1 = w.dt2;
+      d_n1 = nullptr;
+    } else {
+      ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, R1,
+                                w.n1, k, w.nbr1, w.eid1, nullptr, w.dt1, d_status, s));
+    }
     ORCA_TRY(g_trace.mark(PH_SAMPLE_L1, s));
-    ORCA_TRY(orca_last_occurrence(w.nodes1, R1, w.n1, m->n_nodes, m->last_pos, *m->epoch_base, w.win1,
-                                  nullptr, nullptr, s));
-    *m->epoch_base += R1;
+    if (push1) {
+      ORCA_TRY(orca_last_occurrence(w.nodes1, R1, d_n1, m->n_nodes, m->last_pos, *m->epoch_base, w.win1,
+                                    nullptr, nullptr, s));
+      *m->epoch_base += R1;
+    }
     ORCA_TRY(g_trace.mark(PH_LAST_OCC_L1, s));
     // layer 1 over memory rows; its output rows are pushed into the history table
-    ORCA_TRY(orca_attn_query(&m->attn[0], m->mem.memory, w.nodes1, R1, w.n1, w.qt, s));
+    ORCA_TRY(orca_attn_query(&m->attn[0], m->mem.memory, w.nodes1, R1, d_n1, w.qt, s));
     ORCA_TRY(g_trace.mark(PH_QUERY_L1, s));
-    ORCA_TRY(orca_attn_gather(w.qt, m->mem.memory, m->edge_table, m->time_w, w.nbr1, w.eid1, w.dt1, k, R1,
-                              w.n1, w.ctx, w.valid, d_status, s));
+    ORCA_TRY(orca_attn_gather(w.qt, m->mem.memory, m->edge_table, m->time_w, nbr1, eid1, dt1, k, R1,
+                              d_n1, w.ctx, w.valid, d_status, s));
     ORCA_TRY(g_trace.mark(PH_GATHER_L1, s));
-    ORCA_TRY(orca_attn_output(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.nodes1, R1, w.n1, w.emb1,
-                              m->hist_emb, w.nodes1, w.win1, w.hidden, s));
+    ORCA_TRY(orca_attn_output(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.nodes1, R1, d_n1, w.emb1,
+                              push1 ? m->hist_emb : nullptr, push1 ? w.nodes1 : nullptr,
+                              push1 ? w.win1 : nullptr, w.hidden, s));
     ORCA_TRY(g_trace.mark(PH_OUTPUT_L1, s));
     if (g_overlap.enabled && !g_trace.on) {
       ORCA_TRY(g_overlap.ensure());
@@ -284,7 +332,9 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
       forked = true;
     }
     // cache flags follow the plan of this batch (History.update_flag)
-    if (d_plan != nullptr) {
+    if (mode != ORCA_MODE_BUDGET) {
+      // no flags outside the budgeted recursion
+    } else if (d_plan != nullptr) {
       const bool know_prev = *m->n_prev_plan >= 0;
       ORCA_TRY(orca_history_set_flags(m->cache_flag, m->n_nodes, know_prev ? m->prev_plan : nullptr,
                                       know_prev ? *m->n_prev_plan : 0, d_plan, n_plan, s));
@@ -304,7 +354,7 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     // layer 2 over the history rows of the top-level neighbours
     ORCA_TRY(orca_attn_query(&m->attn[1], w.emb1, nullptr, N, nullptr, w.qt, s));
     ORCA_TRY(g_trace.mark(PH_QUERY_L2, s));
-    ORCA_TRY(orca_attn_gather(w.qt, m->hist_emb, m->edge_table, m->time_w, w.nbr2, w.eid2, w.dt2, k, N,
+    ORCA_TRY(orca_attn_gather(w.qt, table2, m->edge_table, m->time_w, gather2, w.eid2, w.dt2, k, N,
                               nullptr, w.ctx, w.valid, d_status, s));
     ORCA_TRY(g_trace.mark(PH_GATHER_L2, s));
     ORCA_TRY(orca_attn_output(&m->attn[1], w.ctx, w.valid, w.emb1, nullptr, N, nullptr, emb_top, nullptr,

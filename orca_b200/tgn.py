@@ -19,6 +19,9 @@ from . import _lib, shard, weights
 from .history import History
 from .memory import Memory, get_memory_updater
 
+# recursion modes of the fused batch entry point (ORCA_MODE_* of the C header)
+MODE_BUDGET, MODE_REUSE_ALL, MODE_NO_REUSE = 0, 1, 2
+
 
 class MergeLayer(nn.Module):
     """utils/util.py:12-24 (parameter container; used as the merger and as the link scorer)."""
@@ -196,6 +199,7 @@ class TGN(nn.Module):
         self._dummy_prev = np.full(1, -1, dtype=np.int32)
         self.last_counts = None
         self._rank, self._world, self._group = 0, 1, None
+        self._mode = MODE_BUDGET
 
     def set_distributed(self, rank, world, group=None):
         """Shard every batch's attention rows and link scores over `world` GPUs of one node (one
@@ -258,7 +262,7 @@ class TGN(nn.Module):
         t.n_layers = self.n_layers
         t.k = k
         t.mem = self.memory.c_struct()
-        if self.n_layers == 2:
+        if self.n_layers == 2 and hasattr(self.embedding_module, "histories"):
             h = self.embedding_module.histories[0]
             t.hist_emb = h.emb.data_ptr()
             t.cache_flag = h.cache_flag_dev.data_ptr()
@@ -271,14 +275,17 @@ class TGN(nn.Module):
         t.epoch_base = self._epoch.ctypes.data_as(C.POINTER(C.c_int64))
         t.rank, t.world = self._rank, self._world
         t.cand_bitmap = self._cand_bitmap.data_ptr()
+        t.mode = self._mode
         return t
 
     def _workspace(self, b, k):
         u_cap = min(3 * b * k, self.n_nodes) if self.n_layers == 2 else 0
+        if self.n_layers == 2 and self._mode == MODE_NO_REUSE:
+            u_cap = 3 * b * k          # one layer-1 row per neighbour slot
         if self._world > 1:
             u_cap = min(u_cap, 3 * b)   # bounds the all-gather; a larger uncached set is reported as an error
         key = (b, u_cap, k)
-        if self._ws_key is None or self._ws_key[0] < b or self._ws_key[2] != k:
+        if self._ws_key is None or self._ws_key[0] < b or self._ws_key[1] < u_cap or self._ws_key[2] != k:
             nbytes = _lib.lib().orca_eval_workspace_bytes(b, u_cap, k, self.n_nodes)
             self._ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
             self._ws_key = key
@@ -290,6 +297,8 @@ class TGN(nn.Module):
         L = _lib.lib()
         b = len(source_nodes)
         k = int(n_neighbors)
+        if self._mode != MODE_BUDGET:
+            cache_plan = None
         if self.n_layers == 2 and cache_plan is not None:
             h = self.embedding_module.histories[0]
             if len(cache_plan) > h.prev_plan.numel():
@@ -360,8 +369,13 @@ class TGN(nn.Module):
     def _enter(self, reuse, train):
         if train:
             raise NotImplementedError("the training path (train=True) is not part of this build")
-        if not reuse or self.args.budget == 0:
-            raise NotImplementedError("only the budgeted-reuse recursion (reuse=True, budget>0) is built")
+        # model/tgn_model.py:114-120: the call's `reuse` and the budget choose the recursion
+        mode = MODE_NO_REUSE if not reuse else (MODE_BUDGET if self.args.budget != 0 else MODE_REUSE_ALL)
+        if mode != MODE_NO_REUSE and self.n_layers == 2 and not hasattr(self.embedding_module, "histories"):
+            raise AttributeError("reuse=True needs a model built with args.reuse (no history tables)")
+        if mode != MODE_BUDGET and self._world > 1:
+            raise NotImplementedError("the multi-GPU split is built for the budgeted recursion only")
+        self._mode = mode
         self.batch_counter += 1
         if self.test_mode is False:
             # model/tgn_model.py:109-111: pending messages are flushed when eval starts

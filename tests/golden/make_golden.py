@@ -59,6 +59,10 @@ CASES = {
     "t_lru": ("t_lru", None),
     "t_2q": ("t_2q", None),
     "c2_prefix": ("c2", 40),
+    # the two other recursions of modules/embedding_module.py: unlimited reuse (budget 0, :154-182)
+    # and no reuse (:116-147); 12 batches each
+    "t_nb2_reuse0": ("t_nb2", 12, "reuse0"),
+    "t_nb2_noreuse": ("t_nb2", 12, "noreuse"),
 }
 
 
@@ -80,14 +84,17 @@ def pack(list_of_arrays, dtype=np.int32):
 
 
 def run_case(case):
-    spec_name, n_run = CASES[case]
+    spec_name, n_run = CASES[case][:2]
+    mode = CASES[case][2] if len(CASES[case]) > 2 else "budget"
     g = synthetic.make_graph(spec_name)
     spec = g.spec
     data = Data(g.sources, g.destinations, g.timestamps, g.edge_idxs, np.zeros(g.n_edges))
     nf = get_neighbor_finder(data)
     args = argparse.Namespace(bs=spec.bs, n_degree=spec.n_degree, budget=spec.budget, reuse=True,
                               gradient=False, n_nodes=g.n_nodes, n_edges=g.n_edges + 1)
-    out = {"graph_sha": g.sha256(), "spec": spec_name}
+    out = {"graph_sha": g.sha256(), "spec": spec_name, "mode": mode}
+    if mode != "budget":
+        return run_other_recursion(case, g, data, nf, args, mode, n_run, out)
 
     # ---- plans for every strategy on the small cases, the spec's own strategy otherwise
     strategies = ["MRD", "LRU", "2Q"] if g.n_edges <= 20000 else [spec.strategy]
@@ -214,6 +221,51 @@ def run_case(case):
     path = os.path.join(HERE, f"{case}.npz")
     np.savez_compressed(path, **out)
     print(case, "->", path, "%.1f KB" % (os.path.getsize(path) / 1024), "AP %.6f" % out["ap"])
+
+
+def run_other_recursion(case, g, data, nf, args, mode, n_run, out):
+    """Scores and state slices of the unlimited-reuse (budget 0) and no-reuse recursions."""
+    spec = g.spec
+    args.budget = 0
+    args.reuse = mode == "reuse0"
+    torch.use_deterministic_algorithms(True)
+    torch.manual_seed(0)
+    tgn = TGN(neighbor_finder=nf, node_features=None, edge_features=g.edge_features,
+              device=torch.device("cpu"), n_layers=spec.n_layers, n_heads=2, dropout=0.1,
+              use_memory=True, node_dimension=172, time_dimension=172, memory_dimension=172,
+              embedding_module_type="graph_attention", message_function="identity",
+              aggregator_type="last", memory_updater_type="gru", n_neighbors=spec.n_degree,
+              args=args)
+    sd = {k: torch.from_numpy(v) for k, v in params.random_state_dict(spec.n_layers, seed=0).items()}
+    sd["embedding_module.time_encoder.w.weight"] = sd["time_encoder.w.weight"]
+    sd["embedding_module.time_encoder.w.bias"] = sd["time_encoder.w.bias"]
+    tgn.load_state_dict(sd, strict=True)
+    tgn.test_mode = False
+    tgn.eval()
+    neg_all = synthetic.negative_destinations(g, seed=0)
+    nb, bs = n_run, spec.bs
+    scores = np.full((nb, 2, bs), np.nan, dtype=np.float32)
+    with torch.no_grad():
+        for b in range(nb):
+            s, e = b * bs, min(g.n_edges, (b + 1) * bs)
+            p, n = tgn.compute_edge_probabilities(g.sources[s:e], g.destinations[s:e], neg_all[s:e],
+                                                  g.timestamps[s:e], g.edge_idxs[s:e], spec.n_degree,
+                                                  mode == "reuse0", False, None)
+            scores[b, 0, :e - s] = p.numpy().ravel()
+            scores[b, 1, :e - s] = n.numpy().ravel()
+    out["scores"] = scores
+    out["neg"] = neg_all[: nb * bs].astype(np.int32)
+    touched = np.unique(np.concatenate([g.sources[: nb * bs], g.destinations[: nb * bs]]))
+    pick = np.sort(np.random.RandomState(1).choice(touched, size=min(128, len(touched)), replace=False))
+    out["state_nodes"] = pick.astype(np.int32)
+    out["state_memory"] = tgn.memory.memory[pick].numpy()
+    if mode == "reuse0":
+        out["state_history"] = tgn.embedding_module.histories[0].emb[pick].numpy()
+    out["versions"] = np.array([f"numba {numba.__version__}", f"torch {torch.__version__}",
+                                f"numpy {np.__version__}"])
+    path = os.path.join(HERE, f"{case}.npz")
+    np.savez_compressed(path, **out)
+    print(case, "->", path, "%.1f KB" % (os.path.getsize(path) / 1024))
 
 
 if __name__ == "__main__":

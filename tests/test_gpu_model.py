@@ -18,12 +18,13 @@ pytestmark = pytest.mark.gpu
 CASES = ["c1", "t_bip2", "t_nb2", "t_lru", "t_2q", "c2_prefix"]
 
 
-def make_model(g, device="cuda:0"):
+def make_model(g, device="cuda:0", reuse=True, budget=None):
     from orca_b200.neighbor_finder import get_neighbor_finder
     from orca_b200.tgn import TGN
     spec = g.spec
     nf = get_neighbor_finder(g, device=device)
-    args = argparse.Namespace(bs=spec.bs, n_degree=spec.n_degree, budget=spec.budget, reuse=True, gradient=False,
+    budget = spec.budget if budget is None else budget
+    args = argparse.Namespace(bs=spec.bs, n_degree=spec.n_degree, budget=budget, reuse=reuse, gradient=False,
                               n_nodes=g.n_nodes, n_edges=g.n_edges + 1)
     tgn = TGN(neighbor_finder=nf, node_features=None, edge_features=g.edge_features, device=torch.device(device),
               n_layers=spec.n_layers, n_heads=2, dropout=0.1, use_memory=True, node_dimension=172,
@@ -131,6 +132,49 @@ def test_eval_matches_oracle_on_fresh_inputs():
     assert max_rel(tgn.memory.memory.cpu().numpy(), orc.memory.numpy(), floor=0.05) < 1e-3
     assert max_rel(tgn.embedding_module.histories[0].emb.cpu().numpy(), orc.hist[0].numpy(), floor=0.05) < 1e-3
     assert np.array_equal(tgn.embedding_module.histories[0].cache_flag != 0, orc.cache_flag[0] != 0)
+
+
+@pytest.mark.parametrize("case,reuse", [("t_nb2_reuse0", True), ("t_nb2_noreuse", False)])
+def test_other_recursions_match_reference_fixture(case, reuse):
+    """compute_embedding_reuse (budget == 0) and compute_embedding (reuse=False) of the reference,
+    modules/embedding_module.py:154-182 and :116-147."""
+    gold = golden(case)
+    g = graph(str(gold["spec"]))
+    spec = g.spec
+    scores, neg = gold["scores"], gold["neg"]
+    tgn = make_model(g, reuse=reuse, budget=0)
+    worst = 0.0
+    for b, src, dst, ts, eidx in batches(g, scores.shape[0]):
+        n = len(src)
+        p, q = tgn.compute_edge_probabilities(src, dst, neg[b * spec.bs: b * spec.bs + n], ts, eidx,
+                                              spec.n_degree, reuse, False, None)
+        n1, n_pos, _ = tgn.check_status()
+        assert n1 == (3 * n if reuse else 3 * n * (1 + spec.n_degree))
+        assert n_pos == len(np.unique(np.r_[src, dst]))
+        worst = max(worst, max_rel(p.cpu().numpy().ravel(), scores[b, 0, :n]),
+                    max_rel(q.cpu().numpy().ravel(), scores[b, 1, :n]))
+    assert worst < 1e-3, worst
+    pick = gold["state_nodes"].astype(np.int64)
+    assert max_rel(tgn.memory.memory[pick].cpu().numpy(), gold["state_memory"], floor=0.05) < 1e-3
+    if reuse:
+        h = tgn.embedding_module.histories[0]
+        assert max_rel(h.emb[pick].cpu().numpy(), gold["state_history"], floor=0.05) < 1e-3
+
+
+def test_recursions_share_one_model():
+    """The call's `reuse` argument picks the recursion per batch (model/tgn_model.py:114-120): a model
+    built with history tables also serves reuse=False, and gives the scores of a model without."""
+    g = graph("t_nb2")
+    a, b = make_model(g, reuse=True), make_model(g, reuse=False, budget=0)
+    spec = g.spec
+    for i, src, dst, ts, eidx in batches(g, 3):
+        neg = np.roll(dst, 1)
+        pa, qa = a.compute_edge_probabilities(src, dst, neg, ts, eidx, spec.n_degree, False, False, None)
+        pb, qb = b.compute_edge_probabilities(src, dst, neg, ts, eidx, spec.n_degree, False, False, None)
+        a.check_status(), b.check_status()
+        assert torch.equal(pa, pb) and torch.equal(qa, qb)
+    with pytest.raises(AttributeError):
+        b.compute_edge_probabilities(src, dst, neg, ts, eidx, spec.n_degree, True, False, None)
 
 
 def test_unsupported_modes_fail_loudly():

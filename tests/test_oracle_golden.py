@@ -103,3 +103,26 @@ def test_forward_matches_reference(case):
     assert max_rel(model.messages[pick[:32]].numpy(), gold["state_messages"], floor=0.05) < 2e-4
     assert np.array_equal(model.msg_ts[pick].numpy(), gold["state_msg_ts"])
     assert np.array_equal(model.msg_flag[pick].astype(np.uint8), gold["state_flags"])
+
+
+@pytest.mark.parametrize("case,reuse,budget", [("t_nb2_reuse0", True, 0), ("t_nb2_noreuse", False, 0)])
+def test_other_recursions_match_reference(case, reuse, budget):
+    """Unlimited reuse (modules/embedding_module.py:154-182) and no reuse (:116-147)."""
+    gold = golden(case)
+    g = graph(str(gold["spec"]))
+    spec = g.spec
+    scores = gold["scores"]
+    model = tgn_oracle.OracleTGN(_adj(g), g.edge_features, state_dict(spec.n_layers), g.n_nodes,
+                                 n_layers=spec.n_layers, budget=budget)
+    neg = gold["neg"]
+    worst = 0.0
+    for b, src, dst, ts, eidx in batches(g, scores.shape[0]):
+        n = len(src)
+        p, q = model.compute_edge_probabilities(src, dst, neg[b * spec.bs: b * spec.bs + n], ts, eidx,
+                                                spec.n_degree, None, reuse=reuse)
+        worst = max(worst, max_rel(p.numpy().ravel(), scores[b, 0, :n]), max_rel(q.numpy().ravel(), scores[b, 1, :n]))
+    assert worst < 2e-5, worst
+    pick = gold["state_nodes"].astype(np.int64)
+    assert max_rel(model.memory[pick].numpy(), gold["state_memory"], floor=0.05) < 2e-4
+    if reuse:
+        assert max_rel(model.hist[0][pick].numpy(), gold["state_history"], floor=0.05) < 2e-4
