@@ -38,6 +38,7 @@ extern "C" {
 #define ORCA_DIM 172
 #define ORCA_HEADS 2
 #define ORCA_MAX_K 32
+#define ORCA_CAND_CAP 2048 /* listed candidates of the uncached set; more fall back to a bitmap scan */
 #define ORCA_MSG_DIM (4 * ORCA_DIM)          /* [mem_src | mem_dst | edge feat | time enc] */
 #define ORCA_KEY_DIM (3 * ORCA_DIM)          /* [neighbour | edge feat | time enc]         */
 #define ORCA_QT_DIM (ORCA_HEADS * ORCA_KEY_DIM)
@@ -332,7 +333,8 @@ typedef struct {
   int64_t *last_pos;        /* [n_nodes] scratch of orca_last_occurrence              */
   int64_t *epoch_base;      /* host-resident counter owned by the caller              */
   int32_t rank, world;      /* orca_tgn_eval_batch_sharded only; world <= 1 means one GPU */
-  uint32_t *cand_bitmap;    /* (n_nodes+31)/32 words, zero-initialised once by the caller       */
+  uint32_t *cand_bitmap;    /* (n_nodes+31)/32 + 1 + ORCA_CAND_CAP words (candidate bitmap, list    */
+                            /* length, list), zero-initialised once by the caller                */
   int32_t mode;             /* ORCA_MODE_*: which recursion of the embedding module runs        */
 } orca_tgn_t;
 

@@ -17,6 +17,7 @@ DIM = 172
 QT_DIM = 1032
 QT_LD = 1056
 MSG_DIM = 688
+CAND_CAP = 2048   # ORCA_CAND_CAP
 
 c_f32p = C.c_void_p
 c_i32p = C.c_void_p

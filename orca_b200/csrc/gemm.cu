@@ -454,10 +454,44 @@ int orca_attn_output(const orca_attn_weights_t *w, const float *d_ctx, const uin
                      const int32_t *d_n_rows, float *d_out, float *d_push_table,
                      const int32_t *d_push_ids, const uint8_t *d_push_win, float *d_scratch_hidden,
                      void *stream) {
+  ORCA_CHECK_ARG(d_push_table == nullptr || (d_push_ids && d_push_win));
+  return orca::attn_output_impl(w, d_ctx, d_valid, d_feat, d_idx, n_rows_cap, d_n_rows, d_out, d_push_table,
+                                d_push_ids, d_push_win, nullptr, 0, 0, d_scratch_hidden, (cudaStream_t)stream);
+}
+
+}  // extern "C"
+
+namespace orca {
+
+// winners of a push from the last-occurrence records (fp32 debug path only; the tensor-core epilogue
+// reads the records itself)
+__global__ void win_from_last_pos_kernel(const int32_t *__restrict__ ids, int cap, const int32_t *d_n,
+                                         const unsigned long long *__restrict__ last_pos, long long base,
+                                         int all_from, uint8_t *__restrict__ win) {
+  const int n = rows_of(cap, d_n);
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    win[i] = (i >= all_from || last_pos[ids[i]] == (unsigned long long)(base + i)) ? 1 : 0;
+}
+
+// d_push_win given: rows with a non-zero byte are pushed.  Otherwise (d_last_pos given) row i is
+// pushed when i >= all_from or when last_pos[push_ids[i]] == base + i; `d_push_win` is then only
+// scratch for the fp32 debug path and may be NULL in tensor-core mode.
+int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uint8_t *d_valid, const float *d_feat,
+                     const int32_t *d_idx, int32_t n_rows_cap, const int32_t *d_n_rows, float *d_out,
+                     float *d_push_table, const int32_t *d_push_ids, const uint8_t *d_push_win,
+                     const int64_t *d_last_pos, long long base, int all_from, float *d_scratch_hidden,
+                     cudaStream_t stream) {
   ORCA_CHECK_ARG(w && w->G && w->b1 && w->g && w->W2t && w->b2 && w->ln_w && w->ln_b);
   ORCA_CHECK_ARG(d_ctx && d_valid && d_feat && d_out && n_rows_cap >= 0);
-  ORCA_CHECK_ARG(d_push_table == nullptr || (d_push_ids && d_push_win));
   if (n_rows_cap == 0) return ORCA_OK;
+  if (g_projection_mode != 0 && d_push_table != nullptr && d_last_pos != nullptr) {
+    ORCA_CHECK_ARG(d_push_win != nullptr);
+    win_from_last_pos_kernel<<<std::min(ceil_div(n_rows_cap, 256), 1024), 256, 0, stream>>>(
+        d_push_ids, n_rows_cap, d_n_rows, reinterpret_cast<const unsigned long long *>(d_last_pos), base, all_from,
+        const_cast<uint8_t *>(d_push_win));
+    ORCA_COUNT_LAUNCH();
+    ORCA_LAUNCH_CHECK();
+  }
   if (g_projection_mode == 0) {
     // (the tensor-core kernel zeroes the whole first source of an invalid row: zero_cols == its width)
     ORCA_CHECK_ARG(w->G_tc && w->W2t_tc && d_scratch_hidden);
@@ -491,7 +525,10 @@ int orca_attn_output(const orca_attn_weights_t *w, const float *d_ctx, const uin
     b.out = d_out;
     b.push_table = d_push_table;
     b.push_ids = d_push_ids;
-    b.push_win = d_push_win;
+    b.push_win = d_last_pos ? nullptr : d_push_win;
+    b.push_last_pos = reinterpret_cast<const unsigned long long *>(d_last_pos);
+    b.push_base = base;
+    b.push_all_from = all_from;
     return tc::launch(tc::EPI_LAYERNORM, b, 1, (cudaStream_t)stream);
   }
   int rc = ensure_f2_smem();
@@ -512,6 +549,10 @@ int orca_attn_output(const orca_attn_weights_t *w, const float *d_ctx, const uin
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;
 }
+
+}  // namespace orca
+
+extern "C" {
 
 int orca_score(const orca_score_weights_t *w, const float *d_emb, int32_t b, float *d_prob, void *stream) {
   ORCA_CHECK_ARG(w && w->W1t && w->b1 && w->w2 && d_emb && d_prob && b >= 0);

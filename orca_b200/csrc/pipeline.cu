@@ -5,13 +5,15 @@
 #include <vector>
 
 #include "common.cuh"
+#include "index_ops.cuh"
+#include "tc_gemm.cuh"
 
 namespace orca {
 
 static inline size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
 
 struct Workspace {
-  int32_t *nodes1; double *ts1; int32_t *n1;
+  int32_t *nodes1; double *ts1; int32_t *n1; int32_t *n_unc;
   int32_t *nbr2, *eid2; float *dt2;
   int32_t *nbr1, *eid1; float *dt1;
   uint8_t *win1, *valid;
@@ -34,6 +36,7 @@ static Workspace carve(void *base, int b_cap, int u_cap, int k, int64_t n_nodes)
   w.nodes1 = (int32_t *)take(R1 * 4);
   w.ts1 = (double *)take(R1 * 8);
   w.n1 = (int32_t *)take(4);
+  w.n_unc = (int32_t *)take(4);
   w.nbr2 = (int32_t *)take(N * k * 4);
   w.eid2 = (int32_t *)take(N * k * 4);
   w.dt2 = (float *)take(N * k * 4);
@@ -81,6 +84,34 @@ __global__ void batch_prep_kernel(const int32_t *__restrict__ batch, const doubl
 __global__ void copy_i32_kernel(const int32_t *__restrict__ src, int32_t *__restrict__ dst, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) dst[i] = src[i];
+}
+
+// History.update_flag with a plan (modules/history.py:25-30) in one block: clear the flags of the plan
+// that set them, set the flags of this batch's plan, and keep a copy of it for the next clearing
+__global__ void __launch_bounds__(1024)
+plan_flags_kernel(uint8_t *__restrict__ flag, int64_t n_nodes, int32_t *__restrict__ prev_plan, int n_prev,
+                  const int32_t *__restrict__ plan, int n_plan) {
+  // eight independent loads per thread in flight: the loop is a chain of L2 round trips otherwise
+  for (int i0 = threadIdx.x; i0 < n_prev; i0 += 8 * 1024) {
+    int v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = i0 + u * 1024 < n_prev ? prev_plan[i0 + u * 1024] : -1;
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (v[u] >= 0 && v[u] < n_nodes) flag[v[u]] = 0;
+  }
+  __threadfence();
+  __syncthreads();
+  for (int i0 = threadIdx.x; i0 < n_plan; i0 += 8 * 1024) {
+    int v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = i0 + u * 1024 < n_plan ? plan[i0 + u * 1024] : -1;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (v[u] >= 0 && v[u] < n_nodes) flag[v[u]] = 1;
+      if (i0 + u * 1024 < n_plan) prev_plan[i0 + u * 1024] = v[u];
+    }
+  }
 }
 
 __global__ void set_flags_counted_kernel(uint8_t *__restrict__ flag, int64_t n_nodes,
@@ -254,9 +285,12 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
   const bool push1 = mode != ORCA_MODE_NO_REUSE;
 
   ORCA_TRY(g_trace.mark(-1, s));
-  batch_prep_kernel<<<ceil_div(N, 256), 256, 0, s>>>(d_batch_i32, d_batch_ts, b, w.nodes1, w.ts1, w.cat_dst, w.n1);
-  ORCA_COUNT_LAUNCH();
-  ORCA_LAUNCH_CHECK();
+  const bool fused_head = m->n_layers == 2 && mode == ORCA_MODE_BUDGET;   // the head kernel builds the row list
+  if (!fused_head) {
+    batch_prep_kernel<<<ceil_div(N, 256), 256, 0, s>>>(d_batch_i32, d_batch_ts, b, w.nodes1, w.ts1, w.cat_dst, w.n1);
+    ORCA_COUNT_LAUNCH();
+    ORCA_LAUNCH_CHECK();
+  }
   ORCA_TRY(g_trace.mark(PH_PREP, s));
 
   float *emb_top = d_emb_out ? d_emb_out : w.emb2;
@@ -275,18 +309,27 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     ORCA_TRY(g_trace.mark(PH_OUTPUT_L2, s));
   } else {
     // top-level neighbour table; then the row list of layer 1 by recursion mode
-    const int32_t *nbr1 = w.nbr1, *eid1 = w.eid1, *gather2 = w.nbr2;
-    const float *dt1 = w.dt1;
+    const int32_t *nbr1 = w.nbr1, *eid1 = w.eid1, *gather2 = w.nbr2, *eid2 = w.eid2;
+    const float *dt1 = w.dt1, *dt2 = w.dt2;
     const float *table2 = m->hist_emb;
     const int32_t *d_n1 = w.n1;
+    const long long base1 = *m->epoch_base;   // layer-1 row i holds the record base1 + i
     if (mode == ORCA_MODE_BUDGET) {
-      // the uncached out-of-batch neighbours join the row list
-      ORCA_TRY(orca_sample_topk_mark(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
-                                     nullptr, k, w.nbr2, w.eid2, nullptr, w.dt2, d_status, m->cache_flag,
-                                     m->cand_bitmap, s));
+      // One launch builds the row list of the batch and its neighbour table -- which is both the top-level
+      // table and the layer-1 table of the same rows (same node, same query time) -- marks the uncached
+      // candidates and records the last occurrence of every row's node.  The uncached out-of-batch
+      // neighbours then join the row list and only those rows are sampled by a second launch.
+      ORCA_TRY(launch_batch_head(m, d_batch_i32, d_batch_ts, b, w.nodes1, w.ts1, w.cat_dst, w.nbr1, w.eid1, w.dt1,
+                                 d_status, base1, s));
       ORCA_TRY(g_trace.mark(PH_SAMPLE_TOP, s));
-      ORCA_TRY(orca_find_uncached_marked(m->cand_bitmap, N, m->n_nodes, w.nodes1, w.ts1, u_cap, w.n1, d_status, s));
+      ORCA_TRY(launch_uncached_finish(m, N, w.nodes1, w.ts1, u_cap, w.n1, w.n_unc, d_status, base1, s));
       ORCA_TRY(g_trace.mark(PH_UNCACHED, s));
+      if (u_cap > 0)
+        ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1 + N, w.ts1 + N,
+                                  u_cap, w.n_unc, k, w.nbr1 + (size_t)N * k, w.eid1 + (size_t)N * k, nullptr,
+                                  w.dt1 + (size_t)N * k, d_status, s));
+      gather2 = w.nbr1, eid2 = w.eid1, dt2 = w.dt1;
+      *m->epoch_base += R1;
     } else {
       ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
                                 nullptr, k, w.nbr2, w.eid2, nullptr, w.dt2, d_status, s));
@@ -299,17 +342,17 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
         table2 = w.emb1;
       }
       ORCA_TRY(g_trace.mark(PH_UNCACHED, s));
-    }
-    if (mode == ORCA_MODE_REUSE_ALL) {
-      // layer 1 covers the batch rows only and shares the top-level neighbour table
-      nbr1 = w.nbr2, eid1 = w.eid2, dt1 = w.dt2;
-      d_n1 = nullptr;
-    } else {
-      ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, R1,
-                                w.n1, k, w.nbr1, w.eid1, nullptr, w.dt1, d_status, s));
+      if (mode == ORCA_MODE_REUSE_ALL) {
+        // layer 1 covers the batch rows only and shares the top-level neighbour table
+        nbr1 = w.nbr2, eid1 = w.eid2, dt1 = w.dt2;
+        d_n1 = nullptr;
+      } else {
+        ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, R1,
+                                  w.n1, k, w.nbr1, w.eid1, nullptr, w.dt1, d_status, s));
+      }
     }
     ORCA_TRY(g_trace.mark(PH_SAMPLE_L1, s));
-    if (push1) {
+    if (mode == ORCA_MODE_REUSE_ALL) {
       ORCA_TRY(orca_last_occurrence(w.nodes1, R1, d_n1, m->n_nodes, m->last_pos, *m->epoch_base, w.win1,
                                     nullptr, nullptr, s));
       *m->epoch_base += R1;
@@ -321,9 +364,11 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     ORCA_TRY(orca_attn_gather(w.qt, m->mem.memory, m->edge_table, m->time_w, nbr1, eid1, dt1, k, R1,
                               d_n1, w.ctx, w.valid, d_status, s));
     ORCA_TRY(g_trace.mark(PH_GATHER_L1, s));
-    ORCA_TRY(orca_attn_output(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.nodes1, R1, d_n1, w.emb1,
-                              push1 ? m->hist_emb : nullptr, push1 ? w.nodes1 : nullptr,
-                              push1 ? w.win1 : nullptr, w.hidden, s));
+    // (budget mode: the winners of the push come from the records of the head kernel; the appended
+    // rows are distinct out-of-batch nodes, so each of them wins)
+    ORCA_TRY(attn_output_impl(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.nodes1, R1, d_n1, w.emb1,
+                              push1 ? m->hist_emb : nullptr, push1 ? w.nodes1 : nullptr, push1 ? w.win1 : nullptr,
+                              mode == ORCA_MODE_BUDGET ? m->last_pos : nullptr, base1, N, w.hidden, s));
     ORCA_TRY(g_trace.mark(PH_OUTPUT_L1, s));
     if (g_overlap.enabled && !g_trace.on) {
       ORCA_TRY(g_overlap.ensure());
@@ -331,22 +376,23 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
       ORCA_CUDA(cudaStreamWaitEvent(g_overlap.aux, g_overlap.fork, 0));
       forked = true;
     }
-    // cache flags follow the plan of this batch (History.update_flag)
+    // cache flags follow the plan of this batch (History.update_flag); the next reader of the flags is
+    // the next batch's head kernel, so this runs beside the top layer
+    cudaStream_t fs = forked ? g_overlap.aux : s;
     if (mode != ORCA_MODE_BUDGET) {
       // no flags outside the budgeted recursion
     } else if (d_plan != nullptr) {
       const bool know_prev = *m->n_prev_plan >= 0;
-      ORCA_TRY(orca_history_set_flags(m->cache_flag, m->n_nodes, know_prev ? m->prev_plan : nullptr,
-                                      know_prev ? *m->n_prev_plan : 0, d_plan, n_plan, s));
-      if (n_plan > 0) {
-        copy_i32_kernel<<<ceil_div(n_plan, 256), 256, 0, s>>>(d_plan, m->prev_plan, n_plan);
-        ORCA_COUNT_LAUNCH();
-      }
+      if (!know_prev) ORCA_CUDA(cudaMemsetAsync(m->cache_flag, 0, (size_t)m->n_nodes, fs));
+      plan_flags_kernel<<<1, 1024, 0, fs>>>(m->cache_flag, m->n_nodes, m->prev_plan, know_prev ? *m->n_prev_plan : 0,
+                                            d_plan, n_plan);
+      ORCA_COUNT_LAUNCH();
+      ORCA_LAUNCH_CHECK();
       *m->n_prev_plan = n_plan;
     } else {
       // plan-less rule: the flags of the pushed ids are set and never cleared
-      set_flags_counted_kernel<<<std::min(ceil_div(R1, 256), 1024), 256, 0, s>>>(m->cache_flag, m->n_nodes,
-                                                                                 w.nodes1, R1, w.n1);
+      set_flags_counted_kernel<<<std::min(ceil_div(R1, 256), 1024), 256, 0, fs>>>(m->cache_flag, m->n_nodes,
+                                                                                  w.nodes1, R1, w.n1);
       ORCA_COUNT_LAUNCH();
       *m->n_prev_plan = -1;
     }
@@ -354,7 +400,7 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     // layer 2 over the history rows of the top-level neighbours
     ORCA_TRY(orca_attn_query(&m->attn[1], w.emb1, nullptr, N, nullptr, w.qt, s));
     ORCA_TRY(g_trace.mark(PH_QUERY_L2, s));
-    ORCA_TRY(orca_attn_gather(w.qt, table2, m->edge_table, m->time_w, gather2, w.eid2, w.dt2, k, N,
+    ORCA_TRY(orca_attn_gather(w.qt, table2, m->edge_table, m->time_w, gather2, eid2, dt2, k, N,
                               nullptr, w.ctx, w.valid, d_status, s));
     ORCA_TRY(g_trace.mark(PH_GATHER_L2, s));
     ORCA_TRY(orca_attn_output(&m->attn[1], w.ctx, w.valid, w.emb1, nullptr, N, nullptr, emb_top, nullptr,
@@ -368,8 +414,7 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
   // raw messages of the batch (last occurrence per node in [src|dst]) and the memory update; on the
   // auxiliary stream when the fork event was recorded after the last reader of the memory table
   cudaStream_t ms = forked ? g_overlap.aux : s;
-  ORCA_TRY(orca_last_occurrence(d_batch_i32, 2 * b, nullptr, m->n_nodes, m->last_pos, *m->epoch_base,
-                                w.is_last2, w.win_pos, w.n_win, ms));
+  ORCA_TRY(launch_last_occ_compact(d_batch_i32, 2 * b, m->n_nodes, m->last_pos, *m->epoch_base, w.win_pos, w.n_win, ms));
   *m->epoch_base += 2 * b;
   ORCA_TRY(g_trace.mark(PH_LAST_OCC_MSG, s));
   ORCA_TRY(orca_message_store(&m->mem, m->edge_table, m->time_w, d_batch_i32, w.cat_dst, d_batch_ts,

@@ -52,6 +52,61 @@ __device__ __forceinline__ long long lower_bound_group(const double *__restrict_
   return lo + __popc(b);
 }
 
+// One query: lower bound, copy of the k entries in front of it (right-aligned, zero padded), and --
+// optionally -- marking of the sampled neighbours as candidates of the uncached set: the neighbour
+// (the padding node 0 for an empty slot) gets its bit in `cand_bitmap` when its cache flag is clear.
+// Hub nodes are sampled thousands of times per batch, so the bit is tested first and only the first
+// few writers pay for an atomic on the same word; the one writer that flips the bit also appends the id
+// to `cand_list` (if given), which lets the finishing kernel skip the scan of the whole bitmap.
+template <int G>
+__device__ __forceinline__ void sample_query(const int64_t *__restrict__ indptr, const int32_t *__restrict__ adj_nbr,
+                                             const int32_t *__restrict__ adj_eid, const double *__restrict__ adj_ts,
+                                             int64_t n_nodes, int node, double t, int q, int k, int lane,
+                                             unsigned gmask, int gshift, int32_t *__restrict__ o_nbr,
+                                             int32_t *__restrict__ o_eid, float *__restrict__ o_et,
+                                             float *__restrict__ o_dt, int32_t *status,
+                                             const uint8_t *__restrict__ cache_flag, uint32_t *__restrict__ cand_bitmap,
+                                             int32_t *__restrict__ cand_count, int32_t *__restrict__ cand_list,
+                                             const unsigned long long *__restrict__ last_pos = nullptr,
+                                             unsigned long long base = 0) {
+  long long beg = 0, end = 0;
+  if (node >= 0 && node < n_nodes) {
+    beg = indptr[node];
+    end = indptr[node + 1];
+  } else {
+    report(status, ORCA_E_BOUNDS, q);
+  }
+  const long long bound = lower_bound_group<G>(adj_ts, beg, end, t, lane, gmask, gshift);
+  if (lane < k) {
+    const long long src = bound - k + lane;
+    int nb = 0, ei = 0;
+    float et = 0.f;
+    if (src >= beg) {
+      nb = adj_nbr[src];
+      ei = adj_eid[src];
+      et = (float)adj_ts[src];
+    }
+    const size_t o = (size_t)q * k + lane;
+    o_nbr[o] = nb;
+    o_eid[o] = ei;
+    if (o_et) o_et[o] = et;
+    if (o_dt) o_dt[o] = (float)(t - (double)et);
+    // (with `last_pos`: a neighbour whose record already carries this batch's epoch is a row of the
+    // batch and can be skipped; rows recorded later than this test slip through and are removed by the
+    // finishing kernel, which sees all records)
+    if (cand_bitmap != nullptr && cache_flag[nb] == 0 && (last_pos == nullptr || __ldcg(&last_pos[nb]) < base)) {
+      const uint32_t bit = 1u << (nb & 31);
+      if ((__ldcg(&cand_bitmap[nb >> 5]) & bit) == 0) {
+        const uint32_t old = atomicOr(&cand_bitmap[nb >> 5], bit);
+        if (cand_list != nullptr && (old & bit) == 0) {
+          const int pos = atomicAdd(cand_count, 1);
+          if (pos < ORCA_CAND_CAP) cand_list[pos] = nb;
+        }
+      }
+    }
+  }
+}
+
 template <int G>
 __global__ void __launch_bounds__(256)
 sample_topk_kernel(const int64_t *__restrict__ indptr, const int32_t *__restrict__ adj_nbr,
@@ -65,40 +120,42 @@ sample_topk_kernel(const int64_t *__restrict__ indptr, const int32_t *__restrict
   const int lane = threadIdx.x % G;
   const int gshift = (threadIdx.x % 32) / G * G;
   const unsigned gmask = (G == 32) ? 0xffffffffu : (((1u << G) - 1u) << gshift);
+  for (int q = blockIdx.x * groups_per_block + threadIdx.x / G; q < n; q += gridDim.x * groups_per_block)
+    sample_query<G>(indptr, adj_nbr, adj_eid, adj_ts, n_nodes, nodes[q], qts[q], q, k, lane, gmask, gshift, o_nbr,
+                    o_eid, o_et, o_dt, status, cache_flag, cand_bitmap, nullptr, nullptr);
+}
+
+// The head of an eval batch in one launch: row list [src | dst | neg] with its query times and the
+// [dst | src] partner list, the top-level neighbour table of those rows (which is also the layer-1
+// table of the same rows), candidate marking, and the last-occurrence record of every row's node
+// (History.push keeps the last of duplicate ids: atomicMax of epoch + position).
+template <int G>
+__global__ void __launch_bounds__(256)
+batch_head_kernel(const int64_t *__restrict__ indptr, const int32_t *__restrict__ adj_nbr,
+                  const int32_t *__restrict__ adj_eid, const double *__restrict__ adj_ts, int64_t n_nodes,
+                  const int32_t *__restrict__ batch, const double *__restrict__ bts, int b, int k,
+                  int32_t *__restrict__ nodes1, double *__restrict__ ts1, int32_t *__restrict__ cat_dst,
+                  int32_t *__restrict__ o_nbr, int32_t *__restrict__ o_eid, float *__restrict__ o_dt, int32_t *status,
+                  const uint8_t *__restrict__ cache_flag, uint32_t *__restrict__ cand_bitmap,
+                  int32_t *__restrict__ cand_count, int32_t *__restrict__ cand_list,
+                  unsigned long long *__restrict__ last_pos, long long base) {
+  const int n = 3 * b;
+  const int groups_per_block = blockDim.x / G;
+  const int lane = threadIdx.x % G;
+  const int gshift = (threadIdx.x % 32) / G * G;
+  const unsigned gmask = (G == 32) ? 0xffffffffu : (((1u << G) - 1u) << gshift);
   for (int q = blockIdx.x * groups_per_block + threadIdx.x / G; q < n; q += gridDim.x * groups_per_block) {
-    const int node = nodes[q];
-    const double t = qts[q];
-    long long beg = 0, end = 0;
-    if (node >= 0 && node < n_nodes) {
-      beg = indptr[node];
-      end = indptr[node + 1];
-    } else {
-      report(status, ORCA_E_BOUNDS, q);
+    const int node = batch[q];
+    const double t = bts[q % b];
+    if (lane == 0) {
+      nodes1[q] = node;
+      ts1[q] = t;
+      if (q < 2 * b) cat_dst[q] = q < b ? batch[b + q] : batch[q - b];
+      if (node >= 0 && node < n_nodes) atomicMax(&last_pos[node], (unsigned long long)(base + q));
     }
-    const long long bound = lower_bound_group<G>(adj_ts, beg, end, t, lane, gmask, gshift);
-    if (lane < k) {
-      const long long src = bound - k + lane;
-      int nb = 0, ei = 0;
-      float et = 0.f;
-      if (src >= beg) {
-        nb = adj_nbr[src];
-        ei = adj_eid[src];
-        et = (float)adj_ts[src];
-      }
-      const size_t o = (size_t)q * k + lane;
-      o_nbr[o] = nb;
-      o_eid[o] = ei;
-      if (o_et) o_et[o] = et;
-      if (o_dt) o_dt[o] = (float)(t - (double)et);
-      // optional: mark the neighbour (the padding node 0 for an empty slot) as a candidate of the
-      // uncached set when its cache flag is clear
-      // (hub nodes are sampled thousands of times per batch: the bit is tested first so that only the
-      // first few writers pay for an atomic on the same word)
-      if (cand_bitmap != nullptr && cache_flag[nb] == 0) {
-        const uint32_t bit = 1u << (nb & 31);
-        if ((__ldcg(&cand_bitmap[nb >> 5]) & bit) == 0) atomicOr(&cand_bitmap[nb >> 5], bit);
-      }
-    }
+    sample_query<G>(indptr, adj_nbr, adj_eid, adj_ts, n_nodes, node, t, q, k, lane, gmask, gshift, o_nbr, o_eid,
+                    nullptr, o_dt, status, cache_flag, cand_bitmap, cand_count, cand_list, last_pos,
+                    (unsigned long long)base);
   }
 }
 
@@ -235,11 +292,10 @@ find_uncached_kernel(const int32_t *__restrict__ nbr, int n_query, int k, const 
 // (orca_sample_topk_mark): only the cheap part is left for the single block -- clear the bits of the
 // query nodes, count, scan, emit -- and the words are zeroed on the way so that the bitmap is clean
 // for the next batch.
-__global__ void __launch_bounds__(FU_THREADS)
-find_uncached_marked_kernel(uint32_t *__restrict__ gbm, int n_query, int64_t n_nodes,
-                            int32_t *__restrict__ nodes_io, double *__restrict__ ts_io, int u_cap,
-                            int32_t *__restrict__ d_n_total, int32_t *status) {
-  extern __shared__ uint32_t s_bitmap[];
+__device__ __forceinline__ int finish_from_bitmap(uint32_t *__restrict__ gbm, uint32_t *s_bitmap, int n_query,
+                                                  int64_t n_nodes, int32_t *__restrict__ nodes_io,
+                                                  double *__restrict__ ts_io, int u_cap,
+                                                  int32_t *__restrict__ d_n_total, int32_t *status) {
   __shared__ int s_scan[FU_THREADS / 32];
   __shared__ double s_tmax[FU_THREADS / 32];
   __shared__ int s_total;
@@ -322,15 +378,95 @@ find_uncached_marked_kernel(uint32_t *__restrict__ gbm, int n_query, int64_t n_n
       }
     }
   }
+  int u = s_total > 0 ? s_total - 1 : 0;
+  if (u > u_cap) {
+    if (tid == 0) report(status, ORCA_E_CAPACITY, u);
+    u = u_cap;
+  }
+  if (tid == 0) *d_n_total = n_query + u;
+  return u;
+}
+
+__global__ void __launch_bounds__(FU_THREADS)
+find_uncached_marked_kernel(uint32_t *__restrict__ gbm, int n_query, int64_t n_nodes,
+                            int32_t *__restrict__ nodes_io, double *__restrict__ ts_io, int u_cap,
+                            int32_t *__restrict__ d_n_total, int32_t *status) {
+  extern __shared__ uint32_t s_bitmap[];
+  finish_from_bitmap(gbm, s_bitmap, n_query, n_nodes, nodes_io, ts_io, u_cap, d_n_total, status);
+}
+
+// The finish when the sampling launch also listed the candidates (batch_head_kernel).  A short list
+// -- the usual case: most sampled neighbours are cached or in the batch -- is ranked directly: clear
+// the bits of the batch's own nodes, keep the candidates whose bit survived, order them by counting
+// (rank = number of smaller kept ids), drop rank 0, and clear their bits again, which leaves the bitmap
+// clean without touching the rest of it.  A list that overflowed falls back to the bitmap scan.
+__global__ void __launch_bounds__(FU_THREADS)
+uncached_finish_kernel(uint32_t *__restrict__ gbm, int32_t *__restrict__ cand_count,
+                       const int32_t *__restrict__ cand_list, int n_query, int64_t n_nodes,
+                       int32_t *__restrict__ nodes_io, double *__restrict__ ts_io, int u_cap,
+                       int32_t *__restrict__ d_n_total, int32_t *__restrict__ d_n_unc, int32_t *status,
+                       const unsigned long long *__restrict__ last_pos, unsigned long long base) {
+  extern __shared__ uint32_t s_bitmap[];
+  __shared__ double s_tmax2[FU_THREADS / 32];
+  __shared__ int s_kept;
+  const int tid = threadIdx.x;
+  const int nc = *cand_count;
+  if (nc > ORCA_CAND_CAP) {
+    const int u = finish_from_bitmap(gbm, s_bitmap, n_query, n_nodes, nodes_io, ts_io, u_cap, d_n_total, status);
+    if (tid == 0) {
+      *d_n_unc = u;
+      *cand_count = 0;
+    }
+    return;
+  }
+  int *s_c = reinterpret_cast<int *>(s_bitmap);   // ORCA_CAND_CAP kept ids (INT_MAX = dropped)
+  if (nc == 0) {   // nothing sampled outside the cache and the batch
+    if (tid == 0) {
+      *d_n_total = n_query;
+      *d_n_unc = 0;
+    }
+    return;
+  }
+  if (tid == 0) s_kept = 0;
+  double tmax = -1.0e300;
+  for (int i = tid; i < n_query; i += FU_THREADS) tmax = fmax(tmax, ts_io[i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) tmax = fmax(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+  if ((tid & 31) == 0) s_tmax2[tid >> 5] = tmax;
+  __syncthreads();
+  tmax = s_tmax2[0];
+  for (int i = 1; i < FU_THREADS / 32; ++i) tmax = fmax(tmax, s_tmax2[i]);
+  for (int i = tid; i < nc; i += FU_THREADS) {
+    const int c = cand_list[i];
+    // a row of this batch carries a record of this batch's epoch (all records are in by now)
+    const bool keep = __ldcg(&last_pos[c]) < base;
+    atomicAnd(&gbm[c >> 5], ~(1u << (c & 31)));
+    if (keep) atomicAdd(&s_kept, 1);
+    s_c[i] = keep ? c : 0x7fffffff;
+  }
+  __syncthreads();
+  for (int i = tid; i < nc; i += FU_THREADS) {
+    const int c = s_c[i];
+    if (c == 0x7fffffff) continue;
+    int rank = 0;
+    for (int j = 0; j < nc; ++j) rank += s_c[j] < c ? 1 : 0;
+    if (rank >= 1 && rank - 1 < u_cap) {   // rank 0 is dropped (modules/embedding_module.py:212)
+      nodes_io[n_query + rank - 1] = c;
+      ts_io[n_query + rank - 1] = tmax;
+    }
+  }
   if (tid == 0) {
-    int u = s_total > 0 ? s_total - 1 : 0;
+    int u = s_kept > 0 ? s_kept - 1 : 0;
     if (u > u_cap) {
       report(status, ORCA_E_CAPACITY, u);
       u = u_cap;
     }
     *d_n_total = n_query + u;
+    *d_n_unc = u;
+    *cand_count = 0;
   }
 }
+
 
 // ---------------------------------------------------------------------------------------------
 // Last occurrence: pass 1 records, per id, the largest (epoch_base + position); pass 2 flags the
@@ -400,6 +536,134 @@ compact_flags_kernel(const uint8_t *__restrict__ is_last, int n_cap, const int32
   if (tid == 0) *n_compact = s_base;
 }
 
+// Last occurrence of every id of a short list and the ordered list of those positions, in one block:
+// record (atomicMax of epoch + position), then flag + scan + emit.
+__global__ void __launch_bounds__(1024)
+last_occ_compact_kernel(const int32_t *__restrict__ ids, int n, int64_t n_nodes,
+                        unsigned long long *__restrict__ last_pos, long long base,
+                        int32_t *__restrict__ compact, int32_t *__restrict__ n_compact) {
+  __shared__ int s_scan[32];
+  __shared__ int s_base;
+  const int tid = threadIdx.x;
+  if (tid == 0) s_base = 0;
+  // four positions per thread and sweep, loaded up front so that their round trips overlap
+  constexpr int U = 4;
+  for (int i0 = 0; i0 < n; i0 += U * 1024) {
+    int v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * 1024 + tid;
+      v[u] = i < n ? ids[i] : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (v[u] >= 0 && v[u] < n_nodes) atomicMax(&last_pos[v[u]], (unsigned long long)(base + i0 + u * 1024 + tid));
+  }
+  __threadfence();
+  __syncthreads();
+  for (int i0 = 0; i0 < n; i0 += U * 1024) {
+    int f[U];
+    {
+      int v[U];
+      unsigned long long rec[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + u * 1024 + tid;
+        v[u] = i < n ? ids[i] : -1;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) rec[u] = (v[u] >= 0 && v[u] < n_nodes) ? __ldcg(&last_pos[v[u]]) : 0ull;
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        f[u] = (v[u] >= 0 && v[u] < n_nodes && rec[u] == (unsigned long long)(base + i0 + u * 1024 + tid)) ? 1 : 0;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (i0 + u * 1024 >= n) break;
+      int incl = f[u];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int y = __shfl_up_sync(0xffffffffu, incl, o);
+        if ((tid & 31) >= o) incl += y;
+      }
+      if ((tid & 31) == 31) s_scan[tid >> 5] = incl;
+      __syncthreads();
+      if (tid < 32) {
+        int x = s_scan[tid], inc2 = x;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          int y = __shfl_up_sync(0xffffffffu, inc2, o);
+          if (tid >= o) inc2 += y;
+        }
+        s_scan[tid] = inc2 - x;
+      }
+      __syncthreads();
+      const int pos = s_base + s_scan[tid >> 5] + incl - f[u];
+      if (f[u]) compact[pos] = i0 + u * 1024 + tid;
+      __syncthreads();
+      if (tid == 1023) s_base = pos + f[u];
+      __syncthreads();
+    }
+  }
+  if (tid == 0) *n_compact = s_base;
+}
+
+// ---- launchers of the fused batch kernels (used by the batch pipeline)
+int launch_batch_head(const orca_tgn_t *m, const int32_t *d_batch, const double *d_bts, int b, int32_t *nodes1,
+                      double *ts1, int32_t *cat_dst, int32_t *o_nbr, int32_t *o_eid, float *o_dt, int32_t *status,
+                      long long base, cudaStream_t s) {
+  const int k = m->k, n = 3 * b, threads = 256;
+  int32_t *cand_count = reinterpret_cast<int32_t *>(m->cand_bitmap + (m->n_nodes + 31) / 32);
+  int32_t *cand_list = cand_count + 1;
+  unsigned long long *lp = reinterpret_cast<unsigned long long *>(m->last_pos);
+  if (k <= 16) {
+    const int grid = std::min(ceil_div(n, threads / 16), 148 * 16);
+    batch_head_kernel<16><<<grid, threads, 0, s>>>(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, d_batch,
+                                                   d_bts, b, k, nodes1, ts1, cat_dst, o_nbr, o_eid, o_dt, status,
+                                                   m->cache_flag, m->cand_bitmap, cand_count, cand_list, lp, base);
+  } else {
+    const int grid = std::min(ceil_div(n, threads / 32), 148 * 16);
+    batch_head_kernel<32><<<grid, threads, 0, s>>>(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, d_batch,
+                                                   d_bts, b, k, nodes1, ts1, cat_dst, o_nbr, o_eid, o_dt, status,
+                                                   m->cache_flag, m->cand_bitmap, cand_count, cand_list, lp, base);
+  }
+  ORCA_COUNT_LAUNCH();
+  ORCA_LAUNCH_CHECK();
+  return ORCA_OK;
+}
+
+int launch_uncached_finish(const orca_tgn_t *m, int n_query, int32_t *nodes_io, double *ts_io, int u_cap,
+                           int32_t *d_n_total, int32_t *d_n_unc, int32_t *status, long long base, cudaStream_t s) {
+  const int64_t words = (m->n_nodes + 31) / 32;
+  ORCA_CHECK_ARG(words < (1ll << 31));
+  size_t smem = std::max<size_t>(words <= FU_SMEM_WORDS ? (size_t)words * 4 : 0, (size_t)ORCA_CAND_CAP * 4);
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  ORCA_CUDA(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    ORCA_CUDA(cudaFuncSetAttribute(uncached_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   FU_SMEM_WORDS * 4));
+    configured_device = dev;
+  }
+  int32_t *cand_count = reinterpret_cast<int32_t *>(m->cand_bitmap + words);
+  uncached_finish_kernel<<<1, FU_THREADS, smem, s>>>(m->cand_bitmap, cand_count, cand_count + 1, n_query, m->n_nodes,
+                                                     nodes_io, ts_io, u_cap, d_n_total, d_n_unc, status,
+                                                     reinterpret_cast<const unsigned long long *>(m->last_pos),
+                                                     (unsigned long long)base);
+  ORCA_COUNT_LAUNCH();
+  ORCA_LAUNCH_CHECK();
+  return ORCA_OK;
+}
+
+int launch_last_occ_compact(const int32_t *d_ids, int n, int64_t n_nodes, int64_t *d_last_pos, long long base,
+                            int32_t *d_compact, int32_t *d_n_compact, cudaStream_t s) {
+  last_occ_compact_kernel<<<1, 1024, 0, s>>>(d_ids, n, n_nodes, reinterpret_cast<unsigned long long *>(d_last_pos),
+                                             base, d_compact, d_n_compact);
+  ORCA_COUNT_LAUNCH();
+  ORCA_LAUNCH_CHECK();
+  return ORCA_OK;
+}
+
 }  // namespace orca
 
 using namespace orca;
@@ -464,7 +728,8 @@ static int orca_sample_topk_impl(const int64_t *d_indptr, const int32_t *d_adj_n
   const int threads = 256;
   if (k <= 16) {
     const int per = threads / 16;
-    const int grid = std::min(ceil_div(n_query_cap, per), 148 * 16);
+    // (a launch whose row count lives on the device usually covers far fewer rows than its capacity)
+    const int grid = std::min(ceil_div(n_query_cap, per), d_n_query ? 148 * 2 : 148 * 16);
     sample_topk_kernel<16><<<grid, threads, 0, s>>>(d_indptr, d_adj_nbr, d_adj_eid, d_adj_ts, n_nodes,
                                                     d_nodes, d_ts, n_query_cap, d_n_query, k, d_nbr,
                                                     d_eid, d_edge_times, d_delta, d_status, d_cache_flag,

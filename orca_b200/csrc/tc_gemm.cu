@@ -12,21 +12,26 @@
 // once on the host; the activation heads/tails are split by the producer warps on their way into
 // shared memory.
 //
-// Tile: 128 rows x 176 columns per CTA, K consumed 64 elements per stage (4 MMA steps of K = 16,
-// 12 MMAs), two stages.  Every hop over an mbarrier costs ~250-300 cycles and a thread that arrives
-// on one stalls until its outstanding global loads have landed, so stages are large and the A side
-// is produced by two warp groups that alternate stages: while one group waits for its loads, the
-// other converts and the tensor core works on the stage before.
+// Tile: 128 rows x 176 columns, K consumed 64 elements per stage (4 MMA steps of K = 16, 12 MMAs),
+// two stages; a CTA walks the row blocks blockIdx.y, blockIdx.y + gridDim.y, ... of its column tile.
+// Every hop over an mbarrier costs ~250-300 cycles and a thread that arrives on one stalls until its
+// outstanding global loads have landed, so stages are large and the A side is produced by two warp
+// groups that alternate stages: while one group waits for its loads, the other converts and the tensor
+// core works on the stage before.  Measured per k-block: ~0.7 us, set by the bytes a stage pulls into
+// the SM (32 KB of fp32 rows + 44 KB of packed weights at ~55 B/clk).
 // Warp roles (320 threads):
 //   warps 0-3, 6-9  producer groups 0 / 1: group g fills stage g for every k-block kb = g (mod 2).
-//              A lane loads 16-byte pieces of the gathered rows (16 lanes cover the 256 contiguous
-//              bytes a row contributes to the stage; table rows picked by an index array, up to two
-//              tables concatenated along K), splits them and stores head and tail in the no-swizzle
-//              K-major core-matrix layout the MMA reads.  Group 0 later runs the epilogue (warp w
-//              owns accumulator lanes 32w..32w+31 = tile rows).
+//              A lane owns one tile row's table index (index array, up to two tables concatenated
+//              along K); inside a stage 8 lanes cover the 256 contiguous bytes a row contributes, 4
+//              rows per load instruction (row indices exchanged by shuffle), each lane splits its 8
+//              floats and stores one 16-byte chunk of the head and of the tail image in the no-swizzle
+//              K-major core-matrix layout the MMA reads.
 //   warp 4     streams the packed weight stage (one 44 KB bulk copy per stage).
 //   warp 5     allocates tensor memory and issues the MMAs (one thread), releasing each stage with
 //              tcgen05.commit.
+// Epilogue: the producer warps move the accumulators (thread = row) into a row-major tile in the idle
+// stage ring; all warps then write whole rows with coalesced stores (bias / ReLU / LayerNorm + push /
+// GRU gates applied on the way).
 //
 // Every wait on an mbarrier is bounded; a wait that gives up records ORCA_E_TIMEOUT and the kernel
 // runs to its end (tensor memory is always released).
@@ -138,18 +143,22 @@ __device__ __forceinline__ void tmem_ld16_sum(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(a[i]) + __uint_as_float(b[i]);
 }
 
-// x ~ head + tail, both bf16 (round to nearest even); returns the two pairs packed for an 8-byte store
-__device__ __forceinline__ void split_bf16(const float4 x, uint2 &hi, uint2 &lo) {
-  const __nv_bfloat16 h0 = __float2bfloat16_rn(x.x), h1 = __float2bfloat16_rn(x.y), h2 = __float2bfloat16_rn(x.z),
-                      h3 = __float2bfloat16_rn(x.w);
-  const __nv_bfloat16 l0 = __float2bfloat16_rn(x.x - __bfloat162float(h0)),
-                      l1 = __float2bfloat16_rn(x.y - __bfloat162float(h1)),
-                      l2 = __float2bfloat16_rn(x.z - __bfloat162float(h2)),
-                      l3 = __float2bfloat16_rn(x.w - __bfloat162float(h3));
-  hi.x = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
-  hi.y = (uint32_t)__bfloat16_as_ushort(h2) | ((uint32_t)__bfloat16_as_ushort(h3) << 16);
-  lo.x = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
-  lo.y = (uint32_t)__bfloat16_as_ushort(l2) | ((uint32_t)__bfloat16_as_ushort(l3) << 16);
+// x ~ head + tail, both bf16 (round to nearest even), for 8 consecutive K elements: one 16-byte chunk
+// of the head image and one of the tail image.  Packed conversions (two floats per instruction).
+__device__ __forceinline__ uint32_t pack_split(float x0, float x1, uint32_t &lo) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+  const uint32_t hb = *reinterpret_cast<const uint32_t *>(&h);
+  const float r0 = x0 - __uint_as_float(hb << 16);
+  const float r1 = x1 - __uint_as_float(hb & 0xffff0000u);
+  const __nv_bfloat162 l = __floats2bfloat162_rn(r0, r1);
+  lo = *reinterpret_cast<const uint32_t *>(&l);
+  return hb;
+}
+__device__ __forceinline__ void split_chunk(const float4 a, const float4 b, uint4 &hi, uint4 &lo) {
+  hi.x = pack_split(a.x, a.y, lo.x);
+  hi.y = pack_split(a.z, a.w, lo.y);
+  hi.z = pack_split(b.x, b.y, lo.z);
+  hi.w = pack_split(b.z, b.w, lo.w);
 }
 
 struct Smem {
@@ -165,20 +174,207 @@ __device__ __forceinline__ const float *src_row(const RowSrc &s, int m) {
   return s.p + (size_t)r * s.width;
 }
 
-__device__ __forceinline__ void st_shared_v2(uint32_t addr, uint2 v) {
-  asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(v.x), "r"(v.y) : "memory");
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
 }
 
 __device__ __align__(16) float g_zero16[4] = {0.f, 0.f, 0.f, 0.f};
 
+// Optional in-kernel timeline (development builds only, -DORCA_TC_TIMELINE): SM clock stamps per CTA.
+#ifdef ORCA_TC_TIMELINE
+__device__ long long g_tl[8192][32];
+#define TL(i)                                                                              \
+  do {                                                                                     \
+    const int bid_ = blockIdx.y * gridDim.x + blockIdx.x;                                  \
+    if (bid_ < 1600) g_tl[EPI * 1600 + bid_][(i)] = clock64();                             \
+  } while (0)
+#else
+#define TL(i)
+#endif
+
+// Pass 2 of the epilogue (all ten warps): one warp per row of the tile that pass 1 left in shared
+// memory, lanes along the columns (two 16-byte pieces per lane); four rows are in flight per warp so
+// that their load / shuffle / store chains overlap.  meta_a / meta_b: lane i of warp w holds the
+// per-row inputs of row w + 10*i (validity, push winner and id, GRU node).
+template <int EPI>
+__device__ __forceinline__ void tile_output(const Args &g, const float *tile, const float *s_bias, const float *s_v1,
+                                            const float *s_v2, const float *s_dot, int m0, int m_rows, int nt,
+                                            int warp, int lane, int meta_a, int meta_b) {
+  if (EPI == EPI_SCORE) {
+    const int tid = warp * 32 + lane;
+    if (tid < m_rows) g.out[m0 + tid] = 1.f / (1.f + expf(-(s_dot[tid] + s_dot[BM + tid] + g.b2)));
+    return;
+  }
+  constexpr int RB = 4;
+  const int c0 = nt * BN;
+  const int j0 = lane, j1 = lane + 32;
+  const int nj = (EPI == EPI_BIAS || EPI == EPI_GRU) ? BN / 4 : D / 4;
+  const bool has1 = j1 < nj;
+  const float4 f4z = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4 bA = *reinterpret_cast<const float4 *>(&s_bias[4 * j0]);
+  const float4 bB = has1 ? *reinterpret_cast<const float4 *>(&s_bias[4 * j1]) : f4z;
+  const float4 vA = *reinterpret_cast<const float4 *>(&s_v1[4 * j0]);
+  const float4 vB = has1 ? *reinterpret_cast<const float4 *>(&s_v1[4 * j1]) : f4z;
+  const float4 lA = *reinterpret_cast<const float4 *>(&s_v2[4 * j0]);
+  const float4 lB = has1 ? *reinterpret_cast<const float4 *>(&s_v2[4 * j1]) : f4z;
+  auto add4 = [](float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); };
+  const int uA = nt * (BN / 4) + j0, uB = nt * (BN / 4) + j1;   // GRU units of this lane
+  for (int it0 = 0; warp + (THREADS / 32) * it0 < m_rows; it0 += RB) {
+    float4 a[RB], b[RB];
+    float hA[RB], hB[RB];
+    int ma[RB], mb[RB], m[RB];
+    bool ok[RB];
+#pragma unroll
+    for (int k = 0; k < RB; ++k) {
+      const int r = warp + (THREADS / 32) * (it0 + k);
+      ok[k] = r < m_rows;
+      m[k] = m0 + r;
+      ma[k] = __shfl_sync(0xffffffffu, meta_a, (it0 + k) & 31);
+      mb[k] = __shfl_sync(0xffffffffu, meta_b, (it0 + k) & 31);
+      const float *trow_s = tile + (ok[k] ? r : 0) * TILE_LD;
+      a[k] = add4(*reinterpret_cast<const float4 *>(trow_s + 4 * j0), bA);
+      b[k] = has1 ? add4(*reinterpret_cast<const float4 *>(trow_s + 4 * j1), bB) : f4z;
+      hA[k] = hB[k] = 0.f;
+      if (EPI == EPI_GRU && ok[k]) {
+        const float *hrow = g.memory + (size_t)mb[k] * D;
+        if (uA < D) hA[k] = hrow[uA];
+        if (has1 && uB < D) hB[k] = hrow[uB];
+      }
+    }
+    if (EPI == EPI_BIAS) {
+#pragma unroll
+      for (int k = 0; k < RB; ++k)
+        if (ok[k]) {
+          float *o = g.out + (size_t)m[k] * g.out_ld + c0;
+          *reinterpret_cast<float4 *>(o + 4 * j0) = a[k];
+          if (has1) *reinterpret_cast<float4 *>(o + 4 * j1) = b[k];
+        }
+    } else if (EPI == EPI_HIDDEN) {
+#pragma unroll
+      for (int k = 0; k < RB; ++k)
+        if (ok[k]) {
+          const float rvf = ma[k] != 0 ? 1.f : 0.f;
+          float *o = g.out + (size_t)m[k] * D;
+          *reinterpret_cast<float4 *>(o + 4 * j0) =
+              make_float4(fmaxf(a[k].x + rvf * vA.x, 0.f), fmaxf(a[k].y + rvf * vA.y, 0.f),
+                          fmaxf(a[k].z + rvf * vA.z, 0.f), fmaxf(a[k].w + rvf * vA.w, 0.f));
+          if (has1)
+            *reinterpret_cast<float4 *>(o + 4 * j1) =
+                make_float4(fmaxf(b[k].x + rvf * vB.x, 0.f), fmaxf(b[k].y + rvf * vB.y, 0.f),
+                            fmaxf(b[k].z + rvf * vB.z, 0.f), fmaxf(b[k].w + rvf * vB.w, 0.f));
+        }
+    } else if (EPI == EPI_LAYERNORM) {
+      // both moments in one sweep (the row is O(1) after the merger, so E[y^2] - mean^2 loses nothing
+      // that matters at the 1e-5 epsilon)
+      float sum[RB], sumsq[RB];
+#pragma unroll
+      for (int k = 0; k < RB; ++k) {
+        sum[k] = (a[k].x + a[k].y) + (a[k].z + a[k].w) + (b[k].x + b[k].y) + (b[k].z + b[k].w);
+        sumsq[k] = a[k].x * a[k].x + a[k].y * a[k].y + a[k].z * a[k].z + a[k].w * a[k].w + b[k].x * b[k].x +
+                   b[k].y * b[k].y + b[k].z * b[k].z + b[k].w * b[k].w;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int k = 0; k < RB; ++k) {
+          sum[k] += __shfl_xor_sync(0xffffffffu, sum[k], o);
+          sumsq[k] += __shfl_xor_sync(0xffffffffu, sumsq[k], o);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < RB; ++k)
+        if (ok[k]) {
+          const float mean = sum[k] * (1.f / D);
+          const float sq = fmaxf(sumsq[k] - sum[k] * mean, 0.f);
+          const float inv = 1.f / sqrtf(sq * (1.f / D) + 1e-5f);
+          const float4 ya = make_float4((a[k].x - mean) * inv * vA.x + lA.x, (a[k].y - mean) * inv * vA.y + lA.y,
+                                        (a[k].z - mean) * inv * vA.z + lA.z, (a[k].w - mean) * inv * vA.w + lA.w);
+          const float4 yb = make_float4((b[k].x - mean) * inv * vB.x + lB.x, (b[k].y - mean) * inv * vB.y + lB.y,
+                                        (b[k].z - mean) * inv * vB.z + lB.z, (b[k].w - mean) * inv * vB.w + lB.w);
+          float *o = g.out + (size_t)m[k] * D;
+          *reinterpret_cast<float4 *>(o + 4 * j0) = ya;
+          if (has1) *reinterpret_cast<float4 *>(o + 4 * j1) = yb;
+          if (g.push_table != nullptr && ma[k] != 0) {
+            float *prow = g.push_table + (size_t)mb[k] * D;
+            *reinterpret_cast<float4 *>(prow + 4 * j0) = ya;
+            if (has1) *reinterpret_cast<float4 *>(prow + 4 * j1) = yb;
+          }
+        }
+    } else {  // EPI_GRU: four gate columns per unit, unit = nt * 44 + j
+#pragma unroll
+      for (int k = 0; k < RB; ++k)
+        if (ok[k]) {
+          if (uA < D) {
+            const float rg = 1.f / (1.f + expf(-a[k].x)), z = 1.f / (1.f + expf(-a[k].y));
+            g.out[(size_t)m[k] * D + uA] = (1.f - z) * tanhf(a[k].z + rg * a[k].w) + z * hA[k];
+          }
+          if (has1 && uB < D) {
+            const float rg = 1.f / (1.f + expf(-b[k].x)), z = 1.f / (1.f + expf(-b[k].y));
+            g.out[(size_t)m[k] * D + uB] = (1.f - z) * tanhf(b[k].z + rg * b[k].w) + z * hB[k];
+          }
+        }
+    }
+  }
+}
+
 template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   extern __shared__ unsigned char raw[];
-  const int M = rows_of(g.m_cap, g.d_m);
-  const int m0 = blockIdx.y * BM;
-  if (m0 >= M) return;  // nothing allocated yet
   const int nt = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool producer = warp < 4 || warp >= 6;
+  const int grp = warp >= 6 ? 1 : 0;
+  const int pw = grp ? warp - 6 : warp;   // producer warp within its group: tile rows pw*32 .. pw*32+31
+  const int rsub = lane >> 3, f = lane & 7;
+  const int w0 = g.a0.width, w1 = g.a1.width, Kd = g.Kd;
+  const int nkb = g.n_kblocks;
+
+  // Loads that head a dependency chain go out first, before anything waits: the table row of tile
+  // row (pw*32 + lane) for the producers, and the per-row inputs of the output pass (warp w writes
+  // rows w, w+10, ...; lane i holds what row w + 10*i needs).  For the CTA's first tile they are
+  // issued before the live row count is known (rows up to m_cap: the arrays are sized for it) and
+  // discarded afterwards if the row is not live.
+  int ri0 = -1, ri1 = -1, meta_a = 0, meta_b = 0;
+  auto prefetch_rows = [&](int m0, int limit) {
+    ri0 = ri1 = -1;
+    meta_a = meta_b = 0;
+    if (producer) {
+      const int m = m0 + pw * 32 + lane;
+      if (m < limit) {
+        ri0 = g.a0.idx ? g.a0.idx[m] : (g.a0.mod > 0 ? m % g.a0.mod : m) + g.a0.add;
+        if (w1) ri1 = g.a1.idx ? g.a1.idx[m] : (g.a1.mod > 0 ? m % g.a1.mod : m) + g.a1.add;
+        // an invalid row reads zeros for its first zero_cols columns: with zero_cols == a0.width (the
+        // only use) that is the whole first source
+        if (g.row_valid != nullptr && g.zero_cols > 0 && g.row_valid[m] == 0) ri0 = -1;
+      }
+    }
+    const int r = warp + (THREADS / 32) * lane;
+    const int m = m0 + r;
+    if (r < BM && m < limit) {
+      if (EPI == EPI_HIDDEN) meta_a = g.row_valid == nullptr ? 1 : g.row_valid[m];
+      if (EPI == EPI_LAYERNORM && g.push_table != nullptr) {
+        meta_b = g.push_ids[m];
+        if (g.push_win != nullptr) meta_a = g.push_win[m];
+      }
+      if (EPI == EPI_GRU) meta_b = g.nodes[m];
+    }
+  };
+  prefetch_rows(blockIdx.y * BM, g.m_cap);
+  const int M = rows_of(g.m_cap, g.d_m);
+  if ((int)blockIdx.y * BM >= M) return;  // nothing allocated yet
+  if (tid == 0) {
+    TL(0);
+#ifdef ORCA_TC_TIMELINE
+    unsigned long long gt_;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_));
+    const int tb_ = min(blockIdx.y * gridDim.x + blockIdx.x, 1599) + EPI * 1600;
+    g_tl[tb_][28] = (long long)gt_;
+    unsigned smid_;
+    asm volatile("mov.u32 %0, %smid;" : "=r"(smid_));
+    g_tl[tb_][29] = smid_;
+#endif
+  }
 
   const uint32_t raw_addr = smem_addr(raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -189,6 +385,40 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   const uint32_t accbar = bar_base + 128u;
   const uint32_t slot = bar_base + 136u;
   volatile uint32_t *slot_ptr = reinterpret_cast<volatile uint32_t *>(raw + (slot - raw_addr));
+
+  // Producer lane layout inside a stage: 8 lanes cover the 256 contiguous bytes a row contributes
+  // (two 16-byte loads each = one 8-element chunk), 4 rows per load instruction, 8 instructions for
+  // the warp's 32 rows.  The table row of each of them comes from the lane that owns it by shuffle.
+  const float4 *zero = reinterpret_cast<const float4 *>(g_zero16);
+  float4 x[16];
+  auto load_stage = [&](int kb) {
+    const int col = kb * BK + f * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r0 = __shfl_sync(0xffffffffu, ri0, 4 * i + rsub);
+      const int r1 = __shfl_sync(0xffffffffu, ri1, 4 * i + rsub);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int c = col + 4 * h;
+        const bool in0 = c < w0;
+        const int r = in0 ? r0 : r1;
+        const float *bp = in0 ? g.a0.p + (size_t)r * w0 + c : g.a1.p + (size_t)r * w1 + (c - w0);
+        x[2 * i + h] = *((c >= Kd || r < 0) ? zero : reinterpret_cast<const float4 *>(bp));
+      }
+    }
+  };
+  auto fix_rows = [&](int m0) {   // after the live count is known
+    if (producer && m0 + pw * 32 + lane >= M) ri0 = ri1 = -1;
+    if (EPI == EPI_LAYERNORM && g.push_table != nullptr && g.push_win == nullptr) {
+      // winners by record; only for live rows: the id of a row past the live count is not a valid index
+      const int r = warp + (THREADS / 32) * lane;
+      const int m = m0 + r;
+      if (r < BM && m < M)
+        meta_a = (m >= g.push_all_from || g.push_last_pos[meta_b] == (unsigned long long)(g.push_base + m)) ? 1 : 0;
+    }
+  };
+  fix_rows(blockIdx.y * BM);
+  if (producer && grp < nkb) load_stage(grp);   // in flight while the CTA sets itself up
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -206,9 +436,9 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   // epilogue vectors of this column tile, staged once (a global load per accumulator chunk would put
   // an L2 round trip into every step of the epilogue)
   __shared__ __align__(16) float s_bias[BN], s_v1[BN], s_v2[BN];
-  if (tid >= 192) {   // warps 6-9
+  if (warp == 4 || warp == 5) {
     const int lim = (EPI == EPI_BIAS || EPI == EPI_GRU) ? BN : D;
-    for (int i = tid - 192; i < BN; i += 128) {
+    for (int i = tid - 128; i < BN; i += 64) {
       const bool in = i < lim;
       s_bias[i] = in ? g.bias[nt * BN + i] : 0.f;
       const float *v1 = EPI == EPI_HIDDEN ? g.bias2 : EPI == EPI_LAYERNORM ? g.ln_w : EPI == EPI_SCORE ? g.w2 : nullptr;
@@ -216,221 +446,135 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
       s_v2[i] = (EPI == EPI_LAYERNORM && in) ? g.ln_b[i] : 0.f;
     }
   }
-  // per-row source pointers of the tile, resolved once (index arrays, validity)
-  __shared__ const float *s_p0[BM];
-  __shared__ const float *s_p1[BM];
-  if (tid < BM) {
-    const int m = m0 + tid;
-    const float *q0 = g_zero16, *q1 = g_zero16;
-    if (m < M) {
-      q0 = src_row(g.a0, m);
-      if (g.a1.width) q1 = src_row(g.a1, m);
-      // an invalid row reads zeros for its first zero_cols columns: with zero_cols == a0.width (the
-      // only use) that is the whole first source
-      if (g.row_valid != nullptr && g.row_valid[m] == 0 && g.zero_cols > 0) q0 = nullptr;
-    } else {
-      q0 = nullptr;
-      q1 = nullptr;
-    }
-    s_p0[tid] = q0;
-    s_p1[tid] = q1;
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *slot_ptr;
-  const int nkb = g.n_kblocks;
+  if (tid == 0) TL(1);
   bool alive = true;
+  float *tile = reinterpret_cast<float *>(raw + (base - raw_addr));
+  __shared__ float s_dot[2][BM];   // scorer: partial dot products of the two column halves
+  // uses of stage s per tile: its k-blocks are s, s+2, ...; the barrier phase of a use is its running index
+  const int uses0 = (nkb + 1) / 2, uses1 = nkb / 2;
 
-  if (warp < 4 || warp >= 6) {
-    // ------------------------------------------------------------------ producer groups
-    const int grp = warp >= 6 ? 1 : 0;
-    const int pw = grp ? warp - 6 : warp;  // warp within the group: rows pw*32 .. pw*32+31
-    const int half = lane >> 4;            // which of the two rows of a load instruction
-    const int f = lane & 15;               // 16-byte piece of the row's 256-byte stage segment
-    const uint32_t piece_off = (uint32_t)(f >> 1) * A_LBO + (uint32_t)(f & 1) * 8u;
-    for (int kb = grp; kb < nkb; kb += 2) {
+  // A CTA walks the row blocks blockIdx.y, blockIdx.y + gridDim.y, ...: barriers, tensor memory and the
+  // epilogue vectors are set up once
+  for (int t = 0, mblk = blockIdx.y; mblk * BM < M; ++t, mblk += gridDim.y) {
+    const int m0 = mblk * BM;
+    if (t > 0) {
+      prefetch_rows(m0, M);
+      fix_rows(m0);
+      if (producer && grp < nkb) load_stage(grp);
+    }
+    if (producer) {
+      // ---------------------------------------------------------------- producer groups
       const int s = grp;
-      const int col = kb * BK + f * 4;
-      // issue the 16 loads of this lane (rows pw*32 + 2i + half), addresses selected up front so
-      // that nothing consumes a loaded register before all loads are in flight
-      float4 x[16];
+      const int u0 = t * (grp ? uses1 : uses0);
+      const uint32_t st_off = (uint32_t)f * A_LBO + (uint32_t)(pw * 32 + rsub) * 16u;
+      for (int kb = grp; kb < nkb; kb += 2) {
+        mbar_wait(empty(s), ((u0 + (kb >> 1)) & 1) ^ 1, g.status, 100 + s, alive);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int r = pw * 32 + 2 * i + half;
-        const float *rowp = nullptr;
-        int c = col;
-        if (col < g.a0.width) rowp = s_p0[r];
-        else if (col < g.Kd) { rowp = s_p1[r]; c = col - g.a0.width; }
-        const float4 *src = rowp ? reinterpret_cast<const float4 *>(rowp + c)
-                                 : reinterpret_cast<const float4 *>(g_zero16);
-        x[i] = *src;
+        for (int i = 0; i < 8; ++i) {
+          uint4 hi, lo;
+          split_chunk(x[2 * i], x[2 * i + 1], hi, lo);
+          st_shared_v4(sm.a_hi(s) + st_off + i * 64u, hi);
+          st_shared_v4(sm.a_lo(s) + st_off + i * 64u, lo);
+        }
+        fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async-proxy reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full(s));
+        // a thread that arrives stalls until its outstanding loads have landed, so the next stage's
+        // loads go out after the arrival
+        if (kb + 2 < nkb) load_stage(kb + 2);
       }
-      mbar_wait(empty(s), ((kb >> 1) & 1) ^ 1, g.status, 100 + s, alive);
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int r = pw * 32 + 2 * i + half;
-        uint2 hi, lo;
-        split_bf16(x[i], hi, lo);
-        const uint32_t off = piece_off + (uint32_t)(r >> 3) * A_SBO + (uint32_t)(r & 7) * 16u;
-        st_shared_v2(sm.a_hi(s) + off, hi);
-        st_shared_v2(sm.a_lo(s) + off, lo);
+    } else if (warp == 4) {
+      // ---------------------------------------------------------------- weight stages
+      if (lane == 0) {
+        const char *wsrc = reinterpret_cast<const char *>(g.w_packed) + (size_t)nt * nkb * (2 * B_BYTES);
+        for (int kb = 0; kb < nkb; ++kb) {
+          const int s = kb & 1;
+          const int u = t * (s ? uses1 : uses0) + (kb >> 1);
+          mbar_wait(empty(s), (u & 1) ^ 1, g.status, 200 + s, alive);
+          mbar_expect_tx(full(s), 2 * B_BYTES);
+          bulk_g2s(sm.b_hi(s), wsrc + (size_t)kb * (2 * B_BYTES), 2 * B_BYTES, full(s));
+        }
       }
-      fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async-proxy reads
       __syncwarp();
-      if (lane == 0) mbar_arrive(full(s));
-    }
-  } else if (warp == 4) {
-    // ------------------------------------------------------------------ weight stages
-    if (lane == 0) {
-      const char *wsrc = reinterpret_cast<const char *>(g.w_packed) + (size_t)nt * nkb * (2 * B_BYTES);
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb & 1;
-        mbar_wait(empty(s), ((kb >> 1) & 1) ^ 1, g.status, 200 + s, alive);
-        mbar_expect_tx(full(s), 2 * B_BYTES);
-        bulk_g2s(sm.b_hi(s), wsrc + (size_t)kb * (2 * B_BYTES), 2 * B_BYTES, full(s));
-      }
-    }
-  } else {
-    // ------------------------------------------------------------------ MMA issue
-    if (lane == 0) {
-      // fp32 accumulate, bf16 x bf16, both K-major, N = 176, M = 128
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-                                 ((uint32_t)(BM >> 4) << 24);
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb & 1;
-        mbar_wait(full(s), (kb >> 1) & 1, g.status, 300 + s, alive);
-        tc_fence_after();
+    } else {
+      // ---------------------------------------------------------------- MMA issue
+      if (lane == 0) {
+        // fp32 accumulate, bf16 x bf16, both K-major, N = 176, M = 128
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                   ((uint32_t)(BM >> 4) << 24);
+        for (int kb = 0; kb < nkb; ++kb) {
+          const int s = kb & 1;
+          const int u = t * (s ? uses1 : uses0) + (kb >> 1);
+          mbar_wait(full(s), u & 1, g.status, 300 + s, alive);
+          tc_fence_after();
+          if (t == 0 && kb < 20) TL(2 + kb);
 #pragma unroll
-        for (int ks = 0; ks < BK / 16; ++ks) {
-          const uint64_t ah = make_desc(sm.a_hi(s) + ks * 2 * A_LBO, A_LBO, A_SBO);
-          const uint64_t al = make_desc(sm.a_lo(s) + ks * 2 * A_LBO, A_LBO, A_SBO);
-          const uint64_t bh = make_desc(sm.b_hi(s) + ks * 2 * B_LBO, B_LBO, B_SBO);
-          const uint64_t bl = make_desc(sm.b_lo(s) + ks * 2 * B_LBO, B_LBO, B_SBO);
-          const uint32_t first = (kb > 0 || ks > 0) ? 1u : 0u;
-          mma_bf16(tmem, ah, bh, idesc, first);
-          mma_bf16(tmem + TMEM_SMALL, al, bh, idesc, first);
-          mma_bf16(tmem + TMEM_SMALL, ah, bl, idesc, 1u);
+          for (int ks = 0; ks < BK / 16; ++ks) {
+            const uint64_t ah = make_desc(sm.a_hi(s) + ks * 2 * A_LBO, A_LBO, A_SBO);
+            const uint64_t al = make_desc(sm.a_lo(s) + ks * 2 * A_LBO, A_LBO, A_SBO);
+            const uint64_t bh = make_desc(sm.b_hi(s) + ks * 2 * B_LBO, B_LBO, B_SBO);
+            const uint64_t bl = make_desc(sm.b_lo(s) + ks * 2 * B_LBO, B_LBO, B_SBO);
+            const uint32_t first = (kb > 0 || ks > 0) ? 1u : 0u;
+            mma_bf16(tmem, ah, bh, idesc, first);
+            mma_bf16(tmem + TMEM_SMALL, al, bh, idesc, first);
+            mma_bf16(tmem + TMEM_SMALL, ah, bl, idesc, 1u);
+          }
+          mma_commit(empty(s));  // the stage may be refilled once these MMAs have read it
         }
-        mma_commit(empty(s));  // the stage may be refilled once these MMAs have read it
+        mma_commit(accbar);
+        if (t == 0) TL(22);
       }
-      mma_commit(accbar);
+      __syncwarp();
     }
-  }
 
-  if (warp < 4) {
-    // ------------------------------------------------------------------ epilogue: thread = tile row
-    mbar_wait(accbar, 0, g.status, 400, alive);
+    // ------------------------------------------------------------------ epilogue
+    // Pass 1 (the eight producer warps): thread = tile row = accumulator lane; a warp may only read the
+    // lane quarter (warp % 4), so warps 0-3 take accumulator columns 0..95 and warps 6-9 columns
+    // 96..175 of their quarter.  Values (both accumulators summed) go to a row-major tile in the now
+    // idle stage ring, so that pass 2 can write whole rows with coalesced stores.
+    const int m_rows = min(BM, M - m0);
+    if (producer) {
+      mbar_wait(accbar, t & 1, g.status, 400, alive);
+      tc_fence_after();
+      if (tid == 0 && t == 0) TL(23);
+      const int quarter = warp & 3;
+      const int row = quarter * 32 + lane;
+      const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
+      float *trow_s = tile + row * TILE_LD;
+      float dot = 0.f;
+      const int ch0 = grp ? 6 : 0, ch1 = grp ? BN / 16 : 6;
+      for (int ch = ch0; ch < ch1; ++ch) {
+        float v[16];
+        tmem_ld16_sum(trow + ch * 16, v);
+        if (EPI == EPI_SCORE) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int c = ch * 16 + i;
+            if (c < D) dot += fmaxf(v[i] + s_bias[c], 0.f) * s_v1[c];
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<float4 *>(trow_s + ch * 16 + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+        }
+      }
+      if (EPI == EPI_SCORE) s_dot[grp][row] = dot;
+    }
+    if (tid == 0 && t == 0) TL(24);
+    tc_fence_before();
+    __syncthreads();
     tc_fence_after();
-    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
-    const int m = m0 + tid;
-    const bool live = m < M;
-    const int c0 = nt * BN;
-    float v[16];
-    if (EPI == EPI_BIAS) {
-      for (int ch = 0; ch < BN / 16; ++ch) {
-        tmem_ld16_sum(trow + ch * 16, v);
-        if (live) {
-          float *o = g.out + (size_t)m * g.out_ld + c0 + ch * 16;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float4 b = *reinterpret_cast<const float4 *>(&s_bias[ch * 16 + q * 4]);
-            *reinterpret_cast<float4 *>(o + q * 4) =
-                make_float4(v[q * 4] + b.x, v[q * 4 + 1] + b.y, v[q * 4 + 2] + b.z, v[q * 4 + 3] + b.w);
-          }
-        }
-      }
-    } else if (EPI == EPI_HIDDEN) {
-      const float rvf = (live && (g.row_valid == nullptr || g.row_valid[m] != 0)) ? 1.f : 0.f;
-      for (int ch = 0; ch < BN / 16; ++ch) {
-        tmem_ld16_sum(trow + ch * 16, v);
-        if (live) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int c = ch * 16 + q * 4;
-            if (c < D) {
-              const float4 b = *reinterpret_cast<const float4 *>(&s_bias[c]);
-              const float4 b2 = *reinterpret_cast<const float4 *>(&s_v1[c]);
-              *reinterpret_cast<float4 *>(g.out + (size_t)m * D + c) =
-                  make_float4(fmaxf(v[q * 4] + b.x + rvf * b2.x, 0.f), fmaxf(v[q * 4 + 1] + b.y + rvf * b2.y, 0.f),
-                              fmaxf(v[q * 4 + 2] + b.z + rvf * b2.z, 0.f), fmaxf(v[q * 4 + 3] + b.w + rvf * b2.w, 0.f));
-            }
-          }
-        }
-      }
-    } else if (EPI == EPI_LAYERNORM) {
-      // one pass over the accumulator for both moments (the row is O(1) after the merger, so
-      // E[y^2] - mean^2 loses nothing that matters at the 1e-5 epsilon)
-      float sum = 0.f, sumsq = 0.f;
-      for (int ch = 0; ch < BN / 16; ++ch) {
-        tmem_ld16_sum(trow + ch * 16, v);
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-          if (ch * 16 + i < D) {
-            const float y = v[i] + s_bias[ch * 16 + i];
-            sum += y;
-            sumsq = fmaf(y, y, sumsq);
-          }
-      }
-      const float mean = sum * (1.f / D);
-      const float sq = fmaxf(sumsq - sum * mean, 0.f);
-      const float inv = 1.f / sqrtf(sq * (1.f / D) + 1e-5f);
-      const bool push = live && g.push_table != nullptr && g.push_win[m] != 0;
-      float *prow = push ? g.push_table + (size_t)g.push_ids[m] * D : nullptr;
-      for (int ch = 0; ch < BN / 16; ++ch) {
-        tmem_ld16_sum(trow + ch * 16, v);
-        if (live) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int c = ch * 16 + q * 4;
-            if (c < D) {
-              const float4 b = *reinterpret_cast<const float4 *>(&s_bias[c]);
-              const float4 w = *reinterpret_cast<const float4 *>(&s_v1[c]);
-              const float4 lb = *reinterpret_cast<const float4 *>(&s_v2[c]);
-              const float4 o = make_float4((v[q * 4] + b.x - mean) * inv * w.x + lb.x,
-                                           (v[q * 4 + 1] + b.y - mean) * inv * w.y + lb.y,
-                                           (v[q * 4 + 2] + b.z - mean) * inv * w.z + lb.z,
-                                           (v[q * 4 + 3] + b.w - mean) * inv * w.w + lb.w);
-              *reinterpret_cast<float4 *>(g.out + (size_t)m * D + c) = o;
-              if (push) *reinterpret_cast<float4 *>(prow + c) = o;
-            }
-          }
-        }
-      }
-    } else if (EPI == EPI_GRU) {
-      const float *hrow = live ? g.memory + (size_t)g.nodes[m] * D : nullptr;
-      for (int ch = 0; ch < BN / 16; ++ch) {
-        tmem_ld16_sum(trow + ch * 16, v);
-        if (live) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int u = nt * (BN / 4) + ch * 4 + q;  // GRU unit of these four gate columns
-            if (u < D) {
-              const float4 b = *reinterpret_cast<const float4 *>(&s_bias[ch * 16 + q * 4]);
-              const float r = 1.f / (1.f + expf(-(v[q * 4] + b.x)));
-              const float z = 1.f / (1.f + expf(-(v[q * 4 + 1] + b.y)));
-              const float nn = tanhf((v[q * 4 + 2] + b.z) + r * (v[q * 4 + 3] + b.w));
-              g.out[(size_t)m * D + u] = (1.f - z) * nn + z * hrow[u];
-            }
-          }
-        }
-      }
-    } else {  // EPI_SCORE
-      float part = 0.f;
-      for (int ch = 0; ch < BN / 16; ++ch) {
-        tmem_ld16_sum(trow + ch * 16, v);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int c = ch * 16 + i;
-          if (c < D) part += fmaxf(v[i] + s_bias[c], 0.f) * s_v1[c];
-        }
-      }
-      if (live) g.out[m] = 1.f / (1.f + expf(-(part + g.b2)));
-    }
+    tile_output<EPI>(g, tile, s_bias, s_v1, s_v2, &s_dot[0][0], m0, m_rows, nt, warp, lane, meta_a, meta_b);
+    if (tid == 0 && t == 0) TL(25);
+    // the tile lives in the stage ring: the next row block's bulk copies and stores may only land
+    // once every warp has read it
+    fence_async_smem();
+    __syncthreads();
   }
-
-  tc_fence_before();
-  __syncthreads();
   if (warp == 5) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
@@ -450,7 +594,9 @@ int launch(int epilogue, const Args &a, int n_tiles, cudaStream_t stream) {
     ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_SCORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     configured_device = dev;
   }
-  dim3 grid(n_tiles, ceil_div(a.m_cap, BM));
+  // one wave: a CTA walks several row blocks when there are more tiles than SMs; CTAs past the live row
+  // count (m_cap is a capacity) leave at once
+  dim3 grid(n_tiles, std::min(ceil_div(a.m_cap, BM), std::max(1, 148 / n_tiles)));
   switch (epilogue) {
     case EPI_BIAS: tc_gemm_kernel<EPI_BIAS><<<grid, THREADS, SMEM_BYTES, stream>>>(a); break;
     case EPI_HIDDEN: tc_gemm_kernel<EPI_HIDDEN><<<grid, THREADS, SMEM_BYTES, stream>>>(a); break;
@@ -466,3 +612,15 @@ int launch(int epilogue, const Args &a, int n_tiles, cudaStream_t stream) {
 
 }  // namespace tc
 }  // namespace orca
+
+#ifdef ORCA_TC_TIMELINE
+extern "C" int orca_tc_timeline_read(long long *h_out, int n_ctas) {
+  if (n_ctas > 8192) n_ctas = 8192;
+  return (int)cudaMemcpyFromSymbol(h_out, orca::tc::g_tl, sizeof(long long) * 32 * n_ctas);
+}
+extern "C" int orca_tc_timeline_clear() {
+  void *p = nullptr;
+  cudaGetSymbolAddress(&p, orca::tc::g_tl);
+  return (int)cudaMemset(p, 0, sizeof(orca::tc::g_tl));
+}
+#endif

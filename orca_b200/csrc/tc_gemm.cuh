@@ -22,6 +22,8 @@ constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;   // A head, A tail, W he
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int TMEM_COLS = 512;   // main accumulator at column 0, cross-term accumulator at column 256
 constexpr int TMEM_SMALL = 256;
+constexpr int TILE_LD = 180;     // floats per row of the epilogue's output tile: 16-byte row-wise stores of a
+                                 // warp (one row per lane) then spread over all banks
 
 // A logical A row is the concatenation of up to two gathered table rows
 struct RowSrc {
@@ -52,7 +54,10 @@ struct Args {
   const float *ln_w, *ln_b;
   float *push_table;
   const int32_t *push_ids;
-  const uint8_t *push_win;
+  const uint8_t *push_win;                  // winners by flag, or (push_win == nullptr) by record:
+  const unsigned long long *push_last_pos;  // row m wins if m >= push_all_from or
+  long long push_base;                      // push_last_pos[push_ids[m]] == push_base + m
+  int push_all_from;
   // GRU
   const float *memory;
   const int32_t *nodes;
@@ -66,4 +71,12 @@ struct Args {
 int launch(int epilogue, const Args &a, int n_tiles, cudaStream_t stream);
 
 }  // namespace tc
+
+// out-projection + merger + LayerNorm of an attention layer with the optional history push; see gemm.cu
+int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uint8_t *d_valid, const float *d_feat,
+                     const int32_t *d_idx, int32_t n_rows_cap, const int32_t *d_n_rows, float *d_out,
+                     float *d_push_table, const int32_t *d_push_ids, const uint8_t *d_push_win,
+                     const int64_t *d_last_pos, long long base, int all_from, float *d_scratch_hidden,
+                     cudaStream_t stream);
+
 }  // namespace orca

@@ -194,7 +194,9 @@ class TGN(nn.Module):
         self._stage_dev = None
         self._status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._last_pos = torch.zeros(self.n_nodes, dtype=torch.int64, device=self.device)
-        self._cand_bitmap = torch.zeros((self.n_nodes + 31) // 32, dtype=torch.int32, device=self.device)
+        # candidate bitmap of the uncached set, followed by the candidate list (length word + entries)
+        self._cand_bitmap = torch.zeros((self.n_nodes + 31) // 32 + 1 + _lib.CAND_CAP, dtype=torch.int32,
+                                        device=self.device)
         self._epoch = np.ones(1, dtype=np.int64)
         self._dummy_prev = np.full(1, -1, dtype=np.int32)
         self.last_counts = None

@@ -134,6 +134,40 @@ def test_eval_matches_oracle_on_fresh_inputs():
     assert np.array_equal(tgn.embedding_module.histories[0].cache_flag != 0, orc.cache_flag[0] != 0)
 
 
+def test_large_uncached_sets_take_the_bitmap_path():
+    """Batches whose uncached set exceeds the candidate list (ORCA_CAND_CAP) fall back to the bitmap
+    scan; both finishes must give the oracle's rows (counts, scores, pushed history rows)."""
+    import dataclasses
+    from orca_b200 import _lib, params, synthetic
+    from oracle import tgn_oracle
+    spec = dataclasses.replace(synthetic.SPECS["t_nb2"], name="wide", n_src=30000, n_edges=24000, budget=40, bs=1500,
+                               zipf_src=0.3, zipf_dst=0.3)
+    g = synthetic.make_graph(spec, seed=3)
+    adj = tgn_oracle.Adjacency(g.sources, g.destinations, g.edge_idxs, g.timestamps, g.n_nodes)
+    sd = params.random_state_dict(2, seed=4)
+    orc = tgn_oracle.OracleTGN(adj, g.edge_features, sd, g.n_nodes, n_layers=2, budget=spec.budget)
+    tgn = make_model(g)
+    t = {k: torch.from_numpy(v) for k, v in sd.items()}
+    t["embedding_module.time_encoder.w.weight"] = t["time_encoder.w.weight"]
+    t["embedding_module.time_encoder.w.bias"] = t["time_encoder.w.bias"]
+    tgn.load_state_dict(t)
+    neg = synthetic.negative_destinations(g, seed=6)
+    worst, sizes = 0.0, []
+    for b, src, dst, ts, eidx in batches(g, 8):
+        ng = neg[b * spec.bs: b * spec.bs + len(src)]
+        pl = np.zeros(0, dtype=np.int64)     # empty plan: nothing stays cached
+        rec = []
+        wp, wq = orc.compute_edge_probabilities(src, dst, ng, ts, eidx, spec.n_degree, pl, record=rec)
+        p, q = tgn.compute_edge_probabilities(src, dst, ng, ts, eidx, spec.n_degree, True, False, pl)
+        n1, _, _ = tgn.check_status()
+        assert n1 == 3 * len(src) + len(rec[0]), f"batch {b}"
+        sizes.append(len(rec[0]))
+        worst = max(worst, max_rel(p.cpu().numpy(), wp.numpy()), max_rel(q.cpu().numpy(), wq.numpy()))
+    assert min(sizes[1:]) < _lib.CAND_CAP < max(sizes), sizes     # both finishes were exercised
+    assert worst < 1e-3, worst
+    assert max_rel(tgn.embedding_module.histories[0].emb.cpu().numpy(), orc.hist[0].numpy(), floor=0.05) < 1e-3
+
+
 @pytest.mark.parametrize("case,reuse", [("t_nb2_reuse0", True), ("t_nb2_noreuse", False)])
 def test_other_recursions_match_reference_fixture(case, reuse):
     """compute_embedding_reuse (budget == 0) and compute_embedding (reuse=False) of the reference,
