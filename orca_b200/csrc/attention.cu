@@ -72,6 +72,19 @@ constexpr int GA_TE_LD = 172;                   // floats per parked time encodi
 constexpr int GA_PART_LD = 33;                  // 32 partial sums + 1 pad (conflict-free column reads)
 __host__ __device__ constexpr int ga_warp_floats(int k) { return k * GA_TE_LD + 2 * k * GA_PART_LD; }
 
+// Time encodings of one slot for this lane's columns lane, lane+32, ...: the first NL column groups
+// hold large arguments (fixed-point reduction), the others small ones (fp32 reduction).  w decreases
+// with the column, so "large" groups are always a prefix; NL is uniform over the warp and the body is
+// branch free, which lets the six cosines of a lane overlap.
+template <int NL>
+__device__ __forceinline__ void time_terms(float dt, const float (&wt)[6], float (&te)[6]) {
+#pragma unroll
+  for (int i = 0; i < 6; ++i) {
+    const float x = dt * wt[i];
+    te[i] = i < NL ? cos_fixed(x) : cos_small(x);
+  }
+}
+
 __global__ void __launch_bounds__(GA_THREADS, 2)
 attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_table,
                    const float *__restrict__ edge_table, const float *__restrict__ time_w,
@@ -88,6 +101,10 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
   float wt[GA_T_ITERS];
 #pragma unroll
   for (int i = 0; i < GA_T_ITERS; ++i) wt[i] = (lane + 32 * i < D) ? __ldg(time_w + lane + 32 * i) : 0.f;
+  // the largest frequency of each column group (columns 32 i .. 32 i + 31)
+  float wg[GA_T_ITERS];
+#pragma unroll
+  for (int i = 0; i < GA_T_ITERS; ++i) wg[i] = __ldg(time_w + 32 * i);
   const bool third = lane + 64 < GA_MEM_F4;       // lanes 0..21 own a third 16-byte piece
   unsigned long long prof_rows = 0, prof_slots = 0;
   (void)status;
@@ -151,13 +168,32 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
       if (todo) load_slot(__ffs(todo) - 1, xn);   // request the next slot before working on this one
       const float dt = __shfl_sync(0xffffffffu, my_dt, j);
       float s0 = 0.f, s1 = 0.f;
+      {
+        float te[GA_T_ITERS];
+        const float adt = fabsf(dt);
+        int nl = 0;
 #pragma unroll
-      for (int i = 0; i < GA_T_ITERS; ++i) {
-        if (lane + 32 * i < D) {
-          const float te = cos_any(dt * wt[i]);
-          s_te[it * GA_TE_LD + lane + 32 * i] = te;
-          s0 = fmaf(te, qta[i], s0);
-          s1 = fmaf(te, qtb[i], s1);
+        for (int i = 0; i < GA_T_ITERS; ++i) nl += adt * wg[i] >= 32768.f ? 1 : 0;
+        if (!(adt * wg[0] < 1073741824.f)) nl = -1;   // beyond the fixed-point range (or not finite)
+        switch (nl) {
+          case 0: time_terms<0>(dt, wt, te); break;
+          case 1: time_terms<1>(dt, wt, te); break;
+          case 2: time_terms<2>(dt, wt, te); break;
+          case 3: time_terms<3>(dt, wt, te); break;
+          case 4: time_terms<4>(dt, wt, te); break;
+          case 5: time_terms<5>(dt, wt, te); break;
+          case 6: time_terms<6>(dt, wt, te); break;
+          default:
+#pragma unroll
+            for (int i = 0; i < GA_T_ITERS; ++i) te[i] = cos_any(dt * wt[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < GA_T_ITERS; ++i) {
+          if (lane + 32 * i < D) {
+            s_te[it * GA_TE_LD + lane + 32 * i] = te[i];
+            s0 = fmaf(te[i], qta[i], s0);
+            s1 = fmaf(te[i], qtb[i], s1);
+          }
         }
       }
 #pragma unroll

@@ -63,19 +63,48 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-// cos(x) for an fp32 argument of any magnitude up to 1e9, accurate to about 5e-7 absolute.
-// The arguments here are delta * w with delta up to 3e8 seconds and w down from 1, so most of them
-// are far outside the range where cosf() stays on its fast path, and its slow path (Payne-Hanek)
-// costs a hundred instructions.  Here the argument is reduced in double precision --
-// r = x - round(x / 2pi) * 2pi with 2pi in two doubles, exact enough for |x| < 1e9 -- and the
-// hardware cosine approximation is applied to r in [-pi, pi], where its absolute error is 2^-21.
+// cos(x) for an fp32 argument of any magnitude, accurate to about 1e-6 absolute.
+// The arguments here are delta * w with delta up to 3e8 seconds and w down from 1, so many of them are
+// far outside the range where cosf() stays on its fast path, and its slow path (Payne-Hanek) costs a
+// hundred instructions; double-precision reduction is no way out either (the fp64 and conversion
+// pipes of this GPU made a warp-wide cosine cost ~160 cycles).  fp32 and integer pipes only:
+//   |x| < 2^15   Cody-Waite: k = rint(x / 2pi) (< 2^13), r = x - k*C1 - k*C2 - k*C3 with 2pi split so that
+//                k*C1 and k*C2 are exact (C1 8 bits, C2 11 bits); reduction error 1e-7;
+//   |x| < 2^30   fixed point: x = m * 2^e with a 24-bit m; the fraction of x / 2pi is the low part of
+//                m * F (F = 2^64 / 2pi) shifted by e, of which the top 32 bits are kept (96-bit product
+//                from two 32 x 32 multiplies); cos is even, so |fraction| (24 bits) goes back to a
+//                float through the 2^23 exponent trick; reduction error 4e-7;
+//   else         cosf().
+// The hardware cosine approximation is applied to the reduced argument in [-pi, pi] (2^-21 absolute).
+// |x| < 2^15, branch free
+__device__ __forceinline__ float cos_small(float x) {
+  const float ax = fabsf(x);
+  const float k = rintf(ax * 0.15915494309189535f);
+  float r = fmaf(-k, 6.28125f, ax);
+  r = fmaf(-k, 0.0019350051879882812f, r);
+  r = fmaf(-k, 3.019916050561733e-07f, r);
+  return __cosf(r);
+}
+// 2^-8 <= |x| < 2^30, branch free
+__device__ __forceinline__ float cos_fixed(float x) {
+  const uint32_t bits = __float_as_uint(fabsf(x));
+  const int e = (int)(bits >> 23) - 150;           // |x| = m * 2^e, e in [-31, 6]
+  const uint32_t m = (bits & 0x7fffffu) | 0x800000u;
+  const unsigned long long a = (unsigned long long)m * 0x9391054aull;   // m * low word of F
+  const unsigned long long mid = (a >> 32) + (unsigned long long)m * 0x28be60dbull;
+  const uint32_t w0 = (uint32_t)a, w1 = (uint32_t)mid, w2 = (uint32_t)(mid >> 32);
+  // top 32 bits of frac(m * F * 2^e / 2^64)
+  const uint32_t top = e >= 0 ? __funnelshift_l(w0, w1, e) : __funnelshift_r(w1, w2, -e);
+  const int t = (int)top;                          // turns in [-1/2, 1/2) scaled by 2^32
+  const uint32_t u = min((uint32_t)(t < 0 ? -t : t) >> 8, 0x7fffffu);
+  const float f = __uint_as_float(0x4b000000u | u) - 8388608.f;   // (float)u, exact
+  return __cosf(f * 3.7450702829239286e-07f);      // 2pi / 2^24
+}
 __device__ __forceinline__ float cos_any(float x) {
-  if (!(fabsf(x) < 1.0e9f)) return cosf(x);
-  const double xd = (double)x;
-  const double k = rint(xd * 0.15915494309189533577);          // 1 / 2pi
-  double r = fma(-k, 6.28318530717958623200e+00, xd);          // 2pi, high part
-  r = fma(-k, 2.44929359829470641435e-16, r);                  // 2pi, low part
-  return __cosf((float)r);
+  const float ax = fabsf(x);
+  if (ax < 32768.f) return cos_small(x);
+  if (ax < 1073741824.f) return cos_fixed(x);
+  return cosf(x);
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
