@@ -380,6 +380,13 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
  * auxiliary stream and two events are created once per device on first use.  Off while tracing. */
 int orca_set_overlap(int32_t enable);
 
+/* With dependent launch on (default) the library's kernels are enqueued with programmatic stream
+ * serialisation: a kernel's blocks may be scheduled and run their set-up while the kernel before it
+ * in the stream drains, and wait (griddepcontrol.wait) before touching anything it produced.  Results
+ * are identical either way; off restores plain stream-ordered launches (no counterpart in the
+ * reference). */
+int orca_set_dependent_launch(int32_t enable);
+
 /* Phase tracing of orca_tgn_eval_batch (the reference only has wall-clock deltas around whole
  * epochs, train.py:189-341): while enabled, CUDA events are recorded at the phase boundaries of every
  * batch; orca_trace_read synchronises on them, returns the summed milliseconds per phase

@@ -47,6 +47,31 @@ int set_error(int code, const char *fmt, ...);
 int &launch_counter();
 #define ORCA_COUNT_LAUNCH() (++orca::launch_counter())
 
+// Programmatic dependent launch: a kernel launched through launch_dep() may begin (block scheduling,
+// set-up that touches nothing an earlier kernel wrote) while its predecessor in the stream is still
+// draining.  EVERY such kernel calls dep_wait() before its first access to memory another kernel
+// produced -- and before returning, even when it has nothing to do, so that completion stays
+// transitive along the stream -- and dep_trigger() as early as it likes.  Both are no-ops in a kernel
+// that was launched the plain way.
+__device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+bool &dependent_launch_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ int rows_of(int cap, const int32_t *d_n) {
   if (d_n == nullptr) return cap;
   int n = *d_n;

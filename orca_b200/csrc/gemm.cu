@@ -356,6 +356,8 @@ __global__ void __launch_bounds__(F2_THREADS) score_kernel(ScoreArgs g) {
 __global__ void gru_scatter_kernel(const float *__restrict__ hnew, orca_memory_t mem,
                                    const int32_t *__restrict__ nodes, int n_cap, const int32_t *d_n,
                                    int clear_flags) {
+  dep_trigger();
+  dep_wait();
   const int n = rows_of(n_cap, d_n);
   const int row = blockIdx.x * (blockDim.x / 64) + threadIdx.x / 64;
   if (row >= n) return;
@@ -372,6 +374,8 @@ __global__ void gru_scatter_kernel(const float *__restrict__ hnew, orca_memory_t
 
 __global__ void gru_clear_kernel(orca_memory_t mem, const int32_t *__restrict__ nodes, int n_cap,
                                  const int32_t *d_n) {
+  dep_trigger();
+  dep_wait();
   const int n = rows_of(n_cap, d_n);
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
     mem.msg_flag[nodes[i]] = 0;
@@ -626,10 +630,11 @@ int orca_gru_update(const orca_gru_weights_t *w, const orca_memory_t *mem, const
     f1_gemm_kernel<EPI_GRU><<<grid, F1_THREADS, 0, s>>>(g);
     ORCA_COUNT_LAUNCH();
   }
-  gru_scatter_kernel<<<ceil_div(n_cap, 4), 256, 0, s>>>(d_scratch_h, *mem, d_nodes, n_cap, d_n, clear_flags);
+  ORCA_CUDA(launch_dep(gru_scatter_kernel, ceil_div(n_cap, 4), 256, 0, s, d_scratch_h, *mem, d_nodes, n_cap, d_n,
+                       (int)clear_flags));
   ORCA_COUNT_LAUNCH();
   if (clear_flags) {
-    gru_clear_kernel<<<std::min(ceil_div(n_cap, 256), 1024), 256, 0, s>>>(*mem, d_nodes, n_cap, d_n);
+    ORCA_CUDA(launch_dep(gru_clear_kernel, std::min(ceil_div(n_cap, 256), 1024), 256, 0, s, *mem, d_nodes, n_cap, d_n));
     ORCA_COUNT_LAUNCH();
   }
   ORCA_LAUNCH_CHECK();

@@ -91,6 +91,8 @@ __global__ void copy_i32_kernel(const int32_t *__restrict__ src, int32_t *__rest
 __global__ void __launch_bounds__(1024)
 plan_flags_kernel(uint8_t *__restrict__ flag, int64_t n_nodes, int32_t *__restrict__ prev_plan, int n_prev,
                   const int32_t *__restrict__ plan, int n_plan) {
+  dep_trigger();
+  dep_wait();
   // eight independent loads per thread in flight: the loop is a chain of L2 round trips otherwise
   for (int i0 = threadIdx.x; i0 < n_prev; i0 += 8 * 1024) {
     int v[8];
@@ -183,6 +185,7 @@ __global__ void expand_rows_kernel(const int32_t *__restrict__ nbr2, int n, int 
 }
 
 __global__ void publish_counts_kernel(const int32_t *n1, const int32_t *n_win, int32_t *status) {
+  dep_wait();
   status[1] = *n1;
   status[2] = *n_win;
 }
@@ -384,8 +387,8 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     } else if (d_plan != nullptr) {
       const bool know_prev = *m->n_prev_plan >= 0;
       if (!know_prev) ORCA_CUDA(cudaMemsetAsync(m->cache_flag, 0, (size_t)m->n_nodes, fs));
-      plan_flags_kernel<<<1, 1024, 0, fs>>>(m->cache_flag, m->n_nodes, m->prev_plan, know_prev ? *m->n_prev_plan : 0,
-                                            d_plan, n_plan);
+      ORCA_CUDA(launch_dep(plan_flags_kernel, 1, 1024, 0, fs, m->cache_flag, m->n_nodes, m->prev_plan,
+                           know_prev ? (int)*m->n_prev_plan : 0, d_plan, (int)n_plan));
       ORCA_COUNT_LAUNCH();
       ORCA_LAUNCH_CHECK();
       *m->n_prev_plan = n_plan;
@@ -540,6 +543,11 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   g_last_batch_launches = launch_counter();
+  return ORCA_OK;
+}
+
+int orca_set_dependent_launch(int32_t enable) {
+  dependent_launch_enabled() = enable != 0;
   return ORCA_OK;
 }
 

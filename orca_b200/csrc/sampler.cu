@@ -22,6 +22,10 @@ int &launch_counter() {
   static thread_local int c = 0;
   return c;
 }
+bool &dependent_launch_enabled() {
+  static bool on = true;
+  return on;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Sampling.  A group of G lanes (16 when k <= 16, else 32) serves one query.  The lower bound of
@@ -115,6 +119,8 @@ sample_topk_kernel(const int64_t *__restrict__ indptr, const int32_t *__restrict
                    int n_cap, const int32_t *__restrict__ d_n, int k, int32_t *__restrict__ o_nbr,
                    int32_t *__restrict__ o_eid, float *__restrict__ o_et, float *__restrict__ o_dt,
                    int32_t *status, const uint8_t *__restrict__ cache_flag, uint32_t *__restrict__ cand_bitmap) {
+  dep_trigger();
+  dep_wait();
   const int n = rows_of(n_cap, d_n);
   const int groups_per_block = blockDim.x / G;
   const int lane = threadIdx.x % G;
@@ -139,6 +145,8 @@ batch_head_kernel(const int64_t *__restrict__ indptr, const int32_t *__restrict_
                   const uint8_t *__restrict__ cache_flag, uint32_t *__restrict__ cand_bitmap,
                   int32_t *__restrict__ cand_count, int32_t *__restrict__ cand_list,
                   unsigned long long *__restrict__ last_pos, long long base) {
+  dep_trigger();
+  dep_wait();
   const int n = 3 * b;
   const int groups_per_block = blockDim.x / G;
   const int lane = threadIdx.x % G;
@@ -410,6 +418,8 @@ uncached_finish_kernel(uint32_t *__restrict__ gbm, int32_t *__restrict__ cand_co
   __shared__ double s_tmax2[FU_THREADS / 32];
   __shared__ int s_kept;
   const int tid = threadIdx.x;
+  dep_trigger();
+  dep_wait();
   const int nc = *cand_count;
   if (nc > ORCA_CAND_CAP) {
     const int u = finish_from_bitmap(gbm, s_bitmap, n_query, n_nodes, nodes_io, ts_io, u_cap, d_n_total, status);
@@ -545,6 +555,8 @@ last_occ_compact_kernel(const int32_t *__restrict__ ids, int n, int64_t n_nodes,
   __shared__ int s_scan[32];
   __shared__ int s_base;
   const int tid = threadIdx.x;
+  dep_trigger();
+  dep_wait();
   if (tid == 0) s_base = 0;
   // four positions per thread and sweep, loaded up front so that their round trips overlap
   constexpr int U = 4;
@@ -618,14 +630,14 @@ int launch_batch_head(const orca_tgn_t *m, const int32_t *d_batch, const double 
   unsigned long long *lp = reinterpret_cast<unsigned long long *>(m->last_pos);
   if (k <= 16) {
     const int grid = std::min(ceil_div(n, threads / 16), 148 * 16);
-    batch_head_kernel<16><<<grid, threads, 0, s>>>(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, d_batch,
-                                                   d_bts, b, k, nodes1, ts1, cat_dst, o_nbr, o_eid, o_dt, status,
-                                                   m->cache_flag, m->cand_bitmap, cand_count, cand_list, lp, base);
+    ORCA_CUDA(launch_dep(batch_head_kernel<16>, grid, threads, 0, s, m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts,
+                         m->n_nodes, d_batch, d_bts, b, k, nodes1, ts1, cat_dst, o_nbr, o_eid, o_dt, status,
+                         m->cache_flag, m->cand_bitmap, cand_count, cand_list, lp, base));
   } else {
     const int grid = std::min(ceil_div(n, threads / 32), 148 * 16);
-    batch_head_kernel<32><<<grid, threads, 0, s>>>(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, d_batch,
-                                                   d_bts, b, k, nodes1, ts1, cat_dst, o_nbr, o_eid, o_dt, status,
-                                                   m->cache_flag, m->cand_bitmap, cand_count, cand_list, lp, base);
+    ORCA_CUDA(launch_dep(batch_head_kernel<32>, grid, threads, 0, s, m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts,
+                         m->n_nodes, d_batch, d_bts, b, k, nodes1, ts1, cat_dst, o_nbr, o_eid, o_dt, status,
+                         m->cache_flag, m->cand_bitmap, cand_count, cand_list, lp, base));
   }
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
@@ -646,10 +658,9 @@ int launch_uncached_finish(const orca_tgn_t *m, int n_query, int32_t *nodes_io, 
     configured_device = dev;
   }
   int32_t *cand_count = reinterpret_cast<int32_t *>(m->cand_bitmap + words);
-  uncached_finish_kernel<<<1, FU_THREADS, smem, s>>>(m->cand_bitmap, cand_count, cand_count + 1, n_query, m->n_nodes,
-                                                     nodes_io, ts_io, u_cap, d_n_total, d_n_unc, status,
-                                                     reinterpret_cast<const unsigned long long *>(m->last_pos),
-                                                     (unsigned long long)base);
+  ORCA_CUDA(launch_dep(uncached_finish_kernel, 1, FU_THREADS, smem, s, m->cand_bitmap, cand_count, cand_count + 1,
+                       n_query, m->n_nodes, nodes_io, ts_io, u_cap, d_n_total, d_n_unc, status,
+                       reinterpret_cast<const unsigned long long *>(m->last_pos), (unsigned long long)base));
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;
@@ -657,8 +668,8 @@ int launch_uncached_finish(const orca_tgn_t *m, int n_query, int32_t *nodes_io, 
 
 int launch_last_occ_compact(const int32_t *d_ids, int n, int64_t n_nodes, int64_t *d_last_pos, long long base,
                             int32_t *d_compact, int32_t *d_n_compact, cudaStream_t s) {
-  last_occ_compact_kernel<<<1, 1024, 0, s>>>(d_ids, n, n_nodes, reinterpret_cast<unsigned long long *>(d_last_pos),
-                                             base, d_compact, d_n_compact);
+  ORCA_CUDA(launch_dep(last_occ_compact_kernel, 1, 1024, 0, s, d_ids, n, n_nodes,
+                       reinterpret_cast<unsigned long long *>(d_last_pos), base, d_compact, d_n_compact));
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;
@@ -730,17 +741,15 @@ static int orca_sample_topk_impl(const int64_t *d_indptr, const int32_t *d_adj_n
     const int per = threads / 16;
     // (a launch whose row count lives on the device usually covers far fewer rows than its capacity)
     const int grid = std::min(ceil_div(n_query_cap, per), d_n_query ? 148 * 2 : 148 * 16);
-    sample_topk_kernel<16><<<grid, threads, 0, s>>>(d_indptr, d_adj_nbr, d_adj_eid, d_adj_ts, n_nodes,
-                                                    d_nodes, d_ts, n_query_cap, d_n_query, k, d_nbr,
-                                                    d_eid, d_edge_times, d_delta, d_status, d_cache_flag,
-                                                    d_cand_bitmap);
+    ORCA_CUDA(launch_dep(sample_topk_kernel<16>, grid, threads, 0, s, d_indptr, d_adj_nbr, d_adj_eid, d_adj_ts, n_nodes,
+                         d_nodes, d_ts, n_query_cap, d_n_query, k, d_nbr, d_eid, d_edge_times, d_delta, d_status,
+                         d_cache_flag, d_cand_bitmap));
   } else {
     const int per = threads / 32;
     const int grid = std::min(ceil_div(n_query_cap, per), 148 * 16);
-    sample_topk_kernel<32><<<grid, threads, 0, s>>>(d_indptr, d_adj_nbr, d_adj_eid, d_adj_ts, n_nodes,
-                                                    d_nodes, d_ts, n_query_cap, d_n_query, k, d_nbr,
-                                                    d_eid, d_edge_times, d_delta, d_status, d_cache_flag,
-                                                    d_cand_bitmap);
+    ORCA_CUDA(launch_dep(sample_topk_kernel<32>, grid, threads, 0, s, d_indptr, d_adj_nbr, d_adj_eid, d_adj_ts, n_nodes,
+                         d_nodes, d_ts, n_query_cap, d_n_query, k, d_nbr, d_eid, d_edge_times, d_delta, d_status,
+                         d_cache_flag, d_cand_bitmap));
   }
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();

@@ -46,6 +46,8 @@ message_store_kernel(orca_memory_t mem, const float *__restrict__ edge_table, co
                      const double *__restrict__ ts, const int32_t *__restrict__ eidx, int b,
                      const int32_t *__restrict__ win_pos, int n_cap, const int32_t *d_n,
                      int32_t *__restrict__ win_nodes) {
+  dep_trigger();
+  dep_wait();
   const int n = rows_of(n_cap, d_n);
   const int w = blockIdx.x;
   if (w >= n) return;
@@ -125,9 +127,8 @@ int orca_message_store(const orca_memory_t *mem, const float *d_edge_table, cons
   ORCA_CHECK_ARG(d_edge_table && d_time_w && d_cat_src && d_cat_dst && d_ts && d_eidx && d_win_pos);
   ORCA_CHECK_ARG(b >= 0 && n_win_cap >= 0);
   if (n_win_cap == 0 || b == 0) return ORCA_OK;
-  message_store_kernel<<<n_win_cap, 256, 0, (cudaStream_t)stream>>>(*mem, d_edge_table, d_time_w, d_cat_src,
-                                                                    d_cat_dst, d_ts, d_eidx, b, d_win_pos,
-                                                                    n_win_cap, d_n_win, d_win_nodes);
+  ORCA_CUDA(launch_dep(message_store_kernel, n_win_cap, 256, 0, (cudaStream_t)stream, *mem, d_edge_table, d_time_w,
+                       d_cat_src, d_cat_dst, d_ts, d_eidx, b, d_win_pos, n_win_cap, d_n_win, d_win_nodes));
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;

@@ -330,6 +330,8 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   const int w0 = g.a0.width, w1 = g.a1.width, Kd = g.Kd;
   const int nkb = g.n_kblocks;
 
+  dep_trigger();
+  int M = 0;   // live rows (known after the wait below)
   // Loads that head a dependency chain go out first, before anything waits: the table row of tile
   // row (pw*32 + lane) for the producers, and the per-row inputs of the output pass (warp w writes
   // rows w, w+10, ...; lane i holds what row w + 10*i needs).  For the CTA's first tile they are
@@ -360,21 +362,6 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
       if (EPI == EPI_GRU) meta_b = g.nodes[m];
     }
   };
-  prefetch_rows(blockIdx.y * BM, g.m_cap);
-  const int M = rows_of(g.m_cap, g.d_m);
-  if ((int)blockIdx.y * BM >= M) return;  // nothing allocated yet
-  if (tid == 0) {
-    TL(0);
-#ifdef ORCA_TC_TIMELINE
-    unsigned long long gt_;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_));
-    const int tb_ = min(blockIdx.y * gridDim.x + blockIdx.x, 1599) + EPI * 1600;
-    g_tl[tb_][28] = (long long)gt_;
-    unsigned smid_;
-    asm volatile("mov.u32 %0, %smid;" : "=r"(smid_));
-    g_tl[tb_][29] = smid_;
-#endif
-  }
 
   const uint32_t raw_addr = smem_addr(raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -417,9 +404,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
         meta_a = (m >= g.push_all_from || g.push_last_pos[meta_b] == (unsigned long long)(g.push_base + m)) ? 1 : 0;
     }
   };
-  fix_rows(blockIdx.y * BM);
-  if (producer && grp < nkb) load_stage(grp);   // in flight while the CTA sets itself up
-
+  // ---- set-up that reads nothing an earlier kernel wrote: barriers, tensor memory, epilogue vectors
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full(s), 4 + 1);  // one elected lane per producer warp of the group + the weight loader
@@ -446,6 +431,25 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
       s_v2[i] = (EPI == EPI_LAYERNORM && in) ? g.ln_b[i] : 0.f;
     }
   }
+  // ---- everything below may read what the previous kernels of the stream produced
+  dep_wait();
+  prefetch_rows(blockIdx.y * BM, g.m_cap);
+  M = rows_of(g.m_cap, g.d_m);
+  if (tid == 0) {
+    TL(0);
+#ifdef ORCA_TC_TIMELINE
+    unsigned long long gt_;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_));
+    const int tb_ = min(blockIdx.y * gridDim.x + blockIdx.x, 1599) + EPI * 1600;
+    g_tl[tb_][28] = (long long)gt_;
+    unsigned smid_;
+    asm volatile("mov.u32 %0, %smid;" : "=r"(smid_));
+    g_tl[tb_][29] = smid_;
+#endif
+  }
+
+  fix_rows(blockIdx.y * BM);
+  if ((int)blockIdx.y * BM < M && producer && grp < nkb) load_stage(grp);   // in flight across the barrier
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -598,11 +602,11 @@ int launch(int epilogue, const Args &a, int n_tiles, cudaStream_t stream) {
   // count (m_cap is a capacity) leave at once
   dim3 grid(n_tiles, std::min(ceil_div(a.m_cap, BM), std::max(1, 148 / n_tiles)));
   switch (epilogue) {
-    case EPI_BIAS: tc_gemm_kernel<EPI_BIAS><<<grid, THREADS, SMEM_BYTES, stream>>>(a); break;
-    case EPI_HIDDEN: tc_gemm_kernel<EPI_HIDDEN><<<grid, THREADS, SMEM_BYTES, stream>>>(a); break;
-    case EPI_LAYERNORM: tc_gemm_kernel<EPI_LAYERNORM><<<grid, THREADS, SMEM_BYTES, stream>>>(a); break;
-    case EPI_GRU: tc_gemm_kernel<EPI_GRU><<<grid, THREADS, SMEM_BYTES, stream>>>(a); break;
-    case EPI_SCORE: tc_gemm_kernel<EPI_SCORE><<<grid, THREADS, SMEM_BYTES, stream>>>(a); break;
+    case EPI_BIAS: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_BIAS>, grid, THREADS, SMEM_BYTES, stream, a)); break;
+    case EPI_HIDDEN: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_HIDDEN>, grid, THREADS, SMEM_BYTES, stream, a)); break;
+    case EPI_LAYERNORM: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_LAYERNORM>, grid, THREADS, SMEM_BYTES, stream, a)); break;
+    case EPI_GRU: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_GRU>, grid, THREADS, SMEM_BYTES, stream, a)); break;
+    case EPI_SCORE: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_SCORE>, grid, THREADS, SMEM_BYTES, stream, a)); break;
     default: return set_error(ORCA_E_BADARG, "tc::launch: unknown epilogue %d", epilogue);
   }
   ORCA_COUNT_LAUNCH();

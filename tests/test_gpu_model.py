@@ -211,6 +211,32 @@ def test_recursions_share_one_model():
         b.compute_edge_probabilities(src, dst, neg, ts, eidx, spec.n_degree, True, False, None)
 
 
+def test_dependent_launch_changes_nothing():
+    """Kernels enqueued with programmatic stream serialisation give bit-identical results to plain
+    stream-ordered launches (scores and state tables)."""
+    from orca_b200 import _lib
+    g = graph("t_nb2")
+    spec = g.spec
+    gold = golden("t_nb2")
+    plan = unpack(gold[f"plan_{spec.strategy}_flat"], gold[f"plan_{spec.strategy}_off"])
+    out = []
+    try:
+        for enable in (0, 1):
+            _lib.check(_lib.lib().orca_set_dependent_launch(enable))
+            tgn = make_model(g)
+            scores = []
+            for b, src, dst, ts, eidx in batches(g, 12):
+                p, q = tgn.compute_edge_probabilities(src, dst, np.roll(dst, 1), ts, eidx, spec.n_degree, True, False,
+                                                      plan[b])
+                scores.append(torch.cat([p, q]).clone())
+            tgn.check_status()
+            out.append((torch.cat(scores), tgn.memory.memory.clone(), tgn.embedding_module.histories[0].emb.clone()))
+    finally:
+        _lib.check(_lib.lib().orca_set_dependent_launch(1))
+    for a, b in zip(out[0], out[1]):
+        assert torch.equal(a, b)
+
+
 def test_unsupported_modes_fail_loudly():
     g = graph("t_nb2")
     tgn = make_model(g)
