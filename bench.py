@@ -353,7 +353,7 @@ def run_ours(a):
 # DRAM traffic of attn_gather_kernel: dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic
 # bytes of the captured launch (profiles/attn_gather_kernel_c4_ncu.md: 15.23 MB read + 0 written for
 # 30.68 MB algorithmic, workload c4), applied to the algorithmic bytes of this run's launches
-GATHER_TRAFFIC_RATIO = 15.233536 / 30.683416
+GATHER_TRAFFIC_RATIO = 15.246848 / 30.683416
 
 
 def oracle_sample(g, neg, plan, first, n_batches, sub_bs, threads, min_seconds=0.0):

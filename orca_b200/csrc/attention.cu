@@ -85,6 +85,18 @@ __device__ __forceinline__ void time_terms(float dt, const float (&wt)[6], float
   }
 }
 
+// Optional in-kernel timeline (development builds only, -DORCA_GA_TIMELINE): SM clock stamps of warp 0
+// of every block for its first rows.
+#ifdef ORCA_GA_TIMELINE
+__device__ long long g_ga_tl[512][8][8];
+#define GTL(i)                                                                                   \
+  do {                                                                                           \
+    if (warp == 0 && lane == 0 && tl_row < 8 && blockIdx.x < 512) g_ga_tl[blockIdx.x][tl_row][(i)] = clock64(); \
+  } while (0)
+#else
+#define GTL(i)
+#endif
+
 __global__ void __launch_bounds__(GA_THREADS, 2)
 attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_table,
                    const float *__restrict__ edge_table, const float *__restrict__ time_w,
@@ -113,7 +125,11 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
 
   const int wpb = blockDim.x >> 5;   // 8 warps per block, 4 when k is large (shared memory)
   const int warps_total = gridDim.x * wpb;
+  int tl_row = -1;
+  (void)tl_row;
   for (int row = blockIdx.x * wpb + warp; row < n; row += warps_total) {
+    ++tl_row;
+    GTL(0);
     int my_nbr = 0, my_eid = 0;
     float my_dt = 0.f;
     if (lane < k) {
@@ -123,6 +139,7 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
       my_dt = delta[o];
     }
     const unsigned vmask = __ballot_sync(0xffffffffu, my_nbr != 0);
+    GTL(1);
     if (vmask == 0) {
       // every slot is padding: the layer ignores the attention term for this row
       if (lane == 0) valid_out[row] = 0;
@@ -143,9 +160,16 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
       x[1] = __ldg(p1);
       x[2] = __ldg(p2);
     };
-    float4 x[3], xn[3];
-    unsigned todo = vmask;
-    load_slot(__ffs(todo) - 1, x);
+    // three slot buffers: two slots are requested ahead of the one being processed
+    float4 x[3], xn[3], xnn[3];
+    unsigned todo = vmask;        // slots not yet processed
+    unsigned ahead = vmask;       // slots not yet requested
+    load_slot(__ffs(ahead) - 1, x);
+    ahead &= ahead - 1;
+    if (ahead) {
+      load_slot(__ffs(ahead) - 1, xn);
+      ahead &= ahead - 1;
+    }
     // the lane's pieces of the two query heads (head h starts at h * 528 in the projected query)
     const float *qrow = qt + (size_t)row * QT_LD;
     float4 qa[3], qb[3];
@@ -163,11 +187,15 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
       qtb[i] = __ldg(qrow + QT_HEAD + 2 * D + c);
     }
 
+    GTL(2);
     // ---- pass 1: time encodings and partial logits, slot by slot
     for (int it = 0; it < n_valid; ++it) {
       const int j = __ffs(todo) - 1;
       todo &= todo - 1;
-      if (todo) load_slot(__ffs(todo) - 1, xn);   // request the next slot before working on this one
+      if (ahead) {                                // request the slot after next before working on this one
+        load_slot(__ffs(ahead) - 1, xnn);
+        ahead &= ahead - 1;
+      }
       const float dt = __shfl_sync(0xffffffffu, my_dt, j);
       float s0 = 0.f, s1 = 0.f;
       {
@@ -208,9 +236,13 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
       s_part[(2 * it) * GA_PART_LD + lane] = s0;
       s_part[(2 * it + 1) * GA_PART_LD + lane] = s1;
 #pragma unroll
-      for (int i = 0; i < 3; ++i) x[i] = xn[i];
+      for (int i = 0; i < 3; ++i) {
+        x[i] = xn[i];
+        xn[i] = xnn[i];
+      }
     }
     __syncwarp();
+    GTL(3);
 
     // ---- softmax: lane p reduces partial row p = 2 * slot + head; heads live on even / odd lanes
     // (k <= 16 keeps all 2k rows on the 32 lanes; for larger k a lane takes rows p and p + 32)
@@ -242,6 +274,7 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
       prob_hi = e_hi * inv;
     }
 
+    GTL(4);
     // ---- pass 2: weighted key sum
     float4 am0[3], am1[3];                         // gathered part, heads 0 / 1
     float at0[GA_T_ITERS], at1[GA_T_ITERS];        // time part
@@ -249,11 +282,18 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
     for (int i = 0; i < 3; ++i) am0[i] = am1[i] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < GA_T_ITERS; ++i) at0[i] = at1[i] = 0.f;
-    todo = vmask;
-    load_slot(__ffs(todo) - 1, x);
+    ahead = vmask;
+    load_slot(__ffs(ahead) - 1, x);
+    ahead &= ahead - 1;
+    if (ahead) {
+      load_slot(__ffs(ahead) - 1, xn);
+      ahead &= ahead - 1;
+    }
     for (int it = 0; it < n_valid; ++it) {
-      todo &= todo - 1;
-      if (todo) load_slot(__ffs(todo) - 1, xn);
+      if (ahead) {
+        load_slot(__ffs(ahead) - 1, xnn);
+        ahead &= ahead - 1;
+      }
       const int p = 2 * it;
       const float p0 = p < 32 ? __shfl_sync(0xffffffffu, prob_lo, p) : __shfl_sync(0xffffffffu, prob_hi, p - 32);
       const float p1 = p < 32 ? __shfl_sync(0xffffffffu, prob_lo, p + 1) : __shfl_sync(0xffffffffu, prob_hi, p - 31);
@@ -273,8 +313,12 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
         }
       }
 #pragma unroll
-      for (int i = 0; i < 3; ++i) x[i] = xn[i];
+      for (int i = 0; i < 3; ++i) {
+        x[i] = xn[i];
+        xn[i] = xnn[i];
+      }
     }
+    GTL(5);
     // write the row: [head 0: gathered 344 | time 172][head 1: ...]
     float *out = ctx + (size_t)row * QT;
 #pragma unroll
@@ -295,6 +339,7 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
     prof_rows += 1;
     prof_slots += (unsigned long long)n_valid;
     __syncwarp();   // the parked values of this row are dead before the next row overwrites them
+    GTL(6);
   }
   if (prof != nullptr && lane == 0 && prof_rows) {
     atomicAdd(&prof[0], prof_rows);     // rows that gathered
@@ -388,3 +433,9 @@ extern "C" int orca_attn_gather(const float *d_qt, const float *d_nbr_table, con
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;
 }
+
+#ifdef ORCA_GA_TIMELINE
+extern "C" int orca_ga_timeline_read(long long *h_out) {
+  return (int)cudaMemcpyFromSymbol(h_out, orca::g_ga_tl, sizeof(long long) * 512 * 8 * 8);
+}
+#endif

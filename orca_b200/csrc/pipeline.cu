@@ -142,12 +142,15 @@ __global__ void shard_l1_kernel(const int32_t *__restrict__ nodes1, const double
 // History.push of ALL layer-1 rows from the all-gathered buffer: row i sits at slot
 // (i % world) * rpr + i / world
 __global__ void push_gathered_kernel(float *__restrict__ table, const float *__restrict__ emb_all,
-                                     const int32_t *__restrict__ ids, const uint8_t *__restrict__ win,
-                                     const int32_t *__restrict__ n1, int world, int rpr) {
+                                     const int32_t *__restrict__ ids, const unsigned long long *__restrict__ last_pos,
+                                     long long base, int all_from, const int32_t *__restrict__ n1, int world,
+                                     int rpr) {
   const int n = *n1;
   const int i = blockIdx.x * 4 + threadIdx.x / 64;
   const int t = threadIdx.x % 64;
-  if (i >= n || t >= D / 4 || win[i] == 0) return;
+  if (i >= n || t >= D / 4) return;
+  // the last occurrence of an id wins; the appended rows are distinct and always win
+  if (i < all_from && last_pos[ids[i]] != (unsigned long long)(base + i)) return;
   const size_t slot = (size_t)(i % world) * rpr + i / world;
   reinterpret_cast<float4 *>(table + (size_t)ids[i] * D)[t] =
       reinterpret_cast<const float4 *>(emb_all + slot * D)[t];
@@ -462,15 +465,12 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
   if (phase == 1) {
     ORCA_CHECK_ARG(d_emb1_local != nullptr);
     launch_counter() = 0;
-    batch_prep_kernel<<<ceil_div(N, 256), 256, 0, s>>>(d_batch_i32, d_batch_ts, b, w.nodes1, w.ts1, w.cat_dst, w.n1);
-    ORCA_COUNT_LAUNCH();
-    // replicated index work: every rank must find the same uncached set and the same winners
-    ORCA_TRY(orca_sample_topk_mark(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
-                                   nullptr, k, w.nbr2, w.eid2, nullptr, w.dt2, d_status, m->cache_flag,
-                                   m->cand_bitmap, s));
-    ORCA_TRY(orca_find_uncached_marked(m->cand_bitmap, N, m->n_nodes, w.nodes1, w.ts1, u_cap, w.n1, d_status, s));
-    ORCA_TRY(orca_last_occurrence(w.nodes1, R1, w.n1, m->n_nodes, m->last_pos, *m->epoch_base, w.win1,
-                                  nullptr, nullptr, s));
+    // replicated index work: every rank must find the same uncached set and the same winners (row list,
+    // top-level table, candidates and last-occurrence records in one launch, as on one GPU)
+    const long long base1 = *m->epoch_base;
+    ORCA_TRY(launch_batch_head(m, d_batch_i32, d_batch_ts, b, w.nodes1, w.ts1, w.cat_dst, w.nbr2, w.eid2, w.dt2,
+                               d_status, base1, s));
+    ORCA_TRY(launch_uncached_finish(m, N, w.nodes1, w.ts1, u_cap, w.n1, w.n_unc, d_status, base1, s));
     *m->epoch_base += R1;
     // this rank's layer-1 rows
     shard_l1_kernel<<<ceil_div(rpr, 256), 256, 0, s>>>(w.nodes1, w.ts1, w.n1, rank, world, rpr, w.loc_nodes,
@@ -489,16 +489,17 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
 
   ORCA_CHECK_ARG(d_emb1_all != nullptr && d_prob_local != nullptr);
   // every replica of the history table receives every layer-1 row
-  push_gathered_kernel<<<ceil_div(R1, 4), 256, 0, s>>>(m->hist_emb, d_emb1_all, w.nodes1, w.win1, w.n1, world, rpr);
+  // (winners by the records phase 1 made: it advanced the epoch by R1 and nothing recorded since)
+  push_gathered_kernel<<<ceil_div(R1, 4), 256, 0, s>>>(m->hist_emb, d_emb1_all, w.nodes1,
+                                                       reinterpret_cast<const unsigned long long *>(m->last_pos),
+                                                       *m->epoch_base - R1, N, w.n1, world, rpr);
   ORCA_COUNT_LAUNCH();
   if (d_plan != nullptr) {
     const bool know_prev = *m->n_prev_plan >= 0;
-    ORCA_TRY(orca_history_set_flags(m->cache_flag, m->n_nodes, know_prev ? m->prev_plan : nullptr,
-                                    know_prev ? *m->n_prev_plan : 0, d_plan, n_plan, s));
-    if (n_plan > 0) {
-      copy_i32_kernel<<<ceil_div(n_plan, 256), 256, 0, s>>>(d_plan, m->prev_plan, n_plan);
-      ORCA_COUNT_LAUNCH();
-    }
+    if (!know_prev) ORCA_CUDA(cudaMemsetAsync(m->cache_flag, 0, (size_t)m->n_nodes, s));
+    plan_flags_kernel<<<1, 1024, 0, s>>>(m->cache_flag, m->n_nodes, m->prev_plan, know_prev ? *m->n_prev_plan : 0,
+                                         d_plan, n_plan);
+    ORCA_COUNT_LAUNCH();
     *m->n_prev_plan = n_plan;
   } else {
     set_flags_counted_kernel<<<std::min(ceil_div(R1, 256), 1024), 256, 0, s>>>(m->cache_flag, m->n_nodes,
@@ -515,8 +516,7 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
     forked = true;
   }
   cudaStream_t ms = forked ? g_overlap.aux : s;
-  ORCA_TRY(orca_last_occurrence(d_batch_i32, 2 * b, nullptr, m->n_nodes, m->last_pos, *m->epoch_base,
-                                w.is_last2, w.win_pos, w.n_win, ms));
+  ORCA_TRY(launch_last_occ_compact(d_batch_i32, 2 * b, m->n_nodes, m->last_pos, *m->epoch_base, w.win_pos, w.n_win, ms));
   *m->epoch_base += 2 * b;
   ORCA_TRY(orca_message_store(&m->mem, m->edge_table, m->time_w, d_batch_i32, w.cat_dst, d_batch_ts,
                               d_batch_i32 + 3 * b, b, w.win_pos, 2 * b, w.n_win, w.win_nodes, ms));
