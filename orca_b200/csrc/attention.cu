@@ -115,10 +115,6 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
   float wt[GA_T_ITERS];
 #pragma unroll
   for (int i = 0; i < GA_T_ITERS; ++i) wt[i] = (lane + 32 * i < D) ? __ldg(time_w + lane + 32 * i) : 0.f;
-  // the largest frequency of each column group (columns 32 i .. 32 i + 31)
-  float wg[GA_T_ITERS];
-#pragma unroll
-  for (int i = 0; i < GA_T_ITERS; ++i) wg[i] = __ldg(time_w + 32 * i);
   const bool third = lane + 64 < GA_MEM_F4;       // lanes 0..21 own a third 16-byte piece
   unsigned long long prof_rows = 0, prof_slots = 0;
   (void)status;
@@ -160,15 +156,20 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
       x[1] = __ldg(p1);
       x[2] = __ldg(p2);
     };
-    // three slot buffers: two slots are requested ahead of the one being processed
-    float4 x[3], xn[3], xnn[3];
-    unsigned todo = vmask;        // slots not yet processed
-    unsigned ahead = vmask;       // slots not yet requested
-    load_slot(__ffs(ahead) - 1, x);
-    ahead &= ahead - 1;
-    if (ahead) {
-      load_slot(__ffs(ahead) - 1, xn);
-      ahead &= ahead - 1;
+    // two slot buffers used alternately (no register copies): while one slot is processed the next one
+    // is in flight
+    float4 xa[3], xb[3];
+    unsigned todo = vmask;
+    int j0 = __ffs(todo) - 1;
+    todo &= todo - 1;
+    load_slot(j0, xa);
+    // which column groups of this lane's slot need the fixed-point cosine (see time_terms)
+    int my_nl = 0;
+    {
+      const float adt = fabsf(my_dt);
+#pragma unroll
+      for (int i = 0; i < GA_T_ITERS; ++i) my_nl += adt * __ldg(time_w + 32 * i) >= 32768.f ? 1 : 0;
+      if (!(adt * __ldg(time_w) < 1073741824.f)) my_nl = -1;   // beyond the fixed-point range (or not finite)
     }
     // the lane's pieces of the two query heads (head h starts at h * 528 in the projected query)
     const float *qrow = qt + (size_t)row * QT_LD;
@@ -189,41 +190,26 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
 
     GTL(2);
     // ---- pass 1: time encodings and partial logits, slot by slot
-    for (int it = 0; it < n_valid; ++it) {
-      const int j = __ffs(todo) - 1;
-      todo &= todo - 1;
-      if (ahead) {                                // request the slot after next before working on this one
-        load_slot(__ffs(ahead) - 1, xnn);
-        ahead &= ahead - 1;
-      }
+    auto pass1_slot = [&](int it, int j, const float4(&x)[3]) {
       const float dt = __shfl_sync(0xffffffffu, my_dt, j);
+      const int nl = __shfl_sync(0xffffffffu, my_nl, j);
       float s0 = 0.f, s1 = 0.f;
-      {
-        float te[GA_T_ITERS];
-        const float adt = fabsf(dt);
-        int nl = 0;
+      float te[GA_T_ITERS];
+      switch (nl) {
+        case 0: time_terms<0>(dt, wt, te); break;
+        case 1: time_terms<1>(dt, wt, te); break;
+        case 2: time_terms<2>(dt, wt, te); break;
+        case 3: time_terms<3>(dt, wt, te); break;
+        default:
 #pragma unroll
-        for (int i = 0; i < GA_T_ITERS; ++i) nl += adt * wg[i] >= 32768.f ? 1 : 0;
-        if (!(adt * wg[0] < 1073741824.f)) nl = -1;   // beyond the fixed-point range (or not finite)
-        switch (nl) {
-          case 0: time_terms<0>(dt, wt, te); break;
-          case 1: time_terms<1>(dt, wt, te); break;
-          case 2: time_terms<2>(dt, wt, te); break;
-          case 3: time_terms<3>(dt, wt, te); break;
-          case 4: time_terms<4>(dt, wt, te); break;
-          case 5: time_terms<5>(dt, wt, te); break;
-          case 6: time_terms<6>(dt, wt, te); break;
-          default:
+          for (int i = 0; i < GA_T_ITERS; ++i) te[i] = cos_any(dt * wt[i]);
+      }
 #pragma unroll
-            for (int i = 0; i < GA_T_ITERS; ++i) te[i] = cos_any(dt * wt[i]);
-        }
-#pragma unroll
-        for (int i = 0; i < GA_T_ITERS; ++i) {
-          if (lane + 32 * i < D) {
-            s_te[it * GA_TE_LD + lane + 32 * i] = te[i];
-            s0 = fmaf(te[i], qta[i], s0);
-            s1 = fmaf(te[i], qtb[i], s1);
-          }
+      for (int i = 0; i < GA_T_ITERS; ++i) {
+        if (lane + 32 * i < D) {
+          s_te[it * GA_TE_LD + lane + 32 * i] = te[i];
+          s0 = fmaf(te[i], qta[i], s0);
+          s1 = fmaf(te[i], qtb[i], s1);
         }
       }
 #pragma unroll
@@ -235,11 +221,22 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
       }
       s_part[(2 * it) * GA_PART_LD + lane] = s0;
       s_part[(2 * it + 1) * GA_PART_LD + lane] = s1;
-#pragma unroll
-      for (int i = 0; i < 3; ++i) {
-        x[i] = xn[i];
-        xn[i] = xnn[i];
+    };
+    for (int it = 0; it < n_valid; it += 2) {
+      int j1 = -1;
+      if (todo) {
+        j1 = __ffs(todo) - 1;
+        todo &= todo - 1;
+        load_slot(j1, xb);
       }
+      pass1_slot(it, j0, xa);
+      if (j1 < 0) break;
+      if (todo) {
+        j0 = __ffs(todo) - 1;
+        todo &= todo - 1;
+        load_slot(j0, xa);
+      }
+      pass1_slot(it + 1, j1, xb);
     }
     __syncwarp();
     GTL(3);
@@ -282,18 +279,7 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
     for (int i = 0; i < 3; ++i) am0[i] = am1[i] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < GA_T_ITERS; ++i) at0[i] = at1[i] = 0.f;
-    ahead = vmask;
-    load_slot(__ffs(ahead) - 1, x);
-    ahead &= ahead - 1;
-    if (ahead) {
-      load_slot(__ffs(ahead) - 1, xn);
-      ahead &= ahead - 1;
-    }
-    for (int it = 0; it < n_valid; ++it) {
-      if (ahead) {
-        load_slot(__ffs(ahead) - 1, xnn);
-        ahead &= ahead - 1;
-      }
+    auto pass2_slot = [&](int it, const float4(&x)[3]) {
       const int p = 2 * it;
       const float p0 = p < 32 ? __shfl_sync(0xffffffffu, prob_lo, p) : __shfl_sync(0xffffffffu, prob_hi, p - 32);
       const float p1 = p < 32 ? __shfl_sync(0xffffffffu, prob_lo, p + 1) : __shfl_sync(0xffffffffu, prob_hi, p - 31);
@@ -312,11 +298,23 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
           at1[i] = fmaf(p1, te, at1[i]);
         }
       }
-#pragma unroll
-      for (int i = 0; i < 3; ++i) {
-        x[i] = xn[i];
-        xn[i] = xnn[i];
+    };
+    todo = vmask;
+    load_slot(__ffs(todo) - 1, xa);
+    todo &= todo - 1;
+    for (int it = 0; it < n_valid; it += 2) {
+      const bool more = todo != 0;
+      if (more) {
+        load_slot(__ffs(todo) - 1, xb);
+        todo &= todo - 1;
       }
+      pass2_slot(it, xa);
+      if (!more) break;
+      if (todo) {
+        load_slot(__ffs(todo) - 1, xa);
+        todo &= todo - 1;
+      }
+      pass2_slot(it + 1, xb);
     }
     GTL(5);
     // write the row: [head 0: gathered 344 | time 172][head 1: ...]
