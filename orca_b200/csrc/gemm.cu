@@ -460,7 +460,7 @@ int orca_attn_output(const orca_attn_weights_t *w, const float *d_ctx, const uin
                      void *stream) {
   ORCA_CHECK_ARG(d_push_table == nullptr || (d_push_ids && d_push_win));
   return orca::attn_output_impl(w, d_ctx, d_valid, d_feat, d_idx, n_rows_cap, d_n_rows, d_out, d_push_table,
-                                d_push_ids, d_push_win, nullptr, 0, 0, d_scratch_hidden, (cudaStream_t)stream);
+                                d_push_ids, d_push_win, nullptr, 0, 0, d_scratch_hidden, 0, (cudaStream_t)stream);
 }
 
 }  // extern "C"
@@ -479,12 +479,13 @@ __global__ void win_from_last_pos_kernel(const int32_t *__restrict__ ids, int ca
 
 // d_push_win given: rows with a non-zero byte are pushed.  Otherwise (d_last_pos given) row i is
 // pushed when i >= all_from or when last_pos[push_ids[i]] == base + i; `d_push_win` is then only
-// scratch for the fp32 debug path and may be NULL in tensor-core mode.
+// scratch for the fp32 debug path and may be NULL in tensor-core mode.  rows_hint (> 0): the live row
+// count the caller expects (n_rows_cap is a capacity); it only steers how the work is spread.
 int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uint8_t *d_valid, const float *d_feat,
                      const int32_t *d_idx, int32_t n_rows_cap, const int32_t *d_n_rows, float *d_out,
                      float *d_push_table, const int32_t *d_push_ids, const uint8_t *d_push_win,
                      const int64_t *d_last_pos, long long base, int all_from, float *d_scratch_hidden,
-                     cudaStream_t stream) {
+                     int rows_hint, cudaStream_t stream) {
   ORCA_CHECK_ARG(w && w->G && w->b1 && w->g && w->W2t && w->b2 && w->ln_w && w->ln_b);
   ORCA_CHECK_ARG(d_ctx && d_valid && d_feat && d_out && n_rows_cap >= 0);
   if (n_rows_cap == 0) return ORCA_OK;
@@ -513,6 +514,12 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
     a.bias = w->b1;
     a.bias2 = w->g;
     a.out = d_scratch_hidden;
+    // 19 k-blocks on a single column tile: with few row blocks, a cluster of CTAs splits them so that
+    // more SMs pull the operands in (the k loop is bound by the bytes a stage moves into one SM)
+    {
+      const int row_blocks = ceil_div(rows_hint > 0 ? std::min(rows_hint, n_rows_cap) : n_rows_cap, tc::BM);
+      a.ksplit = row_blocks * 3 <= 148 ? 3 : row_blocks * 2 <= 148 ? 2 : 1;
+    }
     int rc = tc::launch(tc::EPI_HIDDEN, a, 1, (cudaStream_t)stream);
     if (rc) return rc;
     tc::Args b{};

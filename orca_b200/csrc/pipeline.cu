@@ -374,7 +374,8 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     // rows are distinct out-of-batch nodes, so each of them wins)
     ORCA_TRY(attn_output_impl(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.nodes1, R1, d_n1, w.emb1,
                               push1 ? m->hist_emb : nullptr, push1 ? w.nodes1 : nullptr, push1 ? w.win1 : nullptr,
-                              mode == ORCA_MODE_BUDGET ? m->last_pos : nullptr, base1, N, w.hidden, s));
+                              mode == ORCA_MODE_BUDGET ? m->last_pos : nullptr, base1, N, w.hidden,
+                              mode == ORCA_MODE_NO_REUSE ? R1 : N, s));
     ORCA_TRY(g_trace.mark(PH_OUTPUT_L1, s));
     if (g_overlap.enabled && !g_trace.on) {
       ORCA_TRY(g_overlap.ensure());

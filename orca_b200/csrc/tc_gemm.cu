@@ -143,6 +143,21 @@ __device__ __forceinline__ void tmem_ld16_sum(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(a[i]) + __uint_as_float(b[i]);
 }
 
+// thread-block cluster helpers (split-K: the CTAs of a cluster share a row block and split its k-blocks)
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 ld_peer_f4(uint32_t local_saddr, uint32_t cta_rank) {
+  uint32_t ra;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_saddr), "r"(cta_rank));
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(ra)
+               : "memory");
+  return v;
+}
+
 // x ~ head + tail, both bf16 (round to nearest even), for 8 consecutive K elements: one 16-byte chunk
 // of the head image and one of the tail image.  Packed conversions (two floats per instruction).
 __device__ __forceinline__ uint32_t pack_split(float x0, float x1, uint32_t &lo) {
@@ -200,7 +215,7 @@ __device__ long long g_tl[8192][32];
 template <int EPI>
 __device__ __forceinline__ void tile_output(const Args &g, const float *tile, const float *s_bias, const float *s_v1,
                                             const float *s_v2, const float *s_dot, int m0, int m_rows, int nt,
-                                            int warp, int lane, int meta_a, int meta_b) {
+                                            int warp, int lane, int meta_a, int meta_b, int ksplit, int crank) {
   if (EPI == EPI_SCORE) {
     const int tid = warp * 32 + lane;
     if (tid < m_rows) g.out[m0 + tid] = 1.f / (1.f + expf(-(s_dot[tid] + s_dot[BM + tid] + g.b2)));
@@ -220,21 +235,36 @@ __device__ __forceinline__ void tile_output(const Args &g, const float *tile, co
   const float4 lB = has1 ? *reinterpret_cast<const float4 *>(&s_v2[4 * j1]) : f4z;
   auto add4 = [](float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); };
   const int uA = nt * (BN / 4) + j0, uB = nt * (BN / 4) + j1;   // GRU units of this lane
-  for (int it0 = 0; warp + (THREADS / 32) * it0 < m_rows; it0 += RB) {
+  // with split-K the CTAs of the cluster share the rows (row r belongs to CTA r % ksplit) and every value
+  // is the sum of the partial tiles of all CTAs, read over distributed shared memory in rank order
+  const uint32_t tile_saddr = smem_addr(tile);
+  for (int it0 = 0; crank + ksplit * (warp + (THREADS / 32) * it0) < m_rows; it0 += RB) {
     float4 a[RB], b[RB];
     float hA[RB], hB[RB];
     int ma[RB], mb[RB], m[RB];
     bool ok[RB];
 #pragma unroll
     for (int k = 0; k < RB; ++k) {
-      const int r = warp + (THREADS / 32) * (it0 + k);
+      const int r = crank + ksplit * (warp + (THREADS / 32) * (it0 + k));
       ok[k] = r < m_rows;
       m[k] = m0 + r;
       ma[k] = __shfl_sync(0xffffffffu, meta_a, (it0 + k) & 31);
       mb[k] = __shfl_sync(0xffffffffu, meta_b, (it0 + k) & 31);
-      const float *trow_s = tile + (ok[k] ? r : 0) * TILE_LD;
-      a[k] = add4(*reinterpret_cast<const float4 *>(trow_s + 4 * j0), bA);
-      b[k] = has1 ? add4(*reinterpret_cast<const float4 *>(trow_s + 4 * j1), bB) : f4z;
+      const int rr = ok[k] ? r : 0;
+      if (ksplit == 1) {
+        const float *trow_s = tile + rr * TILE_LD;
+        a[k] = add4(*reinterpret_cast<const float4 *>(trow_s + 4 * j0), bA);
+        b[k] = has1 ? add4(*reinterpret_cast<const float4 *>(trow_s + 4 * j1), bB) : f4z;
+      } else {
+        const uint32_t ra = tile_saddr + (uint32_t)(rr * TILE_LD + 4 * j0) * 4u;
+        float4 va = ld_peer_f4(ra, 0), vb = has1 ? ld_peer_f4(ra + 512u, 0) : f4z;
+        for (int c = 1; c < ksplit; ++c) {
+          va = add4(va, ld_peer_f4(ra, c));
+          if (has1) vb = add4(vb, ld_peer_f4(ra + 512u, c));
+        }
+        a[k] = add4(va, bA);
+        b[k] = has1 ? add4(vb, bB) : f4z;
+      }
       hA[k] = hB[k] = 0.f;
       if (EPI == EPI_GRU && ok[k]) {
         const float *hrow = g.memory + (size_t)mb[k] * D;
@@ -328,7 +358,12 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   const int pw = grp ? warp - 6 : warp;   // producer warp within its group: tile rows pw*32 .. pw*32+31
   const int rsub = lane >> 3, f = lane & 7;
   const int w0 = g.a0.width, w1 = g.a1.width, Kd = g.Kd;
-  const int nkb = g.n_kblocks;
+  // split-K: CTA `crank` of the cluster (1,1,ksplit) takes k-blocks [kb_lo, kb_lo + nkb)
+  const int ksplit = g.ksplit > 1 ? g.ksplit : 1;
+  const int crank = ksplit > 1 ? (int)blockIdx.z : 0;
+  const int kb_per = (g.n_kblocks + ksplit - 1) / ksplit;
+  const int kb_lo = crank * kb_per;
+  const int nkb = max(0, min(g.n_kblocks, kb_lo + kb_per) - kb_lo);
 
   dep_trigger();
   int M = 0;   // live rows (known after the wait below)
@@ -351,7 +386,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
         if (g.row_valid != nullptr && g.zero_cols > 0 && g.row_valid[m] == 0) ri0 = -1;
       }
     }
-    const int r = warp + (THREADS / 32) * lane;
+    const int r = crank + ksplit * (warp + (THREADS / 32) * lane);
     const int m = m0 + r;
     if (r < BM && m < limit) {
       if (EPI == EPI_HIDDEN) meta_a = g.row_valid == nullptr ? 1 : g.row_valid[m];
@@ -379,7 +414,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   const float4 *zero = reinterpret_cast<const float4 *>(g_zero16);
   float4 x[16];
   auto load_stage = [&](int kb) {
-    const int col = kb * BK + f * 8;
+    const int col = (kb_lo + kb) * BK + f * 8;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int r0 = __shfl_sync(0xffffffffu, ri0, 4 * i + rsub);
@@ -398,7 +433,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     if (producer && m0 + pw * 32 + lane >= M) ri0 = ri1 = -1;
     if (EPI == EPI_LAYERNORM && g.push_table != nullptr && g.push_win == nullptr) {
       // winners by record; only for live rows: the id of a row past the live count is not a valid index
-      const int r = warp + (THREADS / 32) * lane;
+      const int r = crank + ksplit * (warp + (THREADS / 32) * lane);
       const int m = m0 + r;
       if (r < BM && m < M)
         meta_a = (m >= g.push_all_from || g.push_last_pos[meta_b] == (unsigned long long)(g.push_base + m)) ? 1 : 0;
@@ -494,7 +529,8 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     } else if (warp == 4) {
       // ---------------------------------------------------------------- weight stages
       if (lane == 0) {
-        const char *wsrc = reinterpret_cast<const char *>(g.w_packed) + (size_t)nt * nkb * (2 * B_BYTES);
+        const char *wsrc = reinterpret_cast<const char *>(g.w_packed) +
+                           ((size_t)nt * g.n_kblocks + kb_lo) * (2 * B_BYTES);
         for (int kb = 0; kb < nkb; ++kb) {
           const int s = kb & 1;
           const int u = t * (s ? uses1 : uses0) + (kb >> 1);
@@ -570,14 +606,15 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     }
     if (tid == 0 && t == 0) TL(24);
     tc_fence_before();
-    __syncthreads();
+    if (ksplit > 1) cluster_sync_all(); else __syncthreads();   // every partial tile of the cluster is complete
     tc_fence_after();
-    tile_output<EPI>(g, tile, s_bias, s_v1, s_v2, &s_dot[0][0], m0, m_rows, nt, warp, lane, meta_a, meta_b);
+    tile_output<EPI>(g, tile, s_bias, s_v1, s_v2, &s_dot[0][0], m0, m_rows, nt, warp, lane, meta_a, meta_b, ksplit,
+                     crank);
     if (tid == 0 && t == 0) TL(25);
     // the tile lives in the stage ring: the next row block's bulk copies and stores may only land
-    // once every warp has read it
+    // once every warp (of every CTA of the cluster) has read it
     fence_async_smem();
-    __syncthreads();
+    if (ksplit > 1) cluster_sync_all(); else __syncthreads();
   }
   if (warp == 5) {
     tc_fence_after();
@@ -598,15 +635,23 @@ int launch(int epilogue, const Args &a, int n_tiles, cudaStream_t stream) {
     ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_SCORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     configured_device = dev;
   }
+  // split-K only where every CTA of the cluster gets k-blocks and the epilogue is linear up to pass 2
+  int ksplit = a.ksplit > 1 ? a.ksplit : 1;
+  if (ksplit > 1) {
+    const int per = ceil_div(a.n_kblocks, ksplit);
+    if (epilogue == EPI_SCORE || (ksplit - 1) * per >= a.n_kblocks || ksplit > 8) ksplit = 1;
+  }
+  Args b = a;
+  b.ksplit = ksplit;
   // one wave: a CTA walks several row blocks when there are more tiles than SMs; CTAs past the live row
   // count (m_cap is a capacity) leave at once
-  dim3 grid(n_tiles, std::min(ceil_div(a.m_cap, BM), std::max(1, 148 / n_tiles)));
+  dim3 grid(n_tiles, std::min(ceil_div(a.m_cap, BM), std::max(1, 148 / (n_tiles * ksplit))), ksplit);
   switch (epilogue) {
-    case EPI_BIAS: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_BIAS>, grid, THREADS, SMEM_BYTES, stream, a)); break;
-    case EPI_HIDDEN: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_HIDDEN>, grid, THREADS, SMEM_BYTES, stream, a)); break;
-    case EPI_LAYERNORM: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_LAYERNORM>, grid, THREADS, SMEM_BYTES, stream, a)); break;
-    case EPI_GRU: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_GRU>, grid, THREADS, SMEM_BYTES, stream, a)); break;
-    case EPI_SCORE: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_SCORE>, grid, THREADS, SMEM_BYTES, stream, a)); break;
+    case EPI_BIAS: ORCA_CUDA(launch_dep_cluster(tc_gemm_kernel<EPI_BIAS>, grid, THREADS, SMEM_BYTES, stream, ksplit, b)); break;
+    case EPI_HIDDEN: ORCA_CUDA(launch_dep_cluster(tc_gemm_kernel<EPI_HIDDEN>, grid, THREADS, SMEM_BYTES, stream, ksplit, b)); break;
+    case EPI_LAYERNORM: ORCA_CUDA(launch_dep_cluster(tc_gemm_kernel<EPI_LAYERNORM>, grid, THREADS, SMEM_BYTES, stream, ksplit, b)); break;
+    case EPI_GRU: ORCA_CUDA(launch_dep_cluster(tc_gemm_kernel<EPI_GRU>, grid, THREADS, SMEM_BYTES, stream, ksplit, b)); break;
+    case EPI_SCORE: ORCA_CUDA(launch_dep_cluster(tc_gemm_kernel<EPI_SCORE>, grid, THREADS, SMEM_BYTES, stream, ksplit, b)); break;
     default: return set_error(ORCA_E_BADARG, "tc::launch: unknown epilogue %d", epilogue);
   }
   ORCA_COUNT_LAUNCH();

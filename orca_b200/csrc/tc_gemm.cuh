@@ -43,6 +43,7 @@ struct Args {
   int zero_cols;
   const void *w_packed;      // [n_tiles][n_kblocks][head | tail] bf16 stage images (weights.pack_tc)
   int n_kblocks;
+  int ksplit;                // > 1: the k-blocks are split over a cluster of this many CTAs (not with SCORE)
   int m_cap;
   const int32_t *d_m;
   const float *bias;         // [n_tiles * BN]
@@ -77,6 +78,6 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
                      const int32_t *d_idx, int32_t n_rows_cap, const int32_t *d_n_rows, float *d_out,
                      float *d_push_table, const int32_t *d_push_ids, const uint8_t *d_push_win,
                      const int64_t *d_last_pos, long long base, int all_from, float *d_scratch_hidden,
-                     cudaStream_t stream);
+                     int rows_hint, cudaStream_t stream);
 
 }  // namespace orca
