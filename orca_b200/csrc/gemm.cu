@@ -514,12 +514,13 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
     a.bias = w->b1;
     a.bias2 = w->g;
     a.out = d_scratch_hidden;
-    // 19 k-blocks on a single column tile: with few row blocks, a cluster of CTAs splits them so that
-    // more SMs pull the operands in (the k loop is bound by the bytes a stage moves into one SM)
-    {
-      const int row_blocks = ceil_div(rows_hint > 0 ? std::min(rows_hint, n_rows_cap) : n_rows_cap, tc::BM);
-      a.ksplit = row_blocks * 3 <= 148 ? 3 : row_blocks * 2 <= 148 ? 2 : 1;
-    }
+    // (19 k-blocks on a single column tile and only ~47 row blocks per batch.  Splitting K over a cluster
+    // of 3 CTAs -- Args::ksplit, which the kernel supports -- was measured slower at 6000 rows: 47
+    // clusters of three 157-KB CTAs do not all fit at once, the summing pass over distributed shared
+    // memory takes 5 us instead of 2, and the raw-message / GRU chain on the side stream loses the SMs
+    // it ran on beside this kernel: 52 us against 47 us for the output phase.)
+    (void)rows_hint;
+    a.ksplit = 1;
     int rc = tc::launch(tc::EPI_HIDDEN, a, 1, (cudaStream_t)stream);
     if (rc) return rc;
     tc::Args b{};

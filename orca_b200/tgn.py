@@ -248,9 +248,28 @@ class TGN(nn.Module):
 
     # ---- model descriptor for the fused batch entry point ----------------------------------------
     def _descriptor(self, k):
+        """The model descriptor of the fused batch entry.  Graph, weights and scratch pointers are filled
+        once per (neighbour finder, prepared weights, k); the state tables can be replaced between calls
+        (restore_memory, restore_history) and are refreshed every time."""
         nf = self.embedding_module.neighbor_finder
         w = self._weights()
+        gw = self.memory_updater.prepared()
+        ref = getattr(self, "_desc_ref", None)   # the objects themselves are kept: identities cannot be reused
+        if ref is not None and ref[0] is nf and ref[1] is w and ref[2] is gw and ref[3] == k:
+            t = self._desc
+            t.mem = self.memory.c_struct()
+            if self.n_layers == 2 and hasattr(self.embedding_module, "histories"):
+                h = self.embedding_module.histories[0]
+                t.hist_emb = h.emb.data_ptr()
+                t.cache_flag = h.cache_flag_dev.data_ptr()
+                t.prev_plan = h.prev_plan.data_ptr()
+                t.n_prev_plan = h.n_prev.ctypes.data_as(C.POINTER(C.c_int32))
+                t.plan_cap = h.prev_plan.numel()
+            t.rank, t.world = self._rank, self._world
+            t.mode = self._mode
+            return t
         t = _lib.TgnT()
+        self._desc_ref, self._desc = (nf, w, gw, k), t
         t.indptr, t.adj_nbr, t.adj_eid, t.adj_ts = (nf.indptr.data_ptr(), nf.adj_nbr.data_ptr(),
                                                     nf.adj_eid.data_ptr(), nf.adj_ts.data_ptr())
         t.edge_table = self.edge_raw_features.data_ptr()
