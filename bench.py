@@ -217,6 +217,8 @@ def run_ours(a):
             dist.barrier()
         torch.cuda.synchronize()
 
+    host_ms = []
+
     def timed(fn_warm, fn_step):
         for i in range(W):
             fn_warm(i)
@@ -225,8 +227,10 @@ def run_ours(a):
         sampler = ClockSampler(local)
         sampler.start()
         e0.record()
+        t_host = time.perf_counter()
         for i in range(K):
             fn_step(i)
+        host_ms.append((time.perf_counter() - t_host) * 1e3)   # time the CPU needed to enqueue the steps
         e1.record()
         barrier()
         clocks = sampler.result()
@@ -246,8 +250,8 @@ def run_ours(a):
         p, q = tgn.compute_edge_probabilities(src, dst, ng, ts, eidx, k, True, False, plan[b])
         if slot is not None:
             n = len(src)
-            host_out[slot, :n].copy_(p.view(-1), non_blocking=True)
-            host_out[slot, bs:bs + n].copy_(q.view(-1), non_blocking=True)
+            # p and q are the two halves of one [2n] tensor (tgn.last_scores): one copy brings both back
+            host_out[slot, :2 * n].copy_(tgn.last_scores, non_blocking=True)
             h2d += 16 * n + 8 * n + 4 * len(plan[b])
             d2h += 8 * n
 
@@ -341,6 +345,7 @@ def run_ours(a):
                 "sharding": "replicated tables; attention rows and scores split by row/edge % n_gpus; one NCCL "
                             "all-gather of the layer-1 rows per batch" if world > 1 else "single GPU"}),
             "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches_per_batch * K), "clocks": clocks,
+            "host_enqueue_ms_per_step": {"e2e": host_ms[0] / K, "value": host_ms[1] / K},
             "phases_us_per_step": phases}
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(a, g, neg, plan, first + W)

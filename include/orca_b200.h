@@ -374,6 +374,11 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
                                 float *d_emb1_local, const float *d_emb1_all, float *d_prob_local,
                                 float *d_emb2_local, int32_t *d_status, void *stream);
 
+/* Asynchronous copy of a staged batch from pinned host memory to the device on `stream` (what
+ * `tensor.to(device)` does for the batch arrays in evaluation/evaluation.py:34 of the reference; here
+ * one copy per batch). */
+int orca_stage_h2d(void *d_dst, const void *h_src, int64_t bytes, void *stream);
+
 /* With overlap on (default) a two-layer batch runs its raw-message / GRU chain on an auxiliary
  * stream of the library, next to the top attention layer and the scorer; `stream` waits for it
  * before orca_tgn_eval_batch's work is complete, so callers see one stream-ordered operation.  The

@@ -94,6 +94,7 @@ SYMBOLS = {
     "orca_tgn_eval_batch": (C.c_int, [C.POINTER(TgnT), _V, _V, _I32, _V, _I32, _I32, _V, _I64, _V, _V, _V, _V]),
     "orca_tgn_eval_batch_sharded": (C.c_int, [C.POINTER(TgnT), _I32, _V, _V, _I32, _V, _I32, _I32, _V, _I64, _V, _V,
                                               _V, _V, _V, _V]),
+    "orca_stage_h2d": (C.c_int, [_V, _V, C.c_int64, _V]),
     "orca_set_overlap": (C.c_int, [_I32]),
     "orca_set_dependent_launch": (C.c_int, [_I32]),
     "orca_trace": (C.c_int, [_I32]),

@@ -352,7 +352,9 @@ __global__ void __launch_bounds__(F2_THREADS) score_kernel(ScoreArgs g) {
   }
 }
 
-// scatter of the GRU result: memory[node] = h', last_update[node] = msg_ts[node], optional flag clear
+// scatter of the GRU result: memory[node] = h', last_update[node] = msg_ts[node], and -- optionally --
+// the message flag of the node is cleared once every lane of the row has seen it set (a listed node
+// without a pending message is left alone)
 __global__ void gru_scatter_kernel(const float *__restrict__ hnew, orca_memory_t mem,
                                    const int32_t *__restrict__ nodes, int n_cap, const int32_t *d_n,
                                    int clear_flags) {
@@ -360,25 +362,23 @@ __global__ void gru_scatter_kernel(const float *__restrict__ hnew, orca_memory_t
   dep_wait();
   const int n = rows_of(n_cap, d_n);
   const int row = blockIdx.x * (blockDim.x / 64) + threadIdx.x / 64;
-  if (row >= n) return;
-  const int node = nodes[row];
-  if (mem.msg_flag[node] == 0) return;
   const int t = threadIdx.x % 64;
+  int node = 0;
+  bool pending = false;
+  if (row < n) {
+    node = nodes[row];
+    pending = mem.msg_flag[node] != 0;
+  }
+  __syncthreads();
+  if (!pending) return;
   if (t < D / 4) {
     reinterpret_cast<float4 *>(mem.memory + (size_t)node * D)[t] =
         reinterpret_cast<const float4 *>(hnew + (size_t)row * D)[t];
   }
-  if (t == 63) mem.last_update[node] = mem.msg_ts[node];
-  // the flag is cleared by a second pass so that every lane has seen it set
-}
-
-__global__ void gru_clear_kernel(orca_memory_t mem, const int32_t *__restrict__ nodes, int n_cap,
-                                 const int32_t *d_n) {
-  dep_trigger();
-  dep_wait();
-  const int n = rows_of(n_cap, d_n);
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
-    mem.msg_flag[nodes[i]] = 0;
+  if (t == 63) {
+    mem.last_update[node] = mem.msg_ts[node];
+    if (clear_flags) mem.msg_flag[node] = 0;
+  }
 }
 
 }  // namespace orca
@@ -641,10 +641,6 @@ int orca_gru_update(const orca_gru_weights_t *w, const orca_memory_t *mem, const
   ORCA_CUDA(launch_dep(gru_scatter_kernel, ceil_div(n_cap, 4), 256, 0, s, d_scratch_h, *mem, d_nodes, n_cap, d_n,
                        (int)clear_flags));
   ORCA_COUNT_LAUNCH();
-  if (clear_flags) {
-    ORCA_CUDA(launch_dep(gru_clear_kernel, std::min(ceil_div(n_cap, 256), 1024), 256, 0, s, *mem, d_nodes, n_cap, d_n));
-    ORCA_COUNT_LAUNCH();
-  }
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;
 }

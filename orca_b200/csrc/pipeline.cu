@@ -301,6 +301,8 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
 
   float *emb_top = d_emb_out ? d_emb_out : w.emb2;
   bool forked = false;
+  bool side_flags = false;   // History.update_flag with a plan rides on the message-winner launch
+  int side_prev = 0;
   if (m->n_layers == 1) {
     ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, w.nodes1, w.ts1, N,
                               nullptr, k, w.nbr1, w.eid1, nullptr, w.dt1, d_status, s));
@@ -365,6 +367,8 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     }
     ORCA_TRY(g_trace.mark(PH_LAST_OCC_L1, s));
     // layer 1 over memory rows; its output rows are pushed into the history table
+    // (projecting the batch's own rows on the side stream beside the index kernels was measured: no gain,
+    // one more launch)
     ORCA_TRY(orca_attn_query(&m->attn[0], m->mem.memory, w.nodes1, R1, d_n1, w.qt, s));
     ORCA_TRY(g_trace.mark(PH_QUERY_L1, s));
     ORCA_TRY(orca_attn_gather(w.qt, m->mem.memory, m->edge_table, m->time_w, nbr1, eid1, dt1, k, R1,
@@ -389,12 +393,10 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     if (mode != ORCA_MODE_BUDGET) {
       // no flags outside the budgeted recursion
     } else if (d_plan != nullptr) {
-      const bool know_prev = *m->n_prev_plan >= 0;
-      if (!know_prev) ORCA_CUDA(cudaMemsetAsync(m->cache_flag, 0, (size_t)m->n_nodes, fs));
-      ORCA_CUDA(launch_dep(plan_flags_kernel, 1, 1024, 0, fs, m->cache_flag, m->n_nodes, m->prev_plan,
-                           know_prev ? (int)*m->n_prev_plan : 0, d_plan, (int)n_plan));
-      ORCA_COUNT_LAUNCH();
-      ORCA_LAUNCH_CHECK();
+      // (done by the message-winner launch below, which is the next single-block kernel of that stream)
+      side_prev = *m->n_prev_plan >= 0 ? *m->n_prev_plan : 0;
+      if (*m->n_prev_plan < 0) ORCA_CUDA(cudaMemsetAsync(m->cache_flag, 0, (size_t)m->n_nodes, fs));
+      side_flags = true;
       *m->n_prev_plan = n_plan;
     } else {
       // plan-less rule: the flags of the pushed ids are set and never cleared
@@ -421,7 +423,9 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
   // raw messages of the batch (last occurrence per node in [src|dst]) and the memory update; on the
   // auxiliary stream when the fork event was recorded after the last reader of the memory table
   cudaStream_t ms = forked ? g_overlap.aux : s;
-  ORCA_TRY(launch_last_occ_compact(d_batch_i32, 2 * b, m->n_nodes, m->last_pos, *m->epoch_base, w.win_pos, w.n_win, ms));
+  ORCA_TRY(launch_last_occ_compact(d_batch_i32, 2 * b, m->n_nodes, m->last_pos, *m->epoch_base, w.win_pos, w.n_win,
+                                   d_status, side_flags ? m->cache_flag : nullptr, m->prev_plan, side_prev, d_plan,
+                                   n_plan, ms));
   *m->epoch_base += 2 * b;
   ORCA_TRY(g_trace.mark(PH_LAST_OCC_MSG, s));
   ORCA_TRY(orca_message_store(&m->mem, m->edge_table, m->time_w, d_batch_i32, w.cat_dst, d_batch_ts,
@@ -434,9 +438,12 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
     ORCA_CUDA(cudaStreamWaitEvent(s, g_overlap.join, 0));
   }
 
-  publish_counts_kernel<<<1, 1, 0, s>>>(w.n1, w.n_win, d_status);
-  ORCA_COUNT_LAUNCH();
-  ORCA_LAUNCH_CHECK();
+  // (the budgeted two-layer batch has its counters written by the kernels that produce them)
+  if (!fused_head) {
+    publish_counts_kernel<<<1, 1, 0, s>>>(w.n1, w.n_win, d_status);
+    ORCA_COUNT_LAUNCH();
+    ORCA_LAUNCH_CHECK();
+  }
   g_last_batch_launches = launch_counter();
   return ORCA_OK;
 }
@@ -517,7 +524,8 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
     forked = true;
   }
   cudaStream_t ms = forked ? g_overlap.aux : s;
-  ORCA_TRY(launch_last_occ_compact(d_batch_i32, 2 * b, m->n_nodes, m->last_pos, *m->epoch_base, w.win_pos, w.n_win, ms));
+  ORCA_TRY(launch_last_occ_compact(d_batch_i32, 2 * b, m->n_nodes, m->last_pos, *m->epoch_base, w.win_pos, w.n_win,
+                                   nullptr, nullptr, nullptr, 0, nullptr, 0, ms));
   *m->epoch_base += 2 * b;
   ORCA_TRY(orca_message_store(&m->mem, m->edge_table, m->time_w, d_batch_i32, w.cat_dst, d_batch_ts,
                               d_batch_i32 + 3 * b, b, w.win_pos, 2 * b, w.n_win, w.win_nodes, ms));
@@ -544,6 +552,13 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   g_last_batch_launches = launch_counter();
+  return ORCA_OK;
+}
+
+int orca_stage_h2d(void *d_dst, const void *h_src, int64_t bytes, void *stream) {
+  ORCA_CHECK_ARG(d_dst && h_src && bytes >= 0);
+  if (bytes == 0) return ORCA_OK;
+  ORCA_CUDA(cudaMemcpyAsync(d_dst, h_src, (size_t)bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
   return ORCA_OK;
 }
 

@@ -426,6 +426,7 @@ uncached_finish_kernel(uint32_t *__restrict__ gbm, int32_t *__restrict__ cand_co
     if (tid == 0) {
       *d_n_unc = u;
       *cand_count = 0;
+      if (status != nullptr) status[1] = n_query + u;
     }
     return;
   }
@@ -434,6 +435,7 @@ uncached_finish_kernel(uint32_t *__restrict__ gbm, int32_t *__restrict__ cand_co
     if (tid == 0) {
       *d_n_total = n_query;
       *d_n_unc = 0;
+      if (status != nullptr) status[1] = n_query;
     }
     return;
   }
@@ -474,6 +476,7 @@ uncached_finish_kernel(uint32_t *__restrict__ gbm, int32_t *__restrict__ cand_co
     *d_n_total = n_query + u;
     *d_n_unc = u;
     *cand_count = 0;
+    if (status != nullptr) status[1] = n_query + u;   // rows at layer 1 (status word layout, common.cuh)
   }
 }
 
@@ -547,16 +550,44 @@ compact_flags_kernel(const uint8_t *__restrict__ is_last, int n_cap, const int32
 }
 
 // Last occurrence of every id of a short list and the ordered list of those positions, in one block:
-// record (atomicMax of epoch + position), then flag + scan + emit.
+// record (atomicMax of epoch + position), then flag + scan + emit.  The block first does the batch's
+// other single-block chore when a plan is given -- History.update_flag (modules/history.py:25-30):
+// clear the flags of the plan that set them, set the flags of this plan, keep a copy of it -- so that
+// the side stream of a batch needs one launch for both.
 __global__ void __launch_bounds__(1024)
 last_occ_compact_kernel(const int32_t *__restrict__ ids, int n, int64_t n_nodes,
                         unsigned long long *__restrict__ last_pos, long long base,
-                        int32_t *__restrict__ compact, int32_t *__restrict__ n_compact) {
+                        int32_t *__restrict__ compact, int32_t *__restrict__ n_compact, int32_t *status,
+                        uint8_t *__restrict__ flag, int32_t *__restrict__ prev_plan, int n_prev,
+                        const int32_t *__restrict__ plan, int n_plan) {
   __shared__ int s_scan[32];
   __shared__ int s_base;
   const int tid = threadIdx.x;
   dep_trigger();
   dep_wait();
+  if (flag != nullptr) {
+    // eight independent loads per thread in flight: the loop is a chain of L2 round trips otherwise
+    for (int i0 = tid; i0 < n_prev; i0 += 8 * 1024) {
+      int v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = i0 + u * 1024 < n_prev ? prev_plan[i0 + u * 1024] : -1;
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (v[u] >= 0 && v[u] < n_nodes) flag[v[u]] = 0;
+    }
+    __threadfence();
+    __syncthreads();
+    for (int i0 = tid; i0 < n_plan; i0 += 8 * 1024) {
+      int v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = i0 + u * 1024 < n_plan ? plan[i0 + u * 1024] : -1;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (v[u] >= 0 && v[u] < n_nodes) flag[v[u]] = 1;
+        if (i0 + u * 1024 < n_plan) prev_plan[i0 + u * 1024] = v[u];
+      }
+    }
+  }
   if (tid == 0) s_base = 0;
   // four positions per thread and sweep, loaded up front so that their round trips overlap
   constexpr int U = 4;
@@ -617,7 +648,10 @@ last_occ_compact_kernel(const int32_t *__restrict__ ids, int n, int64_t n_nodes,
       __syncthreads();
     }
   }
-  if (tid == 0) *n_compact = s_base;
+  if (tid == 0) {
+    *n_compact = s_base;
+    if (status != nullptr) status[2] = s_base;   // unique positives (status word layout, common.cuh)
+  }
 }
 
 // ---- launchers of the fused batch kernels (used by the batch pipeline)
@@ -667,9 +701,11 @@ int launch_uncached_finish(const orca_tgn_t *m, int n_query, int32_t *nodes_io, 
 }
 
 int launch_last_occ_compact(const int32_t *d_ids, int n, int64_t n_nodes, int64_t *d_last_pos, long long base,
-                            int32_t *d_compact, int32_t *d_n_compact, cudaStream_t s) {
+                            int32_t *d_compact, int32_t *d_n_compact, int32_t *d_status, uint8_t *d_flag,
+                            int32_t *d_prev_plan, int n_prev, const int32_t *d_plan, int n_plan, cudaStream_t s) {
   ORCA_CUDA(launch_dep(last_occ_compact_kernel, 1, 1024, 0, s, d_ids, n, n_nodes,
-                       reinterpret_cast<unsigned long long *>(d_last_pos), base, d_compact, d_n_compact));
+                       reinterpret_cast<unsigned long long *>(d_last_pos), base, d_compact, d_n_compact, d_status,
+                       d_flag, d_prev_plan, n_prev, d_plan, n_plan));
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;

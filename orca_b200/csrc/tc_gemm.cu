@@ -239,6 +239,9 @@ __device__ __forceinline__ void tile_output(const Args &g, const float *tile, co
   // is the sum of the partial tiles of all CTAs, read over distributed shared memory in rank order
   const uint32_t tile_saddr = smem_addr(tile);
   for (int it0 = 0; crank + ksplit * (warp + (THREADS / 32) * it0) < m_rows; it0 += RB) {
+#ifdef ORCA_TC_TIMELINE
+    if (warp == 0 && lane == 0 && EPI != EPI_HIDDEN && EPI != EPI_GRU) TL(10 + it0 / RB);
+#endif
     float4 a[RB], b[RB];
     float hA[RB], hB[RB];
     int ma[RB], mb[RB], m[RB];
@@ -283,7 +286,11 @@ __device__ __forceinline__ void tile_output(const Args &g, const float *tile, co
     } else if (EPI == EPI_HIDDEN) {
 #pragma unroll
       for (int k = 0; k < RB; ++k)
+#ifdef ORCA_EXP_NOSTORE
+        if (ok[k] && a[k].x == 12345.678f) {
+#else
         if (ok[k]) {
+#endif
           const float rvf = ma[k] != 0 ? 1.f : 0.f;
           float *o = g.out + (size_t)m[k] * D;
           *reinterpret_cast<float4 *>(o + 4 * j0) =

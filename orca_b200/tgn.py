@@ -108,6 +108,7 @@ class _Staging:
 
     def __init__(self, n_slots=8):
         self.slots = [None] * n_slots
+        self.views = [None] * n_slots     # numpy views of the pinned buffers (made once per buffer)
         self.events = [None] * n_slots
         self.i = 0
 
@@ -120,14 +121,15 @@ class _Staging:
         if buf is None or buf.numel() < nbytes:
             buf = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, pin_memory=True)
             self.slots[i] = buf
-        return i, buf
+            self.views[i] = buf.numpy()
+        return i, buf, self.views[i]
 
-    def mark(self, i):
+    def mark(self, i, stream=None):
         ev = self.events[i]
         if ev is None:
             ev = torch.cuda.Event()
             self.events[i] = ev
-        ev.record()
+        ev.record(stream)
 
 
 class TGN(nn.Module):
@@ -191,7 +193,7 @@ class TGN(nn.Module):
         self._ws = None
         self._ws_key = None
         self._stage = _Staging()
-        self._stage_dev = None
+        self._copy_stream = None       # created with the device ring on the first batch
         self._status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._last_pos = torch.zeros(self.n_nodes, dtype=torch.int64, device=self.device)
         # candidate bitmap of the uncached set, followed by the candidate list (length word + entries)
@@ -329,8 +331,7 @@ class TGN(nn.Module):
         n_i32 = 4 * b + n_plan
         off_ts = (n_i32 * 4 + 15) // 16 * 16
         total = off_ts + 8 * b
-        slot, host = self._stage.get(total)
-        hn = host.numpy()
+        slot, host, hn = self._stage.get(total)
         hi = hn[:n_i32 * 4].view(np.int32)
         hi[0:b] = source_nodes
         hi[b:2 * b] = destination_nodes
@@ -339,11 +340,31 @@ class TGN(nn.Module):
         if n_plan:
             hi[4 * b:] = cache_plan
         hn[off_ts:total].view(np.float64)[:] = edge_times
-        if self._stage_dev is None or self._stage_dev.numel() < total:
-            self._stage_dev = torch.empty(max(total, 1 << 16), dtype=torch.uint8, device=self.device)
-        dev = self._stage_dev
-        dev[:total].copy_(host[:total], non_blocking=True)
-        self._stage.mark(slot)
+        # The staged batch goes to the device on a copy stream of its own, into a ring of device buffers:
+        # the copy of this batch runs while the kernels of the previous one are still busy.  A device
+        # buffer is overwritten only after the batch that read it has finished (ev_free), the kernels
+        # start only after the copy (ev_copied).
+        cur = torch.cuda.current_stream(self.device)
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(self.device)
+            self._dev_ring = [None] * 4
+            self._ev_free = [None] * 4
+            self._ev_copied = [torch.cuda.Event() for _ in range(4)]
+            self._dev_i = 0
+        ds = self._dev_i
+        self._dev_i = (ds + 1) % 4
+        dev = self._dev_ring[ds]
+        if dev is None or dev.numel() < total:
+            dev = torch.empty(max(total, 1 << 16), dtype=torch.uint8, device=self.device)
+            self._dev_ring[ds] = dev
+            self._copy_stream.wait_stream(cur)      # a fresh buffer: ordered after everything enqueued so far
+        elif self._ev_free[ds] is not None:
+            self._copy_stream.wait_event(self._ev_free[ds])
+        _lib.check(L.orca_stage_h2d(dev.data_ptr(), host.data_ptr(), total, self._copy_stream.cuda_stream))
+        self._ev_copied[ds].record(self._copy_stream)
+        self._stage.mark(slot, self._copy_stream)
+        cur.wait_event(self._ev_copied[ds])
+        stream = cur.cuda_stream
         ws, u_cap = self._workspace(b, k)
         prob = torch.empty(2 * b, device=self.device)
         emb = torch.empty(3 * b, _lib.DIM, device=self.device) if want_emb else None
@@ -351,11 +372,22 @@ class TGN(nn.Module):
         base = dev.data_ptr()
         d_plan = base + 16 * b if cache_plan is not None else None
         if self._world > 1:
-            return self._eval_batch_sharded(desc, base, base + off_ts, b, d_plan, n_plan, u_cap, ws, want_emb)
+            prob, emb = self._eval_batch_sharded(desc, base, base + off_ts, b, d_plan, n_plan, u_cap, ws, want_emb)
+            self.last_scores = prob
+            self._release_dev(ds, cur)
+            return prob, emb
         _lib.check(L.orca_tgn_eval_batch(desc, base, base + off_ts, b, d_plan, n_plan, u_cap, ws.data_ptr(),
                                          ws.numel(), prob.data_ptr(), _lib.ptr(emb), self._status.data_ptr(),
-                                         _lib.stream_ptr(self.device)))
+                                         stream))
+        self.last_scores = prob     # [2b] = [pos | neg]: one contiguous tensor for callers that copy both
+        self._release_dev(ds, cur)
         return prob, emb
+
+    def _release_dev(self, ds, stream):
+        ev = self._ev_free[ds]
+        if ev is None:
+            ev = self._ev_free[ds] = torch.cuda.Event()
+        ev.record(stream)
 
     def _eval_batch_sharded(self, desc, d_i32, d_ts, b, d_plan, n_plan, u_cap, ws, want_emb):
         if self.n_layers != 2:
