@@ -158,6 +158,16 @@ __device__ __forceinline__ float4 ld_peer_f4(uint32_t local_saddr, uint32_t cta_
   return v;
 }
 
+__device__ __forceinline__ float4 ld_shared_f4(uint32_t saddr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr));
+  return v;
+}
+__device__ __forceinline__ void st_shared_f4(uint32_t saddr, float4 v) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+
 // x ~ head + tail, both bf16 (round to nearest even), for 8 consecutive K elements: one 16-byte chunk
 // of the head image and one of the tail image.  Packed conversions (two floats per instruction).
 __device__ __forceinline__ uint32_t pack_split(float x0, float x1, uint32_t &lo) {
@@ -255,9 +265,9 @@ __device__ __forceinline__ void tile_output(const Args &g, const float *tile, co
       mb[k] = __shfl_sync(0xffffffffu, meta_b, (it0 + k) & 31);
       const int rr = ok[k] ? r : 0;
       if (ksplit == 1) {
-        const float *trow_s = tile + rr * TILE_LD;
-        a[k] = add4(*reinterpret_cast<const float4 *>(trow_s + 4 * j0), bA);
-        b[k] = has1 ? add4(*reinterpret_cast<const float4 *>(trow_s + 4 * j1), bB) : f4z;
+        const uint32_t ra = tile_saddr + (uint32_t)(rr * TILE_LD + 4 * j0) * 4u;
+        a[k] = add4(ld_shared_f4(ra), bA);
+        b[k] = has1 ? add4(ld_shared_f4(ra + 512u), bB) : f4z;
       } else {
         const uint32_t ra = tile_saddr + (uint32_t)(rr * TILE_LD + 4 * j0) * 4u;
         float4 va = ld_peer_f4(ra, 0), vb = has1 ? ld_peer_f4(ra + 512u, 0) : f4z;
@@ -286,11 +296,7 @@ __device__ __forceinline__ void tile_output(const Args &g, const float *tile, co
     } else if (EPI == EPI_HIDDEN) {
 #pragma unroll
       for (int k = 0; k < RB; ++k)
-#ifdef ORCA_EXP_NOSTORE
-        if (ok[k] && a[k].x == 12345.678f) {
-#else
         if (ok[k]) {
-#endif
           const float rvf = ma[k] != 0 ? 1.f : 0.f;
           float *o = g.out + (size_t)m[k] * D;
           *reinterpret_cast<float4 *>(o + 4 * j0) =
@@ -591,7 +597,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
       const int quarter = warp & 3;
       const int row = quarter * 32 + lane;
       const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
-      float *trow_s = tile + row * TILE_LD;
+      const uint32_t trow_sa = base + (uint32_t)(row * TILE_LD) * 4u;   // the tile starts at the stage ring
       float dot = 0.f;
       const int ch0 = grp ? 6 : 0, ch1 = grp ? BN / 16 : 6;
       for (int ch = ch0; ch < ch1; ++ch) {
@@ -606,7 +612,8 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
         } else {
 #pragma unroll
           for (int q = 0; q < 4; ++q)
-            *reinterpret_cast<float4 *>(trow_s + ch * 16 + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+            st_shared_f4(trow_sa + (uint32_t)(ch * 16 + q * 4) * 4u,
+                         make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
         }
       }
       if (EPI == EPI_SCORE) s_dot[grp][row] = dot;
