@@ -40,6 +40,9 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-batches", type=int, default=None, help="batches of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="N > 1: strong = the workload's batch split over the GPUs (default); weak = a batch of "
+                         "bs edges PER GPU, i.e. the same stream cut into batches of bs * N edges")
     ap.add_argument("--plan-batches", type=int, default=None,
                     help="plan only this many leading batches of the stream (quick runs)")
     return ap.parse_args()
@@ -117,6 +120,10 @@ def build_setup(a, device, quiet=True):
     from orca_b200.tgn import TGN
     t0 = time.time()
     g = synthetic.make_graph(a.workload)
+    if a.scaling == "weak" and a.gpus > 1:
+        # same graph and stream, batches of bs edges per GPU (the batch size only cuts the stream)
+        import dataclasses
+        g.spec = dataclasses.replace(g.spec, bs=g.spec.bs * a.gpus)
     spec = g.spec
     neg = synthetic.negative_destinations(g, seed=0)
     nf = get_neighbor_finder(g, device=device)
@@ -338,10 +345,13 @@ def run_ours(a):
 
     value = edges / (ms_dev / 1e3)
     line = {"metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms_dev / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "ms_per_step": ms_dev / K, "higher_is_better": True, "scaling": a.scaling if world > 1 else "strong",
+            "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": workload_config(g, spec, first + W, {
                 "whole_step_hbm_frac": step_frac / world, "algorithmic_bytes_per_edge": step_bytes / edges,
+                **({"weak_scaling": f"batches of {spec.bs // world} edges per GPU: the stream is cut into batches "
+                                    f"of {spec.bs} edges"} if (world > 1 and a.scaling == "weak") else {}),
                 "sharding": "replicated tables; attention rows and scores split by row/edge % n_gpus; one NCCL "
                             "all-gather of the layer-1 rows per batch" if world > 1 else "single GPU"}),
             "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches_per_batch * K), "clocks": clocks,
