@@ -12,7 +12,11 @@
 
 namespace orca {
 
-constexpr int GA_THREADS = 256;
+#ifndef ORCA_GA_THREADS
+#define ORCA_GA_THREADS 256
+#endif
+constexpr int GA_THREADS = ORCA_GA_THREADS;
+constexpr int GA_SMEM_LIMIT = 226 * 1024;   // dynamic shared memory one block may ask for
 constexpr int GA_WARPS = GA_THREADS / 32;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -393,14 +397,15 @@ extern "C" int orca_attn_gather(const float *d_qt, const float *d_nbr_table, con
   ORCA_CHECK_ARG(((uintptr_t)d_qt % 16 == 0) && ((uintptr_t)d_nbr_table % 16 == 0) &&
                  ((uintptr_t)d_edge_table % 16 == 0));
   if (n_rows_cap == 0) return ORCA_OK;
-  const int warps = k <= 28 ? GA_WARPS : GA_WARPS / 2;
+  // two blocks per SM share its shared memory: as many warps per block as fit into half of it
+  const int warps = std::max(1, std::min(GA_WARPS, GA_SMEM_LIMIT / 2 / (ga_warp_floats(k) * (int)sizeof(float))));
   const size_t smem = (size_t)warps * ga_warp_floats(k) * sizeof(float);
   static thread_local int configured_device = -1;
   int dev = 0;
   ORCA_CUDA(cudaGetDevice(&dev));
   if (configured_device != dev) {
     ORCA_CUDA(cudaFuncSetAttribute(attn_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   GA_WARPS * ga_warp_floats(28) * (int)sizeof(float)));
+                                   GA_SMEM_LIMIT / 2));
     configured_device = dev;
   }
   if (g_prof.on) {
