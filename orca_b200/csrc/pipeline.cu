@@ -81,11 +81,6 @@ __global__ void batch_prep_kernel(const int32_t *__restrict__ batch, const doubl
   if (i == 0) *n1 = 3 * b;
 }
 
-__global__ void copy_i32_kernel(const int32_t *__restrict__ src, int32_t *__restrict__ dst, int n) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) dst[i] = src[i];
-}
-
 // History.update_flag with a plan (modules/history.py:25-30) in one block: clear the flags of the plan
 // that set them, set the flags of this batch's plan, and keep a copy of it for the next clearing
 __global__ void __launch_bounds__(1024)
