@@ -380,11 +380,11 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
 
   dep_trigger();
   int M = 0;   // live rows (known after the wait below)
-  // Loads that head a dependency chain go out first, before anything waits: the table row of tile
-  // row (pw*32 + lane) for the producers, and the per-row inputs of the output pass (warp w writes
-  // rows w, w+10, ...; lane i holds what row w + 10*i needs).  For the CTA's first tile they are
-  // issued before the live row count is known (rows up to m_cap: the arrays are sized for it) and
-  // discarded afterwards if the row is not live.
+  // Per-tile loads that head a dependency chain (issued right after the dependency wait below, together
+  // with the load of the live row count): the table row of tile row (pw*32 + lane) for the producers,
+  // and the per-row inputs of the output pass (warp w writes rows w, w+10, ...; lane i holds what row
+  // w + 10*i needs).  For the CTA's first tile they are issued before the live row count is known (rows
+  // up to m_cap: the arrays are sized for it) and discarded afterwards if the row is not live.
   int ri0 = -1, ri1 = -1, meta_a = 0, meta_b = 0;
   auto prefetch_rows = [&](int m0, int limit) {
     ri0 = ri1 = -1;

@@ -1,9 +1,9 @@
 """Generates the golden fixtures in this folder by running the UNMODIFIED reference.
 
-Run where the reference checkout is available (its location is taken from the environment
-variable ORCA_REFERENCE, default ``/root/reference``)::
+Run where a checkout of the reference is available; its location is given by the environment
+variable ORCA_REFERENCE::
 
-    python tests/golden/make_golden.py [case ...]
+    ORCA_REFERENCE=<path of the checkout> python tests/golden/make_golden.py [case ...]
 
 The reference is imported, never copied.  Settings needed for a repeatable run:
 
@@ -28,7 +28,9 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("ORCA_REFERENCE", "/root/reference")
+REF = os.environ.get("ORCA_REFERENCE")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set ORCA_REFERENCE to the path of a checkout of the reference")
 sys.path.insert(0, ROOT)
 sys.path.insert(0, REF)
 
