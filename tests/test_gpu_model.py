@@ -243,3 +243,65 @@ def test_unsupported_modes_fail_loudly():
     src, dst, ts, eidx = g.sources[:10], g.destinations[:10], g.timestamps[:10], g.edge_idxs[:10]
     with pytest.raises(NotImplementedError):
         tgn.compute_edge_probabilities(src, dst, dst, ts, eidx, 10, True, True, None)
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_sharded_entry_points_with_emulated_ranks(world):
+    """The row/edge split of the multi-GPU path for more ranks than GPUs at hand: every rank is a model
+    replica of its own on this GPU, the two phases are called rank after rank through the C ABI and the
+    all-gather between them is a stack of the ranks' layer-1 rows.  Scores and state must equal the
+    unsharded run."""
+    from orca_b200 import _lib, shard
+    L = _lib.lib()
+    g = graph("t_nb2")
+    spec = g.spec
+    gold = golden("t_nb2")
+    plan = unpack(gold[f"plan_{spec.strategy}_flat"], gold[f"plan_{spec.strategy}_off"])
+    ref = make_model(g)
+    ranks = [make_model(g) for _ in range(world)]
+    for r, m in enumerate(ranks):
+        m._rank, m._world = r, world
+    dev = ref.device
+    stream = _lib.stream_ptr(dev)
+    k = spec.n_degree
+    worst = 0.0
+    for b, src, dst, ts, eidx in batches(g, 8):
+        n = len(src)
+        neg = np.roll(dst, 3)
+        p_ref, q_ref = ref.compute_edge_probabilities(src, dst, neg, ts, eidx, k, True, False, plan[b])
+        ref.check_status()
+        pl = np.asarray(plan[b], dtype=np.int32)
+        ints = torch.from_numpy(np.concatenate([src, dst, neg, eidx, pl]).astype(np.int32)).to(dev)
+        tsd = torch.from_numpy(np.ascontiguousarray(ts, dtype=np.float64)).to(dev)
+        d_plan = ints.data_ptr() + 16 * n
+        locals_, ctx = [], []
+        for m in ranks:
+            desc = m._descriptor(k)
+            ws, u_cap = m._workspace(n, k)
+            rpr = shard.rows_per_rank(3 * n + u_cap, world)
+            emb1 = torch.zeros(rpr, 172, device=dev)
+            _lib.check(L.orca_tgn_eval_batch_sharded(desc, 1, ints.data_ptr(), tsd.data_ptr(), n, d_plan, len(pl),
+                                                     u_cap, ws.data_ptr(), ws.numel(), emb1.data_ptr(), None, None,
+                                                     None, m._status.data_ptr(), stream))
+            locals_.append(emb1)
+            ctx.append((desc, ws, u_cap))
+        emb1_all = torch.stack(locals_).contiguous()
+        p = torch.zeros(n, device=dev)
+        q = torch.zeros(n, device=dev)
+        for r, m in enumerate(ranks):
+            desc, ws, u_cap = ctx[r]
+            n_loc = shard.local_count(n, r, world)
+            prob = torch.zeros(2 * shard.rows_per_rank(n, world), device=dev)
+            _lib.check(L.orca_tgn_eval_batch_sharded(desc, 2, ints.data_ptr(), tsd.data_ptr(), n, d_plan, len(pl),
+                                                     u_cap, ws.data_ptr(), ws.numel(), None, emb1_all.data_ptr(),
+                                                     prob.data_ptr(), None, m._status.data_ptr(), stream))
+            m.check_status()
+            e = torch.arange(r, n, world, device=dev)
+            p[e] = prob[:n_loc]
+            q[e] = prob[n_loc:2 * n_loc]
+        worst = max(worst, float((p - p_ref.view(-1)).abs().max()), float((q - q_ref.view(-1)).abs().max()))
+    assert worst < 1e-6, worst
+    for m in ranks:
+        assert torch.equal(m.memory.memory, ref.memory.memory)
+        assert torch.equal(m.embedding_module.histories[0].emb, ref.embedding_module.histories[0].emb)
+        assert np.array_equal(m.embedding_module.histories[0].cache_flag, ref.embedding_module.histories[0].cache_flag)

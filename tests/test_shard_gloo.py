@@ -63,3 +63,9 @@ def _worker(rank, world, port, b, cap):
 @pytest.mark.parametrize("b,cap", [(200, 1260), (7, 50)])
 def test_two_rank_exchange_reassembles(b, cap):
     mp.spawn(_worker, args=(2, _free_port(), b, cap), nprocs=2, join=True)
+
+
+@pytest.mark.parametrize("world,b,cap", [(4, 203, 1270), (3, 10, 64)])
+def test_more_ranks_exchange_reassembles(world, b, cap):
+    """Row counts that do not divide by the number of ranks, four and three ranks."""
+    mp.spawn(_worker, args=(world, _free_port(), b, cap), nprocs=world, join=True)
