@@ -81,36 +81,6 @@ __global__ void batch_prep_kernel(const int32_t *__restrict__ batch, const doubl
   if (i == 0) *n1 = 3 * b;
 }
 
-// History.update_flag with a plan (modules/history.py:25-30) in one block: clear the flags of the plan
-// that set them, set the flags of this batch's plan, and keep a copy of it for the next clearing
-__global__ void __launch_bounds__(1024)
-plan_flags_kernel(uint8_t *__restrict__ flag, int64_t n_nodes, int32_t *__restrict__ prev_plan, int n_prev,
-                  const int32_t *__restrict__ plan, int n_plan) {
-  dep_trigger();
-  dep_wait();
-  // eight independent loads per thread in flight: the loop is a chain of L2 round trips otherwise
-  for (int i0 = threadIdx.x; i0 < n_prev; i0 += 8 * 1024) {
-    int v[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) v[u] = i0 + u * 1024 < n_prev ? prev_plan[i0 + u * 1024] : -1;
-#pragma unroll
-    for (int u = 0; u < 8; ++u)
-      if (v[u] >= 0 && v[u] < n_nodes) flag[v[u]] = 0;
-  }
-  __threadfence();
-  __syncthreads();
-  for (int i0 = threadIdx.x; i0 < n_plan; i0 += 8 * 1024) {
-    int v[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) v[u] = i0 + u * 1024 < n_plan ? plan[i0 + u * 1024] : -1;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      if (v[u] >= 0 && v[u] < n_nodes) flag[v[u]] = 1;
-      if (i0 + u * 1024 < n_plan) prev_plan[i0 + u * 1024] = v[u];
-    }
-  }
-}
-
 __global__ void set_flags_counted_kernel(uint8_t *__restrict__ flag, int64_t n_nodes,
                                          const int32_t *__restrict__ ids, int cap, const int32_t *d_n) {
   const int n = rows_of(cap, d_n);
@@ -497,12 +467,12 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
                                                        reinterpret_cast<const unsigned long long *>(m->last_pos),
                                                        *m->epoch_base - R1, N, w.n1, world, rpr);
   ORCA_COUNT_LAUNCH();
+  bool side_flags = false;   // History.update_flag with a plan rides on the message-winner launch below
+  int side_prev = 0;
   if (d_plan != nullptr) {
-    const bool know_prev = *m->n_prev_plan >= 0;
-    if (!know_prev) ORCA_CUDA(cudaMemsetAsync(m->cache_flag, 0, (size_t)m->n_nodes, s));
-    plan_flags_kernel<<<1, 1024, 0, s>>>(m->cache_flag, m->n_nodes, m->prev_plan, know_prev ? *m->n_prev_plan : 0,
-                                         d_plan, n_plan);
-    ORCA_COUNT_LAUNCH();
+    side_prev = *m->n_prev_plan >= 0 ? *m->n_prev_plan : 0;
+    if (*m->n_prev_plan < 0) ORCA_CUDA(cudaMemsetAsync(m->cache_flag, 0, (size_t)m->n_nodes, s));
+    side_flags = true;
     *m->n_prev_plan = n_plan;
   } else {
     set_flags_counted_kernel<<<std::min(ceil_div(R1, 256), 1024), 256, 0, s>>>(m->cache_flag, m->n_nodes,
@@ -520,7 +490,8 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
   }
   cudaStream_t ms = forked ? g_overlap.aux : s;
   ORCA_TRY(launch_last_occ_compact(d_batch_i32, 2 * b, m->n_nodes, m->last_pos, *m->epoch_base, w.win_pos, w.n_win,
-                                   nullptr, nullptr, nullptr, 0, nullptr, 0, ms));
+                                   nullptr, side_flags ? m->cache_flag : nullptr, m->prev_plan, side_prev, d_plan,
+                                   n_plan, ms));
   *m->epoch_base += 2 * b;
   ORCA_TRY(orca_message_store(&m->mem, m->edge_table, m->time_w, d_batch_i32, w.cat_dst, d_batch_ts,
                               d_batch_i32 + 3 * b, b, w.win_pos, 2 * b, w.n_win, w.win_nodes, ms));
