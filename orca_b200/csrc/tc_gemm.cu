@@ -444,6 +444,10 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   };
   auto fix_rows = [&](int m0) {   // after the live count is known
     if (producer && m0 + pw * 32 + lane >= M) ri0 = ri1 = -1;
+  };
+  // (called after the tile's first stage has been requested: the lookup is two dependent loads and its
+  // result is only needed by the output pass)
+  auto push_winners = [&](int m0) {
     if (EPI == EPI_LAYERNORM && g.push_table != nullptr && g.push_win == nullptr) {
       // winners by record; only for live rows: the id of a row past the live count is not a valid index
       const int r = crank + ksplit * (warp + (THREADS / 32) * lane);
@@ -498,6 +502,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
 
   fix_rows(blockIdx.y * BM);
   if ((int)blockIdx.y * BM < M && producer && grp < nkb) load_stage(grp);   // in flight across the barrier
+  push_winners(blockIdx.y * BM);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -517,6 +522,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
       prefetch_rows(m0, M);
       fix_rows(m0);
       if (producer && grp < nkb) load_stage(grp);
+      push_winners(m0);
     }
     if (producer) {
       // ---------------------------------------------------------------- producer groups
