@@ -40,6 +40,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-batches", type=int, default=None, help="batches of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="direct", choices=["direct", "nccl"],
+                    help="N > 1: how the layer-1 rows travel between the GPUs (peer stores or an NCCL all-gather)")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="N > 1: strong = the workload's batch split over the GPUs (default); weak = a batch of "
                          "bs edges PER GPU, i.e. the same stream cut into batches of bs * N edges")
@@ -210,7 +212,7 @@ def run_ours(a):
     L = _lib.lib()
     g, neg, plan, tgn = build_setup(a, device, quiet=rank != 0)
     if world > 1:
-        tgn.set_distributed(rank, world)
+        tgn.set_distributed(rank, world, exchange=a.exchange)
     spec = g.spec
     K, W = a.steps, a.warmup
     nb_avail = len(plan)
@@ -287,16 +289,17 @@ def run_ours(a):
             # sharded attention layers and scores, NCCL all-gather of the layer-1 rows in between;
             # the scores stay sharded (every rank keeps those of its edges)
             from orca_b200 import shard
+            direct = tgn._exchange is not None     # rows exchanged by peer stores inside the library
             rpr = shard.rows_per_rank(3 * n + u_cap, world)
-            emb1_local = torch.empty(rpr, 172, device=device)
+            emb1_local = None if direct else torch.empty(rpr, 172, device=device)
             _lib.check(L.orca_tgn_eval_batch_sharded(desc, 1, ints.data_ptr(), ts.data_ptr(), n,
                                                      ints.data_ptr() + 16 * n, n_plan, u_cap, ws.data_ptr(),
-                                                     ws.numel(), emb1_local.data_ptr(), None, None, None,
+                                                     ws.numel(), _lib.ptr(emb1_local), None, None, None,
                                                      tgn._status.data_ptr(), stream))
-            emb1_all = shard.all_gather_rows(emb1_local)
+            emb1_all = None if direct else shard.all_gather_rows(emb1_local)
             _lib.check(L.orca_tgn_eval_batch_sharded(desc, 2, ints.data_ptr(), ts.data_ptr(), n,
                                                      ints.data_ptr() + 16 * n, n_plan, u_cap, ws.data_ptr(),
-                                                     ws.numel(), None, emb1_all.data_ptr(), probs[i].data_ptr(),
+                                                     ws.numel(), None, _lib.ptr(emb1_all), probs[i].data_ptr(),
                                                      None, tgn._status.data_ptr(), stream))
             return
         _lib.check(L.orca_tgn_eval_batch(desc, ints.data_ptr(), ts.data_ptr(), n, ints.data_ptr() + 16 * n, n_plan,
@@ -352,8 +355,9 @@ def run_ours(a):
                 "whole_step_hbm_frac": step_frac / world, "algorithmic_bytes_per_edge": step_bytes / edges,
                 **({"weak_scaling": f"batches of {spec.bs // world} edges per GPU: the stream is cut into batches "
                                     f"of {spec.bs} edges"} if (world > 1 and a.scaling == "weak") else {}),
-                "sharding": "replicated tables; attention rows and scores split by row/edge % n_gpus; one NCCL "
-                            "all-gather of the layer-1 rows per batch" if world > 1 else "single GPU"}),
+                "sharding": ("replicated tables; attention rows and scores split by row/edge % n_gpus; layer-1 rows "
+                             + ("written to every GPU by peer stores over NVLink" if a.exchange == "direct"
+                                else "all-gathered with NCCL") + " once per batch") if world > 1 else "single GPU"}),
             "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches_per_batch * K), "clocks": clocks,
             "host_enqueue_ms_per_step": {"e2e": host_ms[0] / K, "value": host_ms[1] / K},
             "phases_us_per_step": phases}

@@ -38,6 +38,7 @@ extern "C" {
 #define ORCA_DIM 172
 #define ORCA_HEADS 2
 #define ORCA_MAX_K 32
+#define ORCA_MAX_WORLD 8   /* GPUs of one node */
 #define ORCA_CAND_CAP 2048 /* listed candidates of the uncached set; more fall back to a bitmap scan */
 #define ORCA_MSG_DIM (4 * ORCA_DIM)          /* [mem_src | mem_dst | edge feat | time enc] */
 #define ORCA_KEY_DIM (3 * ORCA_DIM)          /* [neighbour | edge feat | time enc]         */
@@ -336,6 +337,14 @@ typedef struct {
   uint32_t *cand_bitmap;    /* (n_nodes+31)/32 + 1 + ORCA_CAND_CAP words (candidate bitmap, list    */
                             /* length, list), zero-initialised once by the caller                */
   int32_t mode;             /* ORCA_MODE_*: which recursion of the embedding module runs        */
+  /* Direct exchange of the layer-1 rows between the GPUs of one node (orca_tgn_eval_batch_sharded; all
+   * NULL / 0: the caller all-gathers).  peer_rows[r] / peer_flags[r]: rank r's exchange buffer (2 halves of
+   * exchange_cap floats, used alternately) and flag words (int32[ORCA_MAX_WORLD + 1], zero-initialised) as
+   * mapped into THIS process (own rank included, peers through CUDA IPC). */
+  float *peer_rows[ORCA_MAX_WORLD];
+  int32_t *peer_flags[ORCA_MAX_WORLD];
+  int64_t exchange_cap;
+  int64_t *exchange_seq;    /* host-resident batch sequence counter owned by the caller (starts at 0) */
 } orca_tgn_t;
 
 /* Workspace sizing: bytes needed for batches of up to b_cap edges with at most u_cap uncached
@@ -373,6 +382,13 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
                                 int32_t u_cap, void *d_workspace, int64_t workspace_bytes,
                                 float *d_emb1_local, const float *d_emb1_all, float *d_prob_local,
                                 float *d_emb2_local, int32_t *d_status, void *stream);
+
+/* Sharing the exchange buffer of the multi-GPU split between the processes of one node (no counterpart
+ * in the reference).  orca_ipc_export: the 64-byte CUDA IPC handle of the allocation that holds d_ptr and
+ * d_ptr's offset inside it; orca_ipc_open (in another process, on its own GPU): the address of the same
+ * memory there, with peer access enabled.  A handle may be opened once per process. */
+int orca_ipc_export(const void *d_ptr, void *h_handle64, int64_t *h_offset);
+int orca_ipc_open(const void *h_handle64, int64_t offset, void **h_ptr_out);
 
 /* Asynchronous copy of a staged batch from pinned host memory to the device on `stream` (what
  * `tensor.to(device)` does for the batch arrays in evaluation/evaluation.py:34 of the reference; here

@@ -58,6 +58,10 @@ class TgnT(C.Structure):
         ("rank", C.c_int32), ("world", C.c_int32),
         ("cand_bitmap", C.c_void_p),
         ("mode", C.c_int32),
+        ("peer_rows", C.c_void_p * 8),
+        ("peer_flags", C.c_void_p * 8),
+        ("exchange_cap", C.c_int64),
+        ("exchange_seq", C.POINTER(C.c_int64)),
     ]
 
 
@@ -95,6 +99,8 @@ SYMBOLS = {
     "orca_tgn_eval_batch_sharded": (C.c_int, [C.POINTER(TgnT), _I32, _V, _V, _I32, _V, _I32, _I32, _V, _I64, _V, _V,
                                               _V, _V, _V, _V]),
     "orca_stage_h2d": (C.c_int, [_V, _V, C.c_int64, _V]),
+    "orca_ipc_export": (C.c_int, [_V, _V, C.POINTER(C.c_int64)]),
+    "orca_ipc_open": (C.c_int, [_V, C.c_int64, C.POINTER(C.c_void_p)]),
     "orca_set_overlap": (C.c_int, [_I32]),
     "orca_set_dependent_launch": (C.c_int, [_I32]),
     "orca_trace": (C.c_int, [_I32]),

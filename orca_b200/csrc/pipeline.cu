@@ -2,6 +2,7 @@
 // sample -> find uncached -> sample -> attention layer 1 (memory rows) -> history push / flags ->
 // attention layer 2 (history rows) -> link scores -> raw messages -> GRU memory update.
 #include <algorithm>
+#include <cstring>
 #include <vector>
 
 #include "common.cuh"
@@ -150,6 +151,62 @@ __global__ void expand_rows_kernel(const int32_t *__restrict__ nbr2, int n, int 
   nodes1[n + i] = v;
   ts1[n + i] = ts1[i / k];
   idx2[i] = v != 0 ? n + i : 0;
+}
+
+// ---- direct exchange of the layer-1 rows between the GPUs of a node (peer stores over NVLink)
+struct Peers {
+  float *rows[ORCA_MAX_WORLD];
+  int32_t *flags[ORCA_MAX_WORLD];
+};
+
+// Every rank copies its live layer-1 rows into slot `rank` of every rank's exchange buffer (its own
+// included), then -- once the last block's stores are fenced system-wide -- posts the batch sequence
+// number in word `rank` of every rank's flag array.  flags[rank][ORCA_MAX_WORLD] of the own array counts
+// the finished blocks.
+__global__ void __launch_bounds__(256)
+exchange_fanout_kernel(const float *__restrict__ src, const int32_t *__restrict__ n_loc, int rpr, Peers p,
+                       int world, int rank, long long off, int seq) {
+  dep_trigger();
+  dep_wait();
+  const int n = min(*n_loc, rpr);
+  const long long total = (long long)n * (D / 4);
+  const float4 *s4 = reinterpret_cast<const float4 *>(src);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = s4[i];
+    for (int q = 0; q < world; ++q) reinterpret_cast<float4 *>(p.rows[q] + off)[i] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int32_t *counter = p.flags[rank] + ORCA_MAX_WORLD;
+    const int prev = atomicAdd(counter, 1);
+    if (prev == (int)gridDim.x - 1) {
+      *counter = 0;
+      __threadfence_system();
+      for (int q = 0; q < world; ++q)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.flags[q] + rank), "r"(seq) : "memory");
+    }
+  }
+}
+
+// Waits (bounded: about a second of SM clocks) until every rank has posted `seq`; a rank that did not
+// sets ORCA_E_TIMEOUT in the status word and the batch goes on with whatever the buffer holds.
+__global__ void exchange_wait_kernel(const int32_t *__restrict__ flags, int world, int seq, int32_t *status) {
+  dep_trigger();
+  dep_wait();
+  const int q = threadIdx.x;
+  if (q < world) {
+    const long long t0 = clock64();
+    for (;;) {
+      int v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + q) : "memory");
+      if (v >= seq) break;
+      if (clock64() - t0 > 2000000000ll) {
+        report(status, ORCA_E_TIMEOUT, 500 + q);
+        break;
+      }
+    }
+  }
 }
 
 __global__ void publish_counts_kernel(const int32_t *n1, const int32_t *n_win, int32_t *status) {
@@ -435,8 +492,16 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
   const int rpr = ceil_div(R1, world);
   const int b_loc = (b - rank + world - 1) / world;
 
+  const bool direct = m->peer_rows[rank] != nullptr;   // rows exchanged by peer stores, not by the caller
+  if (direct) {
+    ORCA_CHECK_ARG(world <= ORCA_MAX_WORLD && m->exchange_seq != nullptr && m->peer_flags[rank] != nullptr);
+    if ((int64_t)world * rpr * D > m->exchange_cap)
+      return set_error(ORCA_E_CAPACITY, "orca_tgn_eval_batch_sharded: exchange buffer of %lld floats, %lld needed",
+                       (long long)m->exchange_cap, (long long)world * rpr * D);
+  }
   if (phase == 1) {
-    ORCA_CHECK_ARG(d_emb1_local != nullptr);
+    ORCA_CHECK_ARG(direct || d_emb1_local != nullptr);
+    if (d_emb1_local == nullptr) d_emb1_local = w.emb1;
     launch_counter() = 0;
     // replicated index work: every rank must find the same uncached set and the same winners (row list,
     // top-level table, candidates and last-occurrence records in one launch, as on one GPU)
@@ -457,9 +522,30 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
                               w.n1_loc, w.ctx, w.valid, d_status, s));
     ORCA_TRY(orca_attn_output(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.loc_nodes, rpr, w.n1_loc,
                               d_emb1_local, nullptr, nullptr, nullptr, w.hidden, s));
+    if (direct) {
+      const long long seq = ++*m->exchange_seq;
+      Peers p{};
+      for (int q = 0; q < world; ++q) {
+        ORCA_CHECK_ARG(m->peer_rows[q] != nullptr && m->peer_flags[q] != nullptr);
+        p.rows[q] = m->peer_rows[q];
+        p.flags[q] = m->peer_flags[q];
+      }
+      const long long off = (seq & 1) * m->exchange_cap + (long long)rank * rpr * D;
+      ORCA_CUDA(launch_dep(exchange_fanout_kernel, std::min(ceil_div(rpr * (D / 4), 256), 148), 256, 0, s,
+                           (const float *)d_emb1_local, (const int32_t *)w.n1_loc, rpr, p, world, rank, off,
+                           (int)seq));
+      ORCA_COUNT_LAUNCH();
+    }
     return ORCA_OK;
   }
 
+  if (direct) {
+    const long long seq = *m->exchange_seq;
+    ORCA_CUDA(launch_dep(exchange_wait_kernel, 1, 32, 0, s, (const int32_t *)m->peer_flags[rank], world, (int)seq,
+                         d_status));
+    ORCA_COUNT_LAUNCH();
+    d_emb1_all = m->peer_rows[rank] + (seq & 1) * m->exchange_cap;
+  }
   ORCA_CHECK_ARG(d_emb1_all != nullptr && d_prob_local != nullptr);
   // every replica of the history table receives every layer-1 row
   // (winners by the records phase 1 made: it advanced the epoch by R1 and nothing recorded since)
@@ -518,6 +604,41 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   g_last_batch_launches = launch_counter();
+  return ORCA_OK;
+}
+
+int orca_ipc_export(const void *d_ptr, void *h_handle, int64_t *h_offset) {
+  ORCA_CHECK_ARG(d_ptr && h_handle && h_offset);
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaPointerAttributes attr;
+  ORCA_CUDA(cudaPointerGetAttributes(&attr, d_ptr));
+  ORCA_CHECK_ARG(attr.type == cudaMemoryTypeDevice);
+  // d_ptr may sit inside a pooled allocation: the handle names the allocation, the offset finds the buffer.
+  // The range query lives in the driver API; the runtime hands out its entry point.
+  typedef int (*range_fn)(unsigned long long *, size_t *, unsigned long long);
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult qr;
+  ORCA_CUDA(cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qr));
+  ORCA_CHECK_ARG(fn != nullptr);
+  unsigned long long base = 0;
+  size_t size = 0;
+  if (((range_fn)fn)(&base, &size, (unsigned long long)(uintptr_t)d_ptr) != 0)
+    return set_error(ORCA_E_CUDA, "orca_ipc_export: address range query failed");
+  cudaIpcMemHandle_t h;
+  ORCA_CUDA(cudaIpcGetMemHandle(&h, (void *)(uintptr_t)base));
+  memcpy(h_handle, &h, sizeof(h));
+  *h_offset = (int64_t)((unsigned long long)(uintptr_t)d_ptr - base);
+  return ORCA_OK;
+}
+
+int orca_ipc_open(const void *h_handle, int64_t offset, void **h_ptr_out) {
+  ORCA_CHECK_ARG(h_handle && h_ptr_out && offset >= 0);
+  cudaIpcMemHandle_t h;
+  memcpy(&h, h_handle, sizeof(h));
+  void *base = nullptr;
+  // opened from the calling process's current device: peer access to the owner is enabled on the way
+  ORCA_CUDA(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+  *h_ptr_out = (char *)base + offset;
   return ORCA_OK;
 }
 

@@ -203,14 +203,59 @@ class TGN(nn.Module):
         self._dummy_prev = np.full(1, -1, dtype=np.int32)
         self.last_counts = None
         self._rank, self._world, self._group = 0, 1, None
+        self._exchange = None          # direct exchange buffers of the multi-GPU split (set_distributed)
         self._mode = MODE_BUDGET
 
-    def set_distributed(self, rank, world, group=None):
+    def set_distributed(self, rank, world, group=None, exchange="direct"):
         """Shard every batch's attention rows and link scores over `world` GPUs of one node (one
         process per GPU, torch.distributed initialised by the caller, NCCL).  Every rank keeps full
-        replicas and must be fed the same batches; results are identical on all ranks."""
+        replicas and must be fed the same batches; results are identical on all ranks.
+
+        exchange="direct": the layer-1 rows travel by peer stores over NVLink into exchange buffers that
+        the ranks map into each other through CUDA IPC (handles are swapped here, once);
+        exchange="nccl": one all-gather per batch instead."""
         self._rank, self._world, self._group = int(rank), int(world), group
         self._ws_key = None
+        self._desc_ref = None
+        self._exchange = None
+        if self._world > 1 and exchange == "direct":
+            import torch.distributed as dist
+            cap = self.exchange_floats(int(self.args.bs), self._world)
+            # one allocation per rank: 2 * cap floats of rows, then 16 flag words
+            xbuf = torch.zeros(2 * cap + 16, dtype=torch.float32, device=self.device)
+            torch.cuda.synchronize(self.device)
+            L = _lib.lib()
+            handle = (C.c_ubyte * 64)()
+            off = C.c_int64(0)
+            _lib.check(L.orca_ipc_export(xbuf.data_ptr(), handle, C.byref(off)))
+            handles = [None] * self._world
+            dist.all_gather_object(handles, (bytes(handle), int(off.value)), group=group)
+            rows, flags, keep = [], [], [xbuf]
+            for r in range(self._world):
+                if r == self._rank:
+                    base = xbuf.data_ptr()
+                else:
+                    h = (C.c_ubyte * 64).from_buffer_copy(handles[r][0])
+                    out = C.c_void_p(0)
+                    _lib.check(L.orca_ipc_open(h, handles[r][1], C.byref(out)))
+                    base = out.value
+                rows.append(base)
+                flags.append(base + 8 * cap)      # byte offset of the flag words: 2 * cap floats
+            self.set_exchange(rows, flags, cap, keep)
+            dist.barrier(group=group)
+
+    @staticmethod
+    def exchange_floats(bs, world):
+        """Floats per half of an exchange buffer for batches of up to `bs` edges: `world` slots of
+        rows_per_rank(3*bs + 3*bs) rows (the sharded path bounds the uncached set by 3*bs)."""
+        return world * shard.rows_per_rank(6 * bs, world) * _lib.DIM
+
+    def set_exchange(self, row_ptrs, flag_ptrs, cap, keep_alive=()):
+        """Device addresses, as seen by this process, of every rank's exchange buffer (2 * cap floats)
+        and flag words (int32[16], zeroed)."""
+        self._exchange = (list(row_ptrs), list(flag_ptrs), int(cap), list(keep_alive))
+        self._exchange_seq = np.zeros(1, dtype=np.int64)
+        self._desc_ref = None
 
     # ---- weights ------------------------------------------------------------------------------
     def load_state_dict(self, state_dict, strict=True, **kw):
@@ -271,6 +316,13 @@ class TGN(nn.Module):
             t.mode = self._mode
             return t
         t = _lib.TgnT()
+        if getattr(self, "_exchange", None) is not None:
+            rows, flags, cap, _ = self._exchange
+            for r in range(len(rows)):
+                t.peer_rows[r] = rows[r]
+                t.peer_flags[r] = flags[r]
+            t.exchange_cap = cap
+            t.exchange_seq = self._exchange_seq.ctypes.data_as(C.POINTER(C.c_int64))
         self._desc_ref, self._desc = (nf, w, gw, k), t
         t.indptr, t.adj_nbr, t.adj_eid, t.adj_ts = (nf.indptr.data_ptr(), nf.adj_nbr.data_ptr(),
                                                     nf.adj_eid.data_ptr(), nf.adj_ts.data_ptr())
@@ -397,15 +449,16 @@ class TGN(nn.Module):
         rpr = shard.rows_per_rank(3 * b + u_cap, world)
         b_max = shard.rows_per_rank(b, world)
         s = _lib.stream_ptr(self.device)
-        emb1_local = torch.empty(rpr, _lib.DIM, device=self.device)
+        direct = getattr(self, "_exchange", None) is not None
+        emb1_local = None if direct else torch.empty(rpr, _lib.DIM, device=self.device)
         _lib.check(L.orca_tgn_eval_batch_sharded(desc, 1, d_i32, d_ts, b, d_plan, n_plan, u_cap, ws.data_ptr(),
-                                                 ws.numel(), emb1_local.data_ptr(), None, None, None,
+                                                 ws.numel(), _lib.ptr(emb1_local), None, None, None,
                                                  self._status.data_ptr(), s))
-        emb1_all = shard.all_gather_rows(emb1_local, self._group)
+        emb1_all = None if direct else shard.all_gather_rows(emb1_local, self._group)
         prob_local = torch.zeros(2 * b_max, device=self.device)
         emb2_local = torch.zeros(3 * b_max, _lib.DIM, device=self.device) if want_emb else None
         _lib.check(L.orca_tgn_eval_batch_sharded(desc, 2, d_i32, d_ts, b, d_plan, n_plan, u_cap, ws.data_ptr(),
-                                                 ws.numel(), None, emb1_all.data_ptr(), prob_local.data_ptr(),
+                                                 ws.numel(), None, _lib.ptr(emb1_all), prob_local.data_ptr(),
                                                  _lib.ptr(emb2_local), self._status.data_ptr(), s))
         prob = shard.assemble_edges(shard.all_gather_rows(prob_local, self._group), b, 2)
         emb = shard.assemble_edges(shard.all_gather_rows(emb2_local, self._group), b, 3) if want_emb else None

@@ -245,12 +245,13 @@ def test_unsupported_modes_fail_loudly():
         tgn.compute_edge_probabilities(src, dst, dst, ts, eidx, 10, True, True, None)
 
 
-@pytest.mark.parametrize("world", [4, 8])
-def test_sharded_entry_points_with_emulated_ranks(world):
+@pytest.mark.parametrize("world,direct", [(4, False), (8, False), (2, True), (8, True)])
+def test_sharded_entry_points_with_emulated_ranks(world, direct):
     """The row/edge split of the multi-GPU path for more ranks than GPUs at hand: every rank is a model
-    replica of its own on this GPU, the two phases are called rank after rank through the C ABI and the
-    all-gather between them is a stack of the ranks' layer-1 rows.  Scores and state must equal the
-    unsharded run."""
+    replica of its own on this GPU, the two phases are called rank after rank through the C ABI (all ranks'
+    phase 1 before any phase 2, so no kernel ever waits for a later launch).  The exchange between the
+    phases is a stack of the ranks' layer-1 rows, or -- direct -- the library's own peer stores into every
+    replica's exchange buffer.  Scores and state must equal the unsharded run."""
     from orca_b200 import _lib, shard
     L = _lib.lib()
     g = graph("t_nb2")
@@ -262,6 +263,14 @@ def test_sharded_entry_points_with_emulated_ranks(world):
     for r, m in enumerate(ranks):
         m._rank, m._world = r, world
     dev = ref.device
+    if direct:
+        # the ranks' exchange buffers and flag words; on one GPU a "peer" address is a plain device address
+        from orca_b200.tgn import TGN
+        cap = TGN.exchange_floats(spec.bs, world)
+        bufs = [torch.zeros(2 * cap, device=dev) for _ in range(world)]
+        flags = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(world)]
+        for m in ranks:
+            m.set_exchange([x.data_ptr() for x in bufs], [f.data_ptr() for f in flags], cap, bufs + flags)
     stream = _lib.stream_ptr(dev)
     k = spec.n_degree
     worst = 0.0
@@ -281,7 +290,8 @@ def test_sharded_entry_points_with_emulated_ranks(world):
             rpr = shard.rows_per_rank(3 * n + u_cap, world)
             emb1 = torch.zeros(rpr, 172, device=dev)
             _lib.check(L.orca_tgn_eval_batch_sharded(desc, 1, ints.data_ptr(), tsd.data_ptr(), n, d_plan, len(pl),
-                                                     u_cap, ws.data_ptr(), ws.numel(), emb1.data_ptr(), None, None,
+                                                     u_cap, ws.data_ptr(), ws.numel(),
+                                                     None if direct else emb1.data_ptr(), None, None,
                                                      None, m._status.data_ptr(), stream))
             locals_.append(emb1)
             ctx.append((desc, ws, u_cap))
@@ -293,7 +303,8 @@ def test_sharded_entry_points_with_emulated_ranks(world):
             n_loc = shard.local_count(n, r, world)
             prob = torch.zeros(2 * shard.rows_per_rank(n, world), device=dev)
             _lib.check(L.orca_tgn_eval_batch_sharded(desc, 2, ints.data_ptr(), tsd.data_ptr(), n, d_plan, len(pl),
-                                                     u_cap, ws.data_ptr(), ws.numel(), None, emb1_all.data_ptr(),
+                                                     u_cap, ws.data_ptr(), ws.numel(), None,
+                                                     None if direct else emb1_all.data_ptr(),
                                                      prob.data_ptr(), None, m._status.data_ptr(), stream))
             m.check_status()
             e = torch.arange(r, n, world, device=dev)
