@@ -477,6 +477,8 @@ __global__ void win_from_last_pos_kernel(const int32_t *__restrict__ ids, int ca
     win[i] = (i >= all_from || last_pos[ids[i]] == (unsigned long long)(base + i)) ? 1 : 0;
 }
 
+bool projections_on_tensor_cores() { return g_projection_mode == 0; }
+
 // d_push_win given: rows with a non-zero byte are pushed.  Otherwise (d_last_pos given) row i is
 // pushed when i >= all_from or when last_pos[push_ids[i]] == base + i; `d_push_win` is then only
 // scratch for the fp32 debug path and may be NULL in tensor-core mode.  rows_hint (> 0): the live row
@@ -485,7 +487,7 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
                      const int32_t *d_idx, int32_t n_rows_cap, const int32_t *d_n_rows, float *d_out,
                      float *d_push_table, const int32_t *d_push_ids, const uint8_t *d_push_win,
                      const int64_t *d_last_pos, long long base, int all_from, float *d_scratch_hidden,
-                     int rows_hint, cudaStream_t stream) {
+                     int rows_hint, cudaStream_t stream, const tc::PeerOut *peer) {
   ORCA_CHECK_ARG(w && w->G && w->b1 && w->g && w->W2t && w->b2 && w->ln_w && w->ln_b);
   ORCA_CHECK_ARG(d_ctx && d_valid && d_feat && d_out && n_rows_cap >= 0);
   if (n_rows_cap == 0) return ORCA_OK;
@@ -541,6 +543,7 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
     b.push_last_pos = reinterpret_cast<const unsigned long long *>(d_last_pos);
     b.push_base = base;
     b.push_all_from = all_from;
+    if (peer != nullptr) b.peer = *peer;
     return tc::launch(tc::EPI_LAYERNORM, b, 1, (cudaStream_t)stream);
   }
   int rc = ensure_f2_smem();

@@ -520,9 +520,26 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
     ORCA_TRY(orca_attn_query(&m->attn[0], m->mem.memory, w.loc_nodes, rpr, w.n1_loc, w.qt, s));
     ORCA_TRY(orca_attn_gather(w.qt, m->mem.memory, m->edge_table, m->time_w, w.nbr1, w.eid1, w.dt1, k, rpr,
                               w.n1_loc, w.ctx, w.valid, d_status, s));
+    if (direct && projections_on_tensor_cores()) {
+      // the LayerNorm epilogue of layer 1 delivers the rows itself: one kernel computes and exchanges
+      const long long seq = ++*m->exchange_seq;
+      tc::PeerOut po{};
+      for (int q = 0; q < world; ++q) {
+        ORCA_CHECK_ARG(m->peer_rows[q] != nullptr && m->peer_flags[q] != nullptr);
+        po.rows[q] = m->peer_rows[q];
+        po.flags[q] = m->peer_flags[q];
+      }
+      po.counter = m->peer_flags[rank] + ORCA_MAX_WORLD;
+      po.off = (seq & 1) * m->exchange_cap + (long long)rank * rpr * D;
+      po.world = world, po.rank = rank, po.seq = (int)seq;
+      ORCA_TRY(attn_output_impl(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.loc_nodes, rpr, w.n1_loc, d_emb1_local,
+                                nullptr, nullptr, nullptr, nullptr, 0, 0, w.hidden, 0, s, &po));
+      return ORCA_OK;
+    }
     ORCA_TRY(orca_attn_output(&m->attn[0], w.ctx, w.valid, m->mem.memory, w.loc_nodes, rpr, w.n1_loc,
                               d_emb1_local, nullptr, nullptr, nullptr, w.hidden, s));
     if (direct) {
+      // (fp32 debug projections: a separate kernel fans the rows out)
       const long long seq = ++*m->exchange_seq;
       Peers p{};
       for (int q = 0; q < world; ++q) {

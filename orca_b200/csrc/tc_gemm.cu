@@ -343,6 +343,12 @@ __device__ __forceinline__ void tile_output(const Args &g, const float *tile, co
             *reinterpret_cast<float4 *>(prow + 4 * j0) = ya;
             if (has1) *reinterpret_cast<float4 *>(prow + 4 * j1) = yb;
           }
+          // multi-GPU exchange: the row also goes to every rank's exchange buffer (peer stores)
+          for (int q = 0; q < g.peer.world; ++q) {
+            float *prow = g.peer.rows[q] + g.peer.off + (size_t)m[k] * D;
+            *reinterpret_cast<float4 *>(prow + 4 * j0) = ya;
+            if (has1) *reinterpret_cast<float4 *>(prow + 4 * j1) = yb;
+          }
         }
     } else {  // EPI_GRU: four gate columns per unit, unit = nt * 44 + j
 #pragma unroll
@@ -639,6 +645,22 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   if (warp == 5) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+  if (EPI == EPI_LAYERNORM && g.peer.world > 0) {
+    // every CTA (with or without rows) checks out; the last one posts the batch's sequence number to all
+    // ranks, after every CTA's peer stores have been fenced system-wide
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+      const int n_cta = (int)(gridDim.x * gridDim.y * gridDim.z);
+      if (atomicAdd(g.peer.counter, 1) == n_cta - 1) {
+        *g.peer.counter = 0;
+        __threadfence_system();
+        for (int q = 0; q < g.peer.world; ++q)
+          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(g.peer.flags[q] + g.peer.rank), "r"(g.peer.seq)
+                       : "memory");
+      }
+    }
   }
 }
 

@@ -34,6 +34,18 @@ struct RowSrc {
   int add;
 };
 
+// LAYERNORM epilogue that also delivers the rows to the other GPUs of the node (the exchange of the
+// multi-GPU split): row m goes to rows[q] + off + m * 172 floats for every rank q (peer stores over
+// NVLink; the own buffer is one of them), and the last CTA to finish posts `seq` in word `rank` of every
+// rank's flag array.  counter: a zeroed word of the own flag array.
+struct PeerOut {
+  float *rows[ORCA_MAX_WORLD];
+  int32_t *flags[ORCA_MAX_WORLD];
+  int32_t *counter;
+  long long off;
+  int world, rank, seq;
+};
+
 enum Epilogue { EPI_BIAS = 0, EPI_HIDDEN = 1, EPI_LAYERNORM = 2, EPI_GRU = 3, EPI_SCORE = 4 };
 
 struct Args {
@@ -66,6 +78,7 @@ struct Args {
   const float *w2;
   float b2;
   int32_t *status;
+  PeerOut peer;              // peer.world == 0: no fan-out
 };
 
 // enqueues the kernel: grid = (n_tiles, ceil(m_cap / 128))
@@ -78,6 +91,9 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
                      const int32_t *d_idx, int32_t n_rows_cap, const int32_t *d_n_rows, float *d_out,
                      float *d_push_table, const int32_t *d_push_ids, const uint8_t *d_push_win,
                      const int64_t *d_last_pos, long long base, int all_from, float *d_scratch_hidden,
-                     int rows_hint, cudaStream_t stream);
+                     int rows_hint, cudaStream_t stream, const tc::PeerOut *peer = nullptr);
+// whether the projections run on the tensor cores (orca_set_projection_mode(0)); the fp32 debug path has
+// no peer fan-out
+bool projections_on_tensor_cores();
 
 }  // namespace orca
