@@ -356,7 +356,7 @@ def run_ours(a):
                 **({"weak_scaling": f"batches of {spec.bs // world} edges per GPU: the stream is cut into batches "
                                     f"of {spec.bs} edges"} if (world > 1 and a.scaling == "weak") else {}),
                 "sharding": ("replicated tables; attention rows and scores split by row/edge % n_gpus; layer-1 rows "
-                             + ("written to every GPU by peer stores over NVLink" if a.exchange == "direct"
+                             + ("written to every GPU by peer stores over NVLink" if tgn._exchange is not None
                                 else "all-gathered with NCCL") + " once per batch") if world > 1 else "single GPU"}),
             "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches_per_batch * K), "clocks": clocks,
             "host_enqueue_ms_per_step": {"e2e": host_ms[0] / K, "value": host_ms[1] / K},

@@ -225,22 +225,40 @@ class TGN(nn.Module):
             xbuf = torch.zeros(2 * cap + 16, dtype=torch.float32, device=self.device)
             torch.cuda.synchronize(self.device)
             L = _lib.lib()
-            handle = (C.c_ubyte * 64)()
-            off = C.c_int64(0)
-            _lib.check(L.orca_ipc_export(xbuf.data_ptr(), handle, C.byref(off)))
+            rows, flags, keep, err = [], [], [xbuf], None
+            try:
+                handle = (C.c_ubyte * 64)()
+                off = C.c_int64(0)
+                _lib.check(L.orca_ipc_export(xbuf.data_ptr(), handle, C.byref(off)))
+                mine = (bytes(handle), int(off.value))
+            except _lib.OrcaError as e:
+                mine, err = None, e
             handles = [None] * self._world
-            dist.all_gather_object(handles, (bytes(handle), int(off.value)), group=group)
-            rows, flags, keep = [], [], [xbuf]
-            for r in range(self._world):
-                if r == self._rank:
-                    base = xbuf.data_ptr()
-                else:
-                    h = (C.c_ubyte * 64).from_buffer_copy(handles[r][0])
-                    out = C.c_void_p(0)
-                    _lib.check(L.orca_ipc_open(h, handles[r][1], C.byref(out)))
-                    base = out.value
-                rows.append(base)
-                flags.append(base + 8 * cap)      # byte offset of the flag words: 2 * cap floats
+            dist.all_gather_object(handles, mine, group=group)
+            if err is None and all(h is not None for h in handles):
+                try:
+                    for r in range(self._world):
+                        if r == self._rank:
+                            base = xbuf.data_ptr()
+                        else:
+                            h = (C.c_ubyte * 64).from_buffer_copy(handles[r][0])
+                            out = C.c_void_p(0)
+                            _lib.check(L.orca_ipc_open(h, handles[r][1], C.byref(out)))
+                            base = out.value
+                        rows.append(base)
+                        flags.append(base + 8 * cap)      # byte offset of the flag words: 2 * cap floats
+                except _lib.OrcaError as e:
+                    err = e
+            else:
+                err = err or RuntimeError("a peer could not export its exchange buffer")
+            # all ranks take the same route: peer stores only if every rank mapped every buffer
+            ok = torch.tensor([0 if err else 1], device=self.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) == 0:
+                import warnings
+                warnings.warn(f"orca_b200: peer exchange buffers could not be shared ({err}); the layer-1 rows "
+                              "are all-gathered with NCCL instead")
+                return
             self.set_exchange(rows, flags, cap, keep)
             dist.barrier(group=group)
 
