@@ -51,11 +51,13 @@ def parse():
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+    """Samples SM clock and throttle reasons of one GPU through NVML every few milliseconds; result()
+    keeps the samples that fall inside the timed windows (host time stamps taken right after the
+    synchronisation before a window and right after the one behind it)."""
 
     def __init__(self, index):
         super().__init__(daemon=True)
-        self.index, self.samples, self.reasons, self.stop_flag, self.max_mhz = index, [], set(), False, None
+        self.index, self.samples, self.stop_flag, self.max_mhz, self.windows = index, [], False, None, []
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -69,27 +71,36 @@ class ClockSampler(threading.Thread):
         if self.nv is None:
             return
         nv = self.nv
+        while not self.stop_flag:
+            try:
+                t = time.perf_counter()
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((t, mhz, r))
+            except Exception:
+                break
+            time.sleep(0.002)
+
+    def window(self, t0, t1):
+        self.windows.append((t0, t1))
+
+    def result(self):
+        self.stop_flag = True
+        nv = self.nv
+        if nv is None or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"], "samples": 0}
         names = {"hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
                  "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
                  "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
                  "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
-        while not self.stop_flag:
-            try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
-                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
-                for k, bit in names.items():
-                    if r & bit:
-                        self.reasons.add(k)
-            except Exception:
-                break
-            time.sleep(0.05)
-
-    def result(self):
-        self.stop_flag = True
-        if self.nv is None or not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
-        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons)}
+        inside = [(m, r) for t, m, r in self.samples if any(a <= t <= b for a, b in self.windows)]
+        where = "inside the timed windows"
+        if not inside:      # windows shorter than the sampling period: the whole measurement phase then
+            inside = [(m, r) for _, m, r in self.samples]
+            where = "over the measurement phase (no sample fell inside a timed window)"
+        reasons = sorted(k for k, bit in names.items() if any(r & bit for _, r in inside))
+        return {"sm_mhz": float(np.median([m for m, _ in inside])), "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(inside), "sampled": where}
 
 
 def load_peaks():
@@ -219,6 +230,7 @@ def run_ours(a):
     first = pick_window(nb_avail, K, W)
     k = spec.n_degree
     stream = _lib.stream_ptr(device)
+    idle = torch.cuda.Stream(device)     # never given work: "inputs ready" for batches preloaded in HBM
 
     def barrier():
         torch.cuda.synchronize()
@@ -226,50 +238,56 @@ def run_ours(a):
             dist.barrier()
         torch.cuda.synchronize()
 
-    host_ms = []
+    sampler = ClockSampler(local)
+    sampler.start()
 
-    def timed(fn_warm, fn_step):
-        for i in range(W):
-            fn_warm(i)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        sampler = ClockSampler(local)
-        sampler.start()
-        e0.record()
-        t_host = time.perf_counter()
-        for i in range(K):
-            fn_step(i)
-        host_ms.append((time.perf_counter() - t_host) * 1e3)   # time the CPU needed to enqueue the steps
-        e1.record()
-        barrier()
-        clocks = sampler.result()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item()), clocks
+    def timed(fn_step, min_seconds=1.0, max_repeats=400):
+        """W untimed + K timed steps from the same reset state, repeated until `min_seconds` of timed region
+        have accumulated; returns (median ms of a K-step window, repeats, host ms per window)."""
+        ms_all, host_all, total = [], [], 0.0
+        while total < min_seconds * 1e3 and len(ms_all) < max_repeats:
+            reset_state(tgn, plan, first)
+            for i in range(W):
+                fn_step(i, False)
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            e0.record()
+            for i in range(K):
+                fn_step(W + i, True)
+            host_all.append((time.perf_counter() - t0) * 1e3)   # time the CPU needed to enqueue the steps
+            e1.record()
+            barrier()
+            sampler.window(t0, time.perf_counter())
+            ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)     # every rank sees the same number: same repeat count
+            ms_all.append(float(ms.item()))
+            total += ms_all[-1]
+        return float(np.median(ms_all)), len(ms_all), float(np.median(host_all))
 
     # ---------------- end to end: public API, host inputs, pinned H2D + D2H of the scores per step
     bs = spec.bs
     host_out = torch.empty((K, 2 * bs), dtype=torch.float32, pin_memory=True)
-    h2d = d2h = 0
+    counted = {}
 
-    def api_step(b, slot=None):
-        nonlocal h2d, d2h
+    def api_step(i, is_timed):
+        b = first + i
         src, dst, ng, ts, eidx = batch_arrays(g, neg, b)
-        p, q = tgn.compute_edge_probabilities(src, dst, ng, ts, eidx, k, True, False, plan[b])
-        if slot is not None:
+        tgn.compute_edge_probabilities(src, dst, ng, ts, eidx, k, True, False, plan[b])
+        if is_timed:
             n = len(src)
-            # p and q are the two halves of one [2n] tensor (tgn.last_scores): one copy brings both back
-            host_out[slot, :2 * n].copy_(tgn.last_scores, non_blocking=True)
-            h2d += 16 * n + 8 * n + 4 * len(plan[b])
-            d2h += 8 * n
+            # the two score vectors are the halves of one [2n] tensor (tgn.last_scores): one copy brings both back
+            host_out[i - W, :2 * n].copy_(tgn.last_scores, non_blocking=True)
+            counted[i] = (16 * n + 8 * n + 4 * len(plan[b]), 8 * n)
 
-    reset_state(tgn, plan, first)
-    ms_e2e, _ = timed(lambda i: api_step(first + i), lambda i: api_step(first + W + i, i))
+    ms_e2e, rep_e2e, host_e2e = timed(api_step)
     tgn.check_status()
     edges = sum(len(batch_arrays(g, neg, first + W + i)[0]) for i in range(K))
     e2e = {"value": edges / (ms_e2e / 1e3), "unit": "edges/s",
-           "h2d_bytes_per_step": h2d // K, "d2h_bytes_per_step": d2h // K, "ms_per_step": ms_e2e / K}
+           "h2d_bytes_per_step": sum(v[0] for v in counted.values()) // K,
+           "d2h_bytes_per_step": sum(v[1] for v in counted.values()) // K, "ms_per_step": ms_e2e / K,
+           "repeats": rep_e2e}
 
     # ---------------- device-resident inputs: packed batches preloaded, the C ABI called directly
     packed = []
@@ -279,46 +297,51 @@ def run_ours(a):
         ints = torch.from_numpy(np.concatenate([src, dst, ng, eidx, pl]).astype(np.int32)).to(device)
         packed.append((ints, torch.from_numpy(np.ascontiguousarray(ts)).to(device), len(src), len(pl)))
     probs = torch.empty((W + K, 2 * bs), device=device)
-    reset_state(tgn, plan, first)
-    desc = tgn._descriptor(k)
+    torch.cuda.synchronize()
+    tgn._input_stream = idle.cuda_stream
     ws, u_cap = tgn._workspace(bs, k)
 
-    def abi_step(i):
+    def abi_step(i, is_timed=True):
         ints, ts, n, n_plan = packed[i]
+        desc = tgn._descriptor(k)        # cached; only the state-table pointers are refreshed (reset_state)
         if world > 1:
-            # sharded attention layers and scores, NCCL all-gather of the layer-1 rows in between;
-            # the scores stay sharded (every rank keeps those of its edges)
+            # sharded attention layers and scores; the scores stay sharded (every rank keeps those of its edges)
             from orca_b200 import shard
-            direct = tgn._exchange is not None     # rows exchanged by peer stores inside the library
+            if tgn._exchange is not None:     # rows exchanged by peer stores inside the library: one call
+                _lib.check(L.orca_tgn_eval_batch_sharded(desc, 0, ints.data_ptr(), ts.data_ptr(), n,
+                                                         ints.data_ptr() + 16 * n, n_plan, u_cap, ws.data_ptr(),
+                                                         ws.numel(), None, None, probs[i].data_ptr(), None,
+                                                         tgn._status.data_ptr(), stream))
+                return
             rpr = shard.rows_per_rank(3 * n + u_cap, world)
-            emb1_local = None if direct else torch.empty(rpr, 172, device=device)
+            emb1_local = torch.empty(rpr, 172, device=device)
             _lib.check(L.orca_tgn_eval_batch_sharded(desc, 1, ints.data_ptr(), ts.data_ptr(), n,
                                                      ints.data_ptr() + 16 * n, n_plan, u_cap, ws.data_ptr(),
-                                                     ws.numel(), _lib.ptr(emb1_local), None, None, None,
+                                                     ws.numel(), emb1_local.data_ptr(), None, None, None,
                                                      tgn._status.data_ptr(), stream))
-            emb1_all = None if direct else shard.all_gather_rows(emb1_local)
+            emb1_all = shard.all_gather_rows(emb1_local)
             _lib.check(L.orca_tgn_eval_batch_sharded(desc, 2, ints.data_ptr(), ts.data_ptr(), n,
                                                      ints.data_ptr() + 16 * n, n_plan, u_cap, ws.data_ptr(),
-                                                     ws.numel(), None, _lib.ptr(emb1_all), probs[i].data_ptr(),
+                                                     ws.numel(), None, emb1_all.data_ptr(), probs[i].data_ptr(),
                                                      None, tgn._status.data_ptr(), stream))
             return
         _lib.check(L.orca_tgn_eval_batch(desc, ints.data_ptr(), ts.data_ptr(), n, ints.data_ptr() + 16 * n, n_plan,
                                          u_cap, ws.data_ptr(), ws.numel(), probs[i].data_ptr(), None,
                                          tgn._status.data_ptr(), stream))
 
-    ms_dev, clocks = timed(lambda i: abi_step(i), lambda i: abi_step(W + i))
+    ms_dev, rep_dev, host_dev = timed(abi_step)
     counts = tgn.check_status()
     launches_per_batch = counts[2]
+    clocks = sampler.result()
 
     # ---------------- roofline pass: same batches, CUDA events around every gather-attention launch
     reset_state(tgn, plan, first)
-    desc = tgn._descriptor(k)
     counters = torch.zeros(2, dtype=torch.int64, device=device)
     for i in range(W):
         abi_step(i)
     torch.cuda.synchronize()
-    _lib.check(L.orca_attn_gather_profile(1, counters.data_ptr()))
-    _lib.check(L.orca_trace(1))
+    _lib.check(L.orca_attn_gather_profile(tgn._ctx, 1, counters.data_ptr()))
+    tgn.set_option(_lib.OPT_TRACE, 1)
     step_bytes = 0
     for i in range(K):
         abi_step(W + i)
@@ -328,12 +351,12 @@ def run_ours(a):
                                         3 * n if spec.n_layers == 2 else 0, p)
     gms = np.zeros(1, dtype=np.float64)
     gl = np.zeros(1, dtype=np.int64)
-    _lib.check(L.orca_attn_gather_profile_read(gms.ctypes.data, gl.ctypes.data))
-    _lib.check(L.orca_attn_gather_profile(0, None))
+    _lib.check(L.orca_attn_gather_profile_read(tgn._ctx, gms.ctypes.data, gl.ctypes.data))
+    _lib.check(L.orca_attn_gather_profile(tgn._ctx, 0, None))
     n_ph = L.orca_trace_phases()
     ph_ms = np.zeros(n_ph, dtype=np.float64)
-    _lib.check(L.orca_trace_read(ph_ms.ctypes.data))
-    _lib.check(L.orca_trace(0))
+    _lib.check(L.orca_trace_read(tgn._ctx, ph_ms.ctypes.data))
+    tgn.set_option(_lib.OPT_TRACE, 0)
     phases = {L.orca_trace_phase_name(i).decode(): round(float(ph_ms[i]) * 1e3 / K, 2) for i in range(n_ph)}
     rows_g, slots_g = (int(x) for x in counters.cpu().numpy())
     peak, peak_kind = load_peaks()
@@ -346,21 +369,26 @@ def run_ours(a):
                 "algorithmic_bytes_per_launch": gather_bytes / max(int(gl[0]), 1)}
     step_frac = step_bytes / (ms_dev / 1e3) / 1e9 / peak
 
+    parity = parity_vs_single(a, g, neg, plan, tgn, first, device, rank, world) if world > 1 else None
+
     value = edges / (ms_dev / 1e3)
     line = {"metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms_dev / K, "higher_is_better": True, "scaling": a.scaling if world > 1 else "strong",
-            "vs_baseline": None,
+            "vs_baseline": None, "repeats": rep_dev,
             "dtype": "f32", "data": "synthetic",
             "config": workload_config(g, spec, first + W, {
                 "whole_step_hbm_frac": step_frac / world, "algorithmic_bytes_per_edge": step_bytes / edges,
+                "timing": f"median of {rep_dev} windows of {K} steps, each after a state reset and {W} warm-up steps",
                 **({"weak_scaling": f"batches of {spec.bs // world} edges per GPU: the stream is cut into batches "
                                     f"of {spec.bs} edges"} if (world > 1 and a.scaling == "weak") else {}),
                 "sharding": ("replicated tables; attention rows and scores split by row/edge % n_gpus; layer-1 rows "
                              + ("written to every GPU by peer stores over NVLink" if tgn._exchange is not None
                                 else "all-gathered with NCCL") + " once per batch") if world > 1 else "single GPU"}),
             "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches_per_batch * K), "clocks": clocks,
-            "host_enqueue_ms_per_step": {"e2e": host_ms[0] / K, "value": host_ms[1] / K},
+            "host_enqueue_ms_per_step": {"e2e": host_e2e / K, "value": host_dev / K},
             "phases_us_per_step": phases}
+    if parity is not None:
+        line["parity_vs_single"] = parity
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(a, g, neg, plan, first + W)
     if rank == 0:
@@ -369,9 +397,53 @@ def run_ours(a):
         dist.destroy_process_group()
 
 
-# DRAM traffic of attn_gather_kernel: dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic
-# bytes of the captured launch (profiles/attn_gather_kernel_c4_ncu.md: 15.23 MB read + 0 written for
-# 30.68 MB algorithmic, workload c4), applied to the algorithmic bytes of this run's launches
+def parity_vs_single(a, g, neg, plan, tgn, first, device, rank, world, n_batches=6):
+    """The sharded model against an unsharded replica on rank 0: the same batches from the same reset
+    state; largest score difference and whether the state tables ended bit-identical."""
+    import torch
+    import torch.distributed as dist
+
+    spec = g.spec
+    k = spec.n_degree
+    reset_state(tgn, plan, first)
+    got = []
+    for i in range(n_batches):
+        src, dst, ng, ts, eidx = batch_arrays(g, neg, first + i)
+        p, q = tgn.compute_edge_probabilities(src, dst, ng, ts, eidx, k, True, False, plan[first + i])
+        got.append(torch.cat([p, q]).clone())
+    tgn.check_status()
+    out = None
+    if rank == 0:
+        import copy
+
+        from orca_b200.tgn import TGN
+        ns = copy.copy(tgn.args)           # a second model on this GPU: same graph and weights, state of its own
+        single = TGN(neighbor_finder=tgn.embedding_module.neighbor_finder, node_features=None,
+                     edge_features=g.edge_features, device=device, n_layers=spec.n_layers, n_heads=2, dropout=0.1,
+                     use_memory=True, node_dimension=172, time_dimension=172, memory_dimension=172,
+                     embedding_module_type="graph_attention", message_function="identity", aggregator_type="last",
+                     memory_updater_type="gru", n_neighbors=k, args=ns)
+        single.load_state_dict(tgn.state_dict())
+        single.eval()
+        reset_state(single, plan, first)
+        worst = 0.0
+        for i in range(n_batches):
+            src, dst, ng, ts, eidx = batch_arrays(g, neg, first + i)
+            p, q = single.compute_edge_probabilities(src, dst, ng, ts, eidx, k, True, False, plan[first + i])
+            worst = max(worst, float((torch.cat([p, q]) - got[i]).abs().max()))
+        single.check_status()
+        out = {"batches": n_batches, "max_abs_score_diff": worst,
+               "memory_equal": bool(torch.equal(single.memory.memory, tgn.memory.memory)),
+               "history_equal": bool(torch.equal(single.embedding_module.histories[0].emb,
+                                                 tgn.embedding_module.histories[0].emb))}
+        del single
+    dist.barrier()
+    return out
+
+
+# DRAM traffic of attn_gather_kernel: (dram__bytes_read.sum + dram__bytes_write.sum) of one launch captured
+# with ncu on workload c4 (15.25 MB read + 0 written) over the algorithmic bytes of that launch (30.68 MB),
+# applied to the algorithmic bytes of this run's launches; the counter cannot be read while timing
 GATHER_TRAFFIC_RATIO = 15.246848 / 30.683416
 
 

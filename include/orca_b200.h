@@ -39,6 +39,8 @@ extern "C" {
 #define ORCA_HEADS 2
 #define ORCA_MAX_K 32
 #define ORCA_MAX_WORLD 8   /* GPUs of one node */
+#define ORCA_EXCHANGE_SLOTS 4 /* batches whose layer-1 rows an exchange buffer holds: with the lanes of the
+                                 batch pipeline a rank's layer 1 may be two batches ahead of a peer's layer 2 */
 #define ORCA_CAND_CAP 2048 /* listed candidates of the uncached set; more fall back to a bitmap scan */
 #define ORCA_MSG_DIM (4 * ORCA_DIM)          /* [mem_src | mem_dst | edge feat | time enc] */
 #define ORCA_KEY_DIM (3 * ORCA_DIM)          /* [neighbour | edge feat | time enc]         */
@@ -47,6 +49,52 @@ extern "C" {
 
 const char *orca_last_error(void);
 int orca_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Contexts (no counterpart in the reference, which is a single Python process on one device).
+ * A context owns what a caller of the batch entry points would otherwise share with every other
+ * caller in the process: three auxiliary CUDA streams and the events that tie them to the caller's
+ * stream, the switches below, the device status word the projection kernels report to, the phase
+ * tracer and 1 KB of zeroed device words (work tickets).  orca_ctx_create works on the current
+ * device and is the one call of the library that allocates device memory.  A model descriptor
+ * (orca_tgn_t.ctx) names its context; two models with contexts of their own share nothing.
+ * Entry points without a descriptor, and descriptors with ctx == NULL, use the default context of
+ * the current device, created on first use; `ctx == NULL` below means that context.
+ */
+typedef struct orca_ctx orca_ctx_t;
+int orca_ctx_create(orca_ctx_t **out);
+int orca_ctx_destroy(orca_ctx_t *ctx);
+/* Projection kernels: 0 (default) = tcgen05 tensor cores, every fp32 operand split into a bf16 head
+ * and a bf16 tail (three MMAs per product, layer error 3-5e-4), 1 = plain fp32 SIMT tiles (debug
+ * reference for the tensor-core path, ~5e-5). */
+#define ORCA_OPT_PROJECTION_MODE 0
+/* 1 (default): the raw-message / GRU chain of a batch runs on an auxiliary stream beside the
+ * attention layers; 0: everything on the caller's stream. */
+#define ORCA_OPT_OVERLAP 1
+/* 1 (default): kernels are enqueued with programmatic stream serialisation: a kernel's blocks may be
+ * scheduled and run their set-up while the kernel before it in the stream drains, and wait
+ * (griddepcontrol.wait) before touching anything it produced.  Results are identical either way. */
+#define ORCA_OPT_DEPENDENT_LAUNCH 2
+/* 1 (default, needs OVERLAP): the budgeted two-layer batch is spread over four streams -- index work
+ * (sampling, uncached set, message winners, cache flags) a batch ahead, layer 1, raw messages + GRU,
+ * and layer 2 + scores on the caller's stream beside the next batch's layer 1.  0: one batch after
+ * the other.  Results are identical either way. */
+#define ORCA_OPT_LOOKAHEAD 3
+/* SM clocks a device-side wait (mbarrier of the projection kernels, peer flags of the multi-GPU
+ * exchange) may spin before it gives up with ORCA_E_TIMEOUT in the status word; default 2e9 (about a
+ * second). */
+#define ORCA_OPT_WAIT_LIMIT 4
+/* 1: CUDA events are recorded at the phase boundaries of every batch (which then runs on the caller's
+ * stream alone); see orca_trace_read. */
+#define ORCA_OPT_TRACE 5
+int orca_ctx_set(orca_ctx_t *ctx, int32_t option, int64_t value);
+/* Device status word (int32[4], see orca_read_status) to which projection kernels launched through the
+ * stand-alone entry points report a bounded wait that gave up; NULL (default) = not reported.  The
+ * batch entry points report to their own d_status. */
+int orca_ctx_set_status_word(orca_ctx_t *ctx, int32_t *d_status);
+/* Which of the two index-buffer sets of the workspace the last batch of the context used (see
+ * orca_eval_workspace_row_list). */
+int orca_ctx_last_parity(orca_ctx_t *ctx);
 
 /* ------------------------------------------------------------------------------------------
  * Time-sorted adjacency.  Replaces get_neighbor_finder (utils/util.py:91-105): every edge is
@@ -133,7 +181,7 @@ int orca_last_occurrence(const int32_t *d_ids, int32_t n_cap, const int32_t *d_n
  *   hid  = relu([ctx | h_src] . G + b1 + valid * g)         [*, 172]
  *   out  = LayerNorm(hid . W2t + b2) * ln_w + ln_b          [*, 172]
  * All matrices are row-major [in, out] float32.  The *_tc members hold the same matrices split into
- * TF32 head and tail and packed into the stage images of the tensor-core kernel
+ * a bf16 head and a bf16 tail and packed into the stage images of the tensor-core kernel
  * (orca_b200/weights.py: pack_tc).
  */
 typedef struct {
@@ -151,14 +199,6 @@ typedef struct {
 
 /* Step 1 of TemporalAttentionLayer.forward (model/temporal_attention.py:41-48, the query side of
  * nn.MultiheadAttention): qt[r] = feat[idx ? idx[r] : r] . Mq + cq. */
-/* Projection kernels: 0 (default) = tcgen05 tensor cores with split-TF32 operands (error ~1e-6),
- * 1 = plain fp32 SIMT tiles (debug reference for the tensor-core path). Process-wide. */
-int orca_set_projection_mode(int32_t mode);
-/* Device status word (int32[4], see orca_read_status) to which the projection kernels report a
- * bounded wait that gave up; NULL (default) = not reported.  orca_tgn_eval_batch sets it to its own
- * d_status.  Process-wide. */
-int orca_set_status_word(int32_t *d_status);
-
 int orca_attn_query(const orca_attn_weights_t *w, const float *d_feat, const int32_t *d_idx,
                     int32_t n_rows_cap, const int32_t *d_n_rows, float *d_qt, void *stream);
 
@@ -180,8 +220,8 @@ int orca_attn_gather(const float *d_qt, const float *d_nbr_table, const float *d
  * orca_attn_gather launch is bracketed by CUDA events on its stream and adds {rows that gathered,
  * neighbour slots gathered} to the two uint64 device counters.  _read synchronises on the recorded
  * events, returns their summed duration and count, and forgets them. */
-int orca_attn_gather_profile(int32_t enable, void *d_counters);
-int orca_attn_gather_profile_read(double *h_ms_total, int64_t *h_launches);
+int orca_attn_gather_profile(orca_ctx_t *ctx, int32_t enable, void *d_counters);
+int orca_attn_gather_profile_read(orca_ctx_t *ctx, double *h_ms_total, int64_t *h_launches);
 
 /* Step 3 (out-projection, merger and LayerNorm, model/temporal_attention.py:48-55 and
  * utils/util.py:21-24): d_out[r] = LN(fc2(relu(fc1([attn | h_src])))).  If d_push_table is
@@ -331,25 +371,36 @@ typedef struct {
   int32_t *prev_plan;       /* [plan_cap] device copy of the plan whose flags are set */
   int32_t *n_prev_plan;     /* host-resident counter owned by the caller              */
   int32_t plan_cap;
-  int64_t *last_pos;        /* [n_nodes] scratch of orca_last_occurrence              */
+  int64_t *last_pos;        /* [3 * n_nodes] last-occurrence records, zero-initialised once: push  */
+                            /* winners of even / odd batches, message winners                     */
   int64_t *epoch_base;      /* host-resident counter owned by the caller              */
   int32_t rank, world;      /* orca_tgn_eval_batch_sharded only; world <= 1 means one GPU */
   uint32_t *cand_bitmap;    /* (n_nodes+31)/32 + 1 + ORCA_CAND_CAP words (candidate bitmap, list    */
                             /* length, list), zero-initialised once by the caller                */
   int32_t mode;             /* ORCA_MODE_*: which recursion of the embedding module runs        */
   /* Direct exchange of the layer-1 rows between the GPUs of one node (orca_tgn_eval_batch_sharded; all
-   * NULL / 0: the caller all-gathers).  peer_rows[r] / peer_flags[r]: rank r's exchange buffer (2 halves of
-   * exchange_cap floats, used alternately) and flag words (int32[ORCA_MAX_WORLD + 1], zero-initialised) as
-   * mapped into THIS process (own rank included, peers through CUDA IPC). */
+   * NULL / 0: the caller all-gathers).  peer_rows[r] / peer_flags[r]: rank r's exchange buffer
+   * (ORCA_EXCHANGE_SLOTS slots of exchange_cap floats, used in turn) and flag words
+   * (int32[ORCA_MAX_WORLD + 1], zero-initialised) as mapped into THIS process (own rank included, peers
+   * through CUDA IPC). */
   float *peer_rows[ORCA_MAX_WORLD];
   int32_t *peer_flags[ORCA_MAX_WORLD];
   int64_t exchange_cap;
   int64_t *exchange_seq;    /* host-resident batch sequence counter owned by the caller (starts at 0) */
+  orca_ctx_t *ctx;          /* context of this model; NULL = default context of the current device   */
+  void *input_stream;       /* cudaStream_t on which the batch arrays (and the plan) of a call were made */
+                            /* ready, e.g. a copy stream; NULL = the call's `stream`.  Only with an    */
+                            /* input stream of its own can the index work of a batch run ahead of the  */
+                            /* previous batch's kernels on `stream`.                                   */
 } orca_tgn_t;
 
 /* Workspace sizing: bytes needed for batches of up to b_cap edges with at most u_cap uncached
  * neighbours per batch. */
 int64_t orca_eval_workspace_bytes(int32_t b_cap, int32_t u_cap, int32_t k, int64_t n_nodes);
+/* Byte offset, inside a workspace of those parameters, of the layer-1 row list (int32 node ids:
+ * [src | dst | neg | uncached]) of the index-buffer set `parity` (0 or 1; orca_ctx_last_parity tells
+ * which one the last batch used).  For tests and debugging. */
+int64_t orca_eval_workspace_row_list(int32_t b_cap, int32_t u_cap, int32_t k, int64_t n_nodes, int32_t parity);
 
 /* d_batch_i32: [src | dst | neg | eidx] (4*b int32), d_batch_ts: [b] float64, d_plan: ids of the
  * batch's cache plan (NULL = plan-less flag rule).  Outputs: d_prob [2*b] = [pos | neg] and, if
@@ -366,6 +417,7 @@ int orca_tgn_eval_batch(const orca_tgn_t *m, const int32_t *d_batch_i32, const d
  * and receives the full batch.  Index work (top-level sampling, uncached set, last occurrences) and the
  * raw-message / GRU chain are replicated -- they are cheap and keep every replica identical -- while
  * the two attention layers and the scorer are sharded:
+ *   phase 0: both phases in one call (only with the direct exchange, where the library moves the rows).
  *   phase 1: layer-1 row i of [src|dst|neg|U] belongs to rank i % world; a rank computes its rows
  *            into d_emb1_local [rows_per_rank, 172], rows_per_rank = ceil((3b + u_cap) / world),
  *            local slot i / world.
@@ -389,38 +441,26 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
  * memory there, with peer access enabled.  A handle may be opened once per process. */
 int orca_ipc_export(const void *d_ptr, void *h_handle64, int64_t *h_offset);
 int orca_ipc_open(const void *h_handle64, int64_t offset, void **h_ptr_out);
+/* unmaps what orca_ipc_open returned (same offset) */
+int orca_ipc_close(void *h_ptr, int64_t offset);
 
 /* Asynchronous copy of a staged batch from pinned host memory to the device on `stream` (what
  * `tensor.to(device)` does for the batch arrays in evaluation/evaluation.py:34 of the reference; here
  * one copy per batch). */
 int orca_stage_h2d(void *d_dst, const void *h_src, int64_t bytes, void *stream);
 
-/* With overlap on (default) a two-layer batch runs its raw-message / GRU chain on an auxiliary
- * stream of the library, next to the top attention layer and the scorer; `stream` waits for it
- * before orca_tgn_eval_batch's work is complete, so callers see one stream-ordered operation.  The
- * auxiliary stream and two events are created once per device on first use.  Off while tracing. */
-int orca_set_overlap(int32_t enable);
-
-/* With dependent launch on (default) the library's kernels are enqueued with programmatic stream
- * serialisation: a kernel's blocks may be scheduled and run their set-up while the kernel before it
- * in the stream drains, and wait (griddepcontrol.wait) before touching anything it produced.  Results
- * are identical either way; off restores plain stream-ordered launches (no counterpart in the
- * reference). */
-int orca_set_dependent_launch(int32_t enable);
-
-/* Phase tracing of orca_tgn_eval_batch (the reference only has wall-clock deltas around whole
- * epochs, train.py:189-341): while enabled, CUDA events are recorded at the phase boundaries of every
- * batch; orca_trace_read synchronises on them, returns the summed milliseconds per phase
- * (orca_trace_phases() entries, names from orca_trace_phase_name) and forgets them. */
-int orca_trace(int32_t enable);
+/* Phase tracing of the batch entry points (the reference only has wall-clock deltas around whole
+ * epochs, train.py:189-341): while ORCA_OPT_TRACE is on, CUDA events are recorded at the phase
+ * boundaries of every batch; orca_trace_read synchronises on them, returns the summed milliseconds per
+ * phase (orca_trace_phases() entries, names from orca_trace_phase_name) and forgets them. */
 int orca_trace_phases(void);
 const char *orca_trace_phase_name(int32_t phase);
-int orca_trace_read(double *h_ms_per_phase);
+int orca_trace_read(orca_ctx_t *ctx, double *h_ms_per_phase);
 
 /* Copies the device status words to the host (synchronises `stream`), returns the first nonzero
  * code and resets the device words. h_counts (may be NULL) receives {status, n_layer1_rows,
  * n_unique_positives, kernels launched by the last batch}. */
-int orca_read_status(int32_t *d_status, int32_t *h_counts, void *stream);
+int orca_read_status(orca_ctx_t *ctx, int32_t *d_status, int32_t *h_counts, void *stream);
 
 #ifdef __cplusplus
 }

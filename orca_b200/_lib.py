@@ -18,6 +18,9 @@ QT_DIM = 1032
 QT_LD = 1056
 MSG_DIM = 688
 CAND_CAP = 2048   # ORCA_CAND_CAP
+EXCHANGE_SLOTS = 4  # ORCA_EXCHANGE_SLOTS
+# options of orca_ctx_set
+OPT_PROJECTION_MODE, OPT_OVERLAP, OPT_DEPENDENT_LAUNCH, OPT_LOOKAHEAD, OPT_WAIT_LIMIT, OPT_TRACE = range(6)
 
 c_f32p = C.c_void_p
 c_i32p = C.c_void_p
@@ -62,6 +65,8 @@ class TgnT(C.Structure):
         ("peer_flags", C.c_void_p * 8),
         ("exchange_cap", C.c_int64),
         ("exchange_seq", C.POINTER(C.c_int64)),
+        ("ctx", C.c_void_p),
+        ("input_stream", C.c_void_p),
     ]
 
 
@@ -70,6 +75,11 @@ _V, _I32, _I64 = C.c_void_p, C.c_int32, C.c_int64
 SYMBOLS = {
     "orca_last_error": (C.c_char_p, []),
     "orca_version": (C.c_int, []),
+    "orca_ctx_create": (C.c_int, [C.POINTER(C.c_void_p)]),
+    "orca_ctx_destroy": (C.c_int, [_V]),
+    "orca_ctx_set": (C.c_int, [_V, _I32, _I64]),
+    "orca_ctx_set_status_word": (C.c_int, [_V, _V]),
+    "orca_ctx_last_parity": (C.c_int, [_V]),
     "orca_csr_build_host": (C.c_int, [_V, _V, _V, _V, _I64, _I64, _V, _V, _V, _V]),
     "orca_sample_topk": (C.c_int, [_V, _V, _V, _V, _I64, _V, _V, _I32, _V, _I32, _V, _V, _V, _V, _V, _V]),
     "orca_sample_topk_mark": (C.c_int, [_V, _V, _V, _V, _I64, _V, _V, _I32, _V, _I32, _V, _V, _V, _V, _V, _V, _V, _V]),
@@ -80,11 +90,9 @@ SYMBOLS = {
     "orca_last_occurrence": (C.c_int, [_V, _I32, _V, _I64, _V, _I64, _V, _V, _V, _V]),
     "orca_attn_query": (C.c_int, [C.POINTER(AttnWeights), _V, _V, _I32, _V, _V, _V]),
     "orca_attn_gather": (C.c_int, [_V, _V, _V, _V, _V, _V, _V, _I32, _I32, _V, _V, _V, _V, _V]),
-    "orca_attn_gather_profile": (C.c_int, [_I32, _V]),
-    "orca_attn_gather_profile_read": (C.c_int, [_V, _V]),
+    "orca_attn_gather_profile": (C.c_int, [_V, _I32, _V]),
+    "orca_attn_gather_profile_read": (C.c_int, [_V, _V, _V]),
     "orca_attn_output": (C.c_int, [C.POINTER(AttnWeights), _V, _V, _V, _V, _I32, _V, _V, _V, _V, _V, _V, _V]),
-    "orca_set_projection_mode": (C.c_int, [_I32]),
-    "orca_set_status_word": (C.c_int, [_V]),
     "orca_history_pull": (C.c_int, [_V, _V, _I64, _V, _V]),
     "orca_history_push": (C.c_int, [_V, _V, _V, _V, _I32, _V, _V]),
     "orca_history_set_flags": (C.c_int, [_V, _I64, _V, _I32, _V, _I32, _V]),
@@ -95,19 +103,18 @@ SYMBOLS = {
     "orca_gru_update_static": (C.c_int, [C.POINTER(GruWeights), C.POINTER(MemoryT), _V, _I32, _V, _I32, _V]),
     "orca_plan_host": (C.c_int, [_I32, _V, _V, _I64, _I32, _I32, _V, _I64, _I32, C.c_uint32, _V, _I64, _V, _V]),
     "orca_eval_workspace_bytes": (_I64, [_I32, _I32, _I32, _I64]),
+    "orca_eval_workspace_row_list": (_I64, [_I32, _I32, _I32, _I64, _I32]),
     "orca_tgn_eval_batch": (C.c_int, [C.POINTER(TgnT), _V, _V, _I32, _V, _I32, _I32, _V, _I64, _V, _V, _V, _V]),
     "orca_tgn_eval_batch_sharded": (C.c_int, [C.POINTER(TgnT), _I32, _V, _V, _I32, _V, _I32, _I32, _V, _I64, _V, _V,
                                               _V, _V, _V, _V]),
     "orca_stage_h2d": (C.c_int, [_V, _V, C.c_int64, _V]),
     "orca_ipc_export": (C.c_int, [_V, _V, C.POINTER(C.c_int64)]),
     "orca_ipc_open": (C.c_int, [_V, C.c_int64, C.POINTER(C.c_void_p)]),
-    "orca_set_overlap": (C.c_int, [_I32]),
-    "orca_set_dependent_launch": (C.c_int, [_I32]),
-    "orca_trace": (C.c_int, [_I32]),
+    "orca_ipc_close": (C.c_int, [_V, C.c_int64]),
     "orca_trace_phases": (C.c_int, []),
     "orca_trace_phase_name": (C.c_char_p, [_I32]),
-    "orca_trace_read": (C.c_int, [_V]),
-    "orca_read_status": (C.c_int, [_V, _V, _V]),
+    "orca_trace_read": (C.c_int, [_V, _V]),
+    "orca_read_status": (C.c_int, [_V, _V, _V, _V]),
 }
 
 _lib = None

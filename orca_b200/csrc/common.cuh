@@ -55,38 +55,25 @@ int &launch_counter();
 // that was launched the plain way.
 __device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-bool &dependent_launch_enabled();
-// (cluster_z > 1: thread-block clusters of (1, 1, cluster_z); grid.z must be a multiple of it)
+bool dependent_launch_enabled();   // switch of the context in effect (context.cuh)
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_dep_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                      cudaStream_t stream, int cluster_z, Args &&...args) {
+inline cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args &&...args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
+  cudaLaunchAttribute attr[1];
   int n = 0;
   if (dependent_launch_enabled()) {
     attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;
   }
-  if (cluster_z > 1) {
-    attr[n].id = cudaLaunchAttributeClusterDimension;
-    attr[n].val.clusterDim.x = 1;
-    attr[n].val.clusterDim.y = 1;
-    attr[n].val.clusterDim.z = (unsigned)cluster_z;
-    ++n;
-  }
   cfg.attrs = attr;
   cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
-}
-template <typename... KArgs, typename... Args>
-inline cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                              Args &&...args) {
-  return launch_dep_cluster(kernel, grid, block, smem, stream, 1, static_cast<Args &&>(args)...);
 }
 
 __device__ __forceinline__ int rows_of(int cap, const int32_t *d_n) {

@@ -6,6 +6,8 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "context.cuh"
+#include "index_ops.cuh"
 #include "tc_gemm.cuh"
 
 namespace orca {
@@ -385,8 +387,15 @@ __global__ void gru_scatter_kernel(const float *__restrict__ hnew, orca_memory_t
 
 using namespace orca;
 
-static int g_projection_mode = 0;  // 0 = tensor cores (split TF32), 1 = fp32 SIMT tiles
-static int32_t *g_status_word = nullptr;  // where the projection kernels report bounded-wait time-outs
+// projection kernels of the context in effect: 0 = tensor cores (bf16 head/tail split), 1 = fp32 SIMT tiles
+static int projection_mode() {
+  Ctx *c = cur();
+  return c != nullptr ? c->projection_mode : 0;
+}
+static int sm_count() {
+  Ctx *c = cur();
+  return c != nullptr ? c->sm_count : 148;
+}
 
 static int ensure_f2_smem() {
   static thread_local int configured_device = -1;
@@ -406,25 +415,13 @@ static inline int kblocks(int k) { return (k + tc::BK - 1) / tc::BK; }
 
 extern "C" {
 
-int orca_set_status_word(int32_t *d_status) {
-  g_status_word = d_status;
-  return ORCA_OK;
-}
-
-int orca_set_projection_mode(int32_t mode) {
-  ORCA_CHECK_ARG(mode == 0 || mode == 1);
-  g_projection_mode = mode;
-  return ORCA_OK;
-}
-
 int orca_attn_query(const orca_attn_weights_t *w, const float *d_feat, const int32_t *d_idx,
                     int32_t n_rows_cap, const int32_t *d_n_rows, float *d_qt, void *stream) {
   ORCA_CHECK_ARG(w && w->Mq && w->cq && d_feat && d_qt && n_rows_cap >= 0);
   if (n_rows_cap == 0) return ORCA_OK;
-  if (g_projection_mode == 0) {
+  if (projection_mode() == 0) {
     ORCA_CHECK_ARG(w->Mq_tc != nullptr);
     tc::Args a{};
-    a.status = g_status_word;
     a.a0 = tc::RowSrc{d_feat, d_idx, D, 0, 0};
     a.Kd = D;
     a.w_packed = w->Mq_tc;
@@ -446,7 +443,7 @@ int orca_attn_query(const orca_attn_weights_t *w, const float *d_feat, const int
   g.m_cap = n_rows_cap;
   g.d_m = d_n_rows;
   g.C = d_qt;
-  dim3 grid(ceil_div(QT_LD, F1_BN), std::min(ceil_div(n_rows_cap, F1_BM), 148));
+  dim3 grid(ceil_div(QT_LD, F1_BN), std::min(ceil_div(n_rows_cap, F1_BM), sm_count()));
   f1_gemm_kernel<EPI_BIAS><<<grid, F1_THREADS, 0, (cudaStream_t)stream>>>(g);
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
@@ -477,7 +474,7 @@ __global__ void win_from_last_pos_kernel(const int32_t *__restrict__ ids, int ca
     win[i] = (i >= all_from || last_pos[ids[i]] == (unsigned long long)(base + i)) ? 1 : 0;
 }
 
-bool projections_on_tensor_cores() { return g_projection_mode == 0; }
+bool projections_on_tensor_cores() { return projection_mode() == 0; }
 
 // d_push_win given: rows with a non-zero byte are pushed.  Otherwise (d_last_pos given) row i is
 // pushed when i >= all_from or when last_pos[push_ids[i]] == base + i; `d_push_win` is then only
@@ -491,7 +488,7 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
   ORCA_CHECK_ARG(w && w->G && w->b1 && w->g && w->W2t && w->b2 && w->ln_w && w->ln_b);
   ORCA_CHECK_ARG(d_ctx && d_valid && d_feat && d_out && n_rows_cap >= 0);
   if (n_rows_cap == 0) return ORCA_OK;
-  if (g_projection_mode != 0 && d_push_table != nullptr && d_last_pos != nullptr) {
+  if (projection_mode() != 0 && d_push_table != nullptr && d_last_pos != nullptr) {
     ORCA_CHECK_ARG(d_push_win != nullptr);
     win_from_last_pos_kernel<<<std::min(ceil_div(n_rows_cap, 256), 1024), 256, 0, stream>>>(
         d_push_ids, n_rows_cap, d_n_rows, reinterpret_cast<const unsigned long long *>(d_last_pos), base, all_from,
@@ -499,11 +496,10 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
     ORCA_COUNT_LAUNCH();
     ORCA_LAUNCH_CHECK();
   }
-  if (g_projection_mode == 0) {
+  if (projection_mode() == 0) {
     // (the tensor-core kernel zeroes the whole first source of an invalid row: zero_cols == its width)
     ORCA_CHECK_ARG(w->G_tc && w->W2t_tc && d_scratch_hidden);
     tc::Args a{};
-    a.status = g_status_word;
     a.a0 = tc::RowSrc{d_ctx, nullptr, QT, 0, 0};
     a.a1 = tc::RowSrc{d_feat, d_idx, D, 0, 0};
     a.Kd = QT + D;
@@ -517,16 +513,12 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
     a.bias2 = w->g;
     a.out = d_scratch_hidden;
     // (19 k-blocks on a single column tile and only ~47 row blocks per batch.  Splitting K over a cluster
-    // of 3 CTAs -- Args::ksplit, which the kernel supports -- was measured slower at 6000 rows: 47
-    // clusters of three 157-KB CTAs do not all fit at once, the summing pass over distributed shared
-    // memory takes 5 us instead of 2, and the raw-message / GRU chain on the side stream loses the SMs
-    // it ran on beside this kernel: 52 us against 47 us for the output phase.)
+    // of 3 CTAs was measured slower at 6000 rows -- 47 clusters of three 157-KB CTAs do not all fit at
+    // once and the summing pass over distributed shared memory takes 5 us instead of 2 -- and was removed.)
     (void)rows_hint;
-    a.ksplit = 1;
     int rc = tc::launch(tc::EPI_HIDDEN, a, 1, (cudaStream_t)stream);
     if (rc) return rc;
     tc::Args b{};
-    b.status = g_status_word;
     b.a0 = tc::RowSrc{d_scratch_hidden, nullptr, D, 0, 0};
     b.Kd = D;
     b.w_packed = w->W2t_tc;
@@ -559,7 +551,63 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
   g.push_table = d_push_table;
   g.push_ids = d_push_ids;
   g.push_win = d_push_win;
-  attn_output_kernel<<<std::min(ceil_div(n_rows_cap, F2_BM), 148 * 4), F2_THREADS, sizeof(F2Smem), (cudaStream_t)stream>>>(g);
+  attn_output_kernel<<<std::min(ceil_div(n_rows_cap, F2_BM), sm_count() * 4), F2_THREADS, sizeof(F2Smem), (cudaStream_t)stream>>>(g);
+  ORCA_COUNT_LAUNCH();
+  ORCA_LAUNCH_CHECK();
+  return ORCA_OK;
+}
+
+}  // namespace orca
+
+namespace orca {
+
+int gru_project(const orca_gru_weights_t *w, const orca_memory_t *mem, const int32_t *d_nodes, int32_t n_cap,
+                const int32_t *d_n, float *d_scratch_h, cudaStream_t s) {
+  ORCA_CHECK_ARG(w && w->Wg && w->bg && mem && mem->memory && mem->last_update && mem->messages &&
+                 mem->msg_ts && mem->msg_flag && d_nodes && d_scratch_h && n_cap >= 0);
+  if (n_cap == 0) return ORCA_OK;
+  if (projection_mode() == 0) {
+    ORCA_CHECK_ARG(w->Wg_tc != nullptr);
+    tc::Args a{};
+    a.a0 = tc::RowSrc{mem->messages, d_nodes, MSG, 0, 0};
+    a.a1 = tc::RowSrc{mem->memory, d_nodes, D, 0, 0};
+    a.Kd = MSG + D;
+    a.w_packed = w->Wg_tc;
+    a.n_kblocks = kblocks(MSG + D);
+    a.m_cap = n_cap;
+    a.d_m = d_n;
+    a.bias = w->bg;
+    a.out = d_scratch_h;
+    a.memory = mem->memory;
+    a.nodes = d_nodes;
+    return tc::launch(tc::EPI_GRU, a, 4, s);
+  }
+  F1Args g{};
+  g.a0 = RowSrc{mem->messages, d_nodes, MSG, 0, 0};
+  g.a1 = RowSrc{mem->memory, d_nodes, D, 0, 0};
+  g.Kd = MSG + D;
+  g.B = w->Wg;
+  g.Nc = 4 * D;
+  g.bias = w->bg;
+  g.m_cap = n_cap;
+  g.d_m = d_n;
+  g.C = d_scratch_h;
+  g.memory = mem->memory;
+  g.nodes = d_nodes;
+  dim3 grid(ceil_div(4 * D, F1_BN), std::min(ceil_div(n_cap, F1_BM), sm_count()));
+  f1_gemm_kernel<EPI_GRU><<<grid, F1_THREADS, 0, s>>>(g);
+  ORCA_COUNT_LAUNCH();
+  ORCA_LAUNCH_CHECK();
+  return ORCA_OK;
+}
+
+int gru_scatter(const orca_memory_t *mem, const int32_t *d_nodes, int32_t n_cap, const int32_t *d_n,
+                int32_t clear_flags, const float *d_scratch_h, cudaStream_t s) {
+  ORCA_CHECK_ARG(mem && mem->memory && mem->last_update && mem->msg_ts && mem->msg_flag && d_nodes && d_scratch_h &&
+                 n_cap >= 0);
+  if (n_cap == 0) return ORCA_OK;
+  ORCA_CUDA(launch_dep(gru_scatter_kernel, ceil_div(n_cap, 4), 256, 0, s, d_scratch_h, *mem, d_nodes, n_cap, d_n,
+                       (int)clear_flags));
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;
@@ -572,10 +620,9 @@ extern "C" {
 int orca_score(const orca_score_weights_t *w, const float *d_emb, int32_t b, float *d_prob, void *stream) {
   ORCA_CHECK_ARG(w && w->W1t && w->b1 && w->w2 && d_emb && d_prob && b >= 0);
   if (b == 0) return ORCA_OK;
-  if (g_projection_mode == 0) {
+  if (projection_mode() == 0) {
     ORCA_CHECK_ARG(w->W1t_tc != nullptr);
     tc::Args a{};
-    a.status = g_status_word;
     // row m < b pairs (src m, dst m); row m >= b pairs (src m-b, neg m-b): table rows m % b and b + m
     a.a0 = tc::RowSrc{d_emb, nullptr, D, b, 0};
     a.a1 = tc::RowSrc{d_emb, nullptr, D, 0, b};
@@ -603,49 +650,9 @@ int64_t orca_gru_scratch_bytes(int32_t n_cap) { return (int64_t)(n_cap > 0 ? n_c
 int orca_gru_update(const orca_gru_weights_t *w, const orca_memory_t *mem, const int32_t *d_nodes,
                     int32_t n_cap, const int32_t *d_n, int32_t clear_flags, float *d_scratch_h,
                     void *stream) {
-  ORCA_CHECK_ARG(w && w->Wg && w->bg && mem && mem->memory && mem->last_update && mem->messages &&
-                 mem->msg_ts && mem->msg_flag && d_nodes && d_scratch_h && n_cap >= 0);
-  if (n_cap == 0) return ORCA_OK;
-  cudaStream_t s = (cudaStream_t)stream;
-  if (g_projection_mode == 0) {
-    ORCA_CHECK_ARG(w->Wg_tc != nullptr);
-    tc::Args a{};
-    a.status = g_status_word;
-    a.a0 = tc::RowSrc{mem->messages, d_nodes, MSG, 0, 0};
-    a.a1 = tc::RowSrc{mem->memory, d_nodes, D, 0, 0};
-    a.Kd = MSG + D;
-    a.w_packed = w->Wg_tc;
-    a.n_kblocks = kblocks(MSG + D);
-    a.m_cap = n_cap;
-    a.d_m = d_n;
-    a.bias = w->bg;
-    a.out = d_scratch_h;
-    a.memory = mem->memory;
-    a.nodes = d_nodes;
-    int rc = tc::launch(tc::EPI_GRU, a, 4, s);
-    if (rc) return rc;
-  } else {
-    F1Args g{};
-    g.a0 = RowSrc{mem->messages, d_nodes, MSG, 0, 0};
-    g.a1 = RowSrc{mem->memory, d_nodes, D, 0, 0};
-    g.Kd = MSG + D;
-    g.B = w->Wg;
-    g.Nc = 4 * D;
-    g.bias = w->bg;
-    g.m_cap = n_cap;
-    g.d_m = d_n;
-    g.C = d_scratch_h;
-    g.memory = mem->memory;
-    g.nodes = d_nodes;
-    dim3 grid(ceil_div(4 * D, F1_BN), std::min(ceil_div(n_cap, F1_BM), 148));
-    f1_gemm_kernel<EPI_GRU><<<grid, F1_THREADS, 0, s>>>(g);
-    ORCA_COUNT_LAUNCH();
-  }
-  ORCA_CUDA(launch_dep(gru_scatter_kernel, ceil_div(n_cap, 4), 256, 0, s, d_scratch_h, *mem, d_nodes, n_cap, d_n,
-                       (int)clear_flags));
-  ORCA_COUNT_LAUNCH();
-  ORCA_LAUNCH_CHECK();
-  return ORCA_OK;
+  int rc = orca::gru_project(w, mem, d_nodes, n_cap, d_n, d_scratch_h, (cudaStream_t)stream);
+  if (rc) return rc;
+  return orca::gru_scatter(mem, d_nodes, n_cap, d_n, clear_flags, d_scratch_h, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------------

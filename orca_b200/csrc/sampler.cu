@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "context.cuh"
 
 namespace orca {
 
@@ -21,10 +22,6 @@ int set_error(int code, const char *fmt, ...) {
 int &launch_counter() {
   static thread_local int c = 0;
   return c;
-}
-bool &dependent_launch_enabled() {
-  static bool on = true;
-  return on;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -550,44 +547,16 @@ compact_flags_kernel(const uint8_t *__restrict__ is_last, int n_cap, const int32
 }
 
 // Last occurrence of every id of a short list and the ordered list of those positions, in one block:
-// record (atomicMax of epoch + position), then flag + scan + emit.  The block first does the batch's
-// other single-block chore when a plan is given -- History.update_flag (modules/history.py:25-30):
-// clear the flags of the plan that set them, set the flags of this plan, keep a copy of it -- so that
-// the side stream of a batch needs one launch for both.
+// record (atomicMax of epoch + position), then flag + scan + emit.
 __global__ void __launch_bounds__(1024)
 last_occ_compact_kernel(const int32_t *__restrict__ ids, int n, int64_t n_nodes,
                         unsigned long long *__restrict__ last_pos, long long base,
-                        int32_t *__restrict__ compact, int32_t *__restrict__ n_compact, int32_t *status,
-                        uint8_t *__restrict__ flag, int32_t *__restrict__ prev_plan, int n_prev,
-                        const int32_t *__restrict__ plan, int n_plan) {
+                        int32_t *__restrict__ compact, int32_t *__restrict__ n_compact, int32_t *status) {
   __shared__ int s_scan[32];
   __shared__ int s_base;
   const int tid = threadIdx.x;
   dep_trigger();
   dep_wait();
-  if (flag != nullptr) {
-    // eight independent loads per thread in flight: the loop is a chain of L2 round trips otherwise
-    for (int i0 = tid; i0 < n_prev; i0 += 8 * 1024) {
-      int v[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = i0 + u * 1024 < n_prev ? prev_plan[i0 + u * 1024] : -1;
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        if (v[u] >= 0 && v[u] < n_nodes) flag[v[u]] = 0;
-    }
-    __threadfence();
-    __syncthreads();
-    for (int i0 = tid; i0 < n_plan; i0 += 8 * 1024) {
-      int v[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = i0 + u * 1024 < n_plan ? plan[i0 + u * 1024] : -1;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        if (v[u] >= 0 && v[u] < n_nodes) flag[v[u]] = 1;
-        if (i0 + u * 1024 < n_plan) prev_plan[i0 + u * 1024] = v[u];
-      }
-    }
-  }
   if (tid == 0) s_base = 0;
   // four positions per thread and sweep, loaded up front so that their round trips overlap
   constexpr int U = 4;
@@ -655,20 +624,25 @@ last_occ_compact_kernel(const int32_t *__restrict__ ids, int n, int64_t n_nodes,
 }
 
 // ---- launchers of the fused batch kernels (used by the batch pipeline)
+static int sm_count() {
+  Ctx *c = cur();
+  return c != nullptr ? c->sm_count : 148;
+}
+
 int launch_batch_head(const orca_tgn_t *m, const int32_t *d_batch, const double *d_bts, int b, int32_t *nodes1,
                       double *ts1, int32_t *cat_dst, int32_t *o_nbr, int32_t *o_eid, float *o_dt, int32_t *status,
-                      long long base, cudaStream_t s) {
+                      int64_t *d_last_pos, long long base, cudaStream_t s) {
   const int k = m->k, n = 3 * b, threads = 256;
   int32_t *cand_count = reinterpret_cast<int32_t *>(m->cand_bitmap + (m->n_nodes + 31) / 32);
   int32_t *cand_list = cand_count + 1;
-  unsigned long long *lp = reinterpret_cast<unsigned long long *>(m->last_pos);
+  unsigned long long *lp = reinterpret_cast<unsigned long long *>(d_last_pos);
   if (k <= 16) {
-    const int grid = std::min(ceil_div(n, threads / 16), 148 * 16);
+    const int grid = std::min(ceil_div(n, threads / 16), sm_count() * 16);
     ORCA_CUDA(launch_dep(batch_head_kernel<16>, grid, threads, 0, s, m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts,
                          m->n_nodes, d_batch, d_bts, b, k, nodes1, ts1, cat_dst, o_nbr, o_eid, o_dt, status,
                          m->cache_flag, m->cand_bitmap, cand_count, cand_list, lp, base));
   } else {
-    const int grid = std::min(ceil_div(n, threads / 32), 148 * 16);
+    const int grid = std::min(ceil_div(n, threads / 32), sm_count() * 16);
     ORCA_CUDA(launch_dep(batch_head_kernel<32>, grid, threads, 0, s, m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts,
                          m->n_nodes, d_batch, d_bts, b, k, nodes1, ts1, cat_dst, o_nbr, o_eid, o_dt, status,
                          m->cache_flag, m->cand_bitmap, cand_count, cand_list, lp, base));
@@ -679,7 +653,8 @@ int launch_batch_head(const orca_tgn_t *m, const int32_t *d_batch, const double 
 }
 
 int launch_uncached_finish(const orca_tgn_t *m, int n_query, int32_t *nodes_io, double *ts_io, int u_cap,
-                           int32_t *d_n_total, int32_t *d_n_unc, int32_t *status, long long base, cudaStream_t s) {
+                           int32_t *d_n_total, int32_t *d_n_unc, int32_t *status, const int64_t *d_last_pos,
+                           long long base, cudaStream_t s) {
   const int64_t words = (m->n_nodes + 31) / 32;
   ORCA_CHECK_ARG(words < (1ll << 31));
   size_t smem = std::max<size_t>(words <= FU_SMEM_WORDS ? (size_t)words * 4 : 0, (size_t)ORCA_CAND_CAP * 4);
@@ -694,18 +669,16 @@ int launch_uncached_finish(const orca_tgn_t *m, int n_query, int32_t *nodes_io, 
   int32_t *cand_count = reinterpret_cast<int32_t *>(m->cand_bitmap + words);
   ORCA_CUDA(launch_dep(uncached_finish_kernel, 1, FU_THREADS, smem, s, m->cand_bitmap, cand_count, cand_count + 1,
                        n_query, m->n_nodes, nodes_io, ts_io, u_cap, d_n_total, d_n_unc, status,
-                       reinterpret_cast<const unsigned long long *>(m->last_pos), (unsigned long long)base));
+                       reinterpret_cast<const unsigned long long *>(d_last_pos), (unsigned long long)base));
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;
 }
 
 int launch_last_occ_compact(const int32_t *d_ids, int n, int64_t n_nodes, int64_t *d_last_pos, long long base,
-                            int32_t *d_compact, int32_t *d_n_compact, int32_t *d_status, uint8_t *d_flag,
-                            int32_t *d_prev_plan, int n_prev, const int32_t *d_plan, int n_plan, cudaStream_t s) {
+                            int32_t *d_compact, int32_t *d_n_compact, int32_t *d_status, cudaStream_t s) {
   ORCA_CUDA(launch_dep(last_occ_compact_kernel, 1, 1024, 0, s, d_ids, n, n_nodes,
-                       reinterpret_cast<unsigned long long *>(d_last_pos), base, d_compact, d_n_compact, d_status,
-                       d_flag, d_prev_plan, n_prev, d_plan, n_plan));
+                       reinterpret_cast<unsigned long long *>(d_last_pos), base, d_compact, d_n_compact, d_status));
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;
@@ -776,13 +749,13 @@ static int orca_sample_topk_impl(const int64_t *d_indptr, const int32_t *d_adj_n
   if (k <= 16) {
     const int per = threads / 16;
     // (a launch whose row count lives on the device usually covers far fewer rows than its capacity)
-    const int grid = std::min(ceil_div(n_query_cap, per), d_n_query ? 148 * 2 : 148 * 16);
+    const int grid = std::min(ceil_div(n_query_cap, per), d_n_query ? sm_count() * 2 : sm_count() * 16);
     ORCA_CUDA(launch_dep(sample_topk_kernel<16>, grid, threads, 0, s, d_indptr, d_adj_nbr, d_adj_eid, d_adj_ts, n_nodes,
                          d_nodes, d_ts, n_query_cap, d_n_query, k, d_nbr, d_eid, d_edge_times, d_delta, d_status,
                          d_cache_flag, d_cand_bitmap));
   } else {
     const int per = threads / 32;
-    const int grid = std::min(ceil_div(n_query_cap, per), 148 * 16);
+    const int grid = std::min(ceil_div(n_query_cap, per), sm_count() * 16);
     ORCA_CUDA(launch_dep(sample_topk_kernel<32>, grid, threads, 0, s, d_indptr, d_adj_nbr, d_adj_eid, d_adj_ts, n_nodes,
                          d_nodes, d_ts, n_query_cap, d_n_query, k, d_nbr, d_eid, d_edge_times, d_delta, d_status,
                          d_cache_flag, d_cand_bitmap));
@@ -818,7 +791,7 @@ int orca_find_before(const int64_t *d_indptr, const double *d_adj_ts, int64_t n_
                      int32_t *d_count, void *stream) {
   ORCA_CHECK_ARG(d_indptr && d_adj_ts && d_nodes && d_ts && d_count && n_query >= 0);
   if (n_query == 0) return ORCA_OK;
-  const int grid = std::min(ceil_div(n_query, 8), 148 * 8);
+  const int grid = std::min(ceil_div(n_query, 8), sm_count() * 8);
   find_before_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(d_indptr, d_adj_ts, n_nodes, d_nodes, d_ts,
                                                             n_query, d_count);
   ORCA_COUNT_LAUNCH();
@@ -896,7 +869,7 @@ int orca_last_occurrence(const int32_t *d_ids, int32_t n_cap, const int32_t *d_n
     if (d_n_compact) ORCA_CUDA(cudaMemsetAsync(d_n_compact, 0, sizeof(int32_t), s));
     return ORCA_OK;
   }
-  const int grid = std::min(ceil_div(n_cap, 256), 148 * 8);
+  const int grid = std::min(ceil_div(n_cap, 256), sm_count() * 8);
   last_pos_mark_kernel<<<grid, 256, 0, s>>>(d_ids, n_cap, d_n, n_nodes, (unsigned long long *)d_last_pos,
                                             (long long)epoch_base);
   ORCA_COUNT_LAUNCH();

@@ -39,6 +39,7 @@
 #include <cuda_bf16.h>
 
 #include "common.cuh"
+#include "context.cuh"
 #include "tc_gemm.cuh"
 
 namespace orca {
@@ -64,15 +65,16 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// bounded wait (about a second of SM clocks); records the failure if the barrier never flipped.
-// `alive` makes the failure sticky: a thread that gave up once does not wait again, so a broken
-// pipeline drains in about a second instead of one time-out per stage.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int32_t *status, int where, bool &alive) {
+// bounded wait (`limit` SM clocks, about a second by default); records the failure if the barrier never
+// flipped.  `alive` makes the failure sticky: a thread that gave up once does not wait again, so a
+// broken pipeline drains in one limit instead of one time-out per stage.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int32_t *status, int where, bool &alive,
+                                          long long limit) {
   if (!alive) return;
   if (mbar_try(bar, parity)) return;
   const long long t0 = clock64();
   while (!mbar_try(bar, parity)) {
-    if (clock64() - t0 > 2000000000ll) {
+    if (clock64() - t0 > limit) {
       report(status, ORCA_E_TIMEOUT, where);
       alive = false;
       return;
@@ -143,21 +145,6 @@ __device__ __forceinline__ void tmem_ld16_sum(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(a[i]) + __uint_as_float(b[i]);
 }
 
-// thread-block cluster helpers (split-K: the CTAs of a cluster share a row block and split its k-blocks)
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float4 ld_peer_f4(uint32_t local_saddr, uint32_t cta_rank) {
-  uint32_t ra;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_saddr), "r"(cta_rank));
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(ra)
-               : "memory");
-  return v;
-}
-
 __device__ __forceinline__ float4 ld_shared_f4(uint32_t saddr) {
   float4 v;
   asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr));
@@ -206,18 +193,6 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
 
 __device__ __align__(16) float g_zero16[4] = {0.f, 0.f, 0.f, 0.f};
 
-// Optional in-kernel timeline (development builds only, -DORCA_TC_TIMELINE): SM clock stamps per CTA.
-#ifdef ORCA_TC_TIMELINE
-__device__ long long g_tl[8192][32];
-#define TL(i)                                                                              \
-  do {                                                                                     \
-    const int bid_ = blockIdx.y * gridDim.x + blockIdx.x;                                  \
-    if (bid_ < 1600) g_tl[EPI * 1600 + bid_][(i)] = clock64();                             \
-  } while (0)
-#else
-#define TL(i)
-#endif
-
 // Pass 2 of the epilogue (all ten warps): one warp per row of the tile that pass 1 left in shared
 // memory, lanes along the columns (two 16-byte pieces per lane); four rows are in flight per warp so
 // that their load / shuffle / store chains overlap.  meta_a / meta_b: lane i of warp w holds the
@@ -225,7 +200,7 @@ __device__ long long g_tl[8192][32];
 template <int EPI>
 __device__ __forceinline__ void tile_output(const Args &g, const float *tile, const float *s_bias, const float *s_v1,
                                             const float *s_v2, const float *s_dot, int m0, int m_rows, int nt,
-                                            int warp, int lane, int meta_a, int meta_b, int ksplit, int crank) {
+                                            int warp, int lane, int meta_a, int meta_b) {
   if (EPI == EPI_SCORE) {
     const int tid = warp * 32 + lane;
     if (tid < m_rows) g.out[m0 + tid] = 1.f / (1.f + expf(-(s_dot[tid] + s_dot[BM + tid] + g.b2)));
@@ -245,39 +220,23 @@ __device__ __forceinline__ void tile_output(const Args &g, const float *tile, co
   const float4 lB = has1 ? *reinterpret_cast<const float4 *>(&s_v2[4 * j1]) : f4z;
   auto add4 = [](float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); };
   const int uA = nt * (BN / 4) + j0, uB = nt * (BN / 4) + j1;   // GRU units of this lane
-  // with split-K the CTAs of the cluster share the rows (row r belongs to CTA r % ksplit) and every value
-  // is the sum of the partial tiles of all CTAs, read over distributed shared memory in rank order
   const uint32_t tile_saddr = smem_addr(tile);
-  for (int it0 = 0; crank + ksplit * (warp + (THREADS / 32) * it0) < m_rows; it0 += RB) {
-#ifdef ORCA_TC_TIMELINE
-    if (warp == 0 && lane == 0 && EPI != EPI_HIDDEN && EPI != EPI_GRU) TL(10 + it0 / RB);
-#endif
+  for (int it0 = 0; warp + (THREADS / 32) * it0 < m_rows; it0 += RB) {
     float4 a[RB], b[RB];
     float hA[RB], hB[RB];
     int ma[RB], mb[RB], m[RB];
     bool ok[RB];
 #pragma unroll
     for (int k = 0; k < RB; ++k) {
-      const int r = crank + ksplit * (warp + (THREADS / 32) * (it0 + k));
+      const int r = warp + (THREADS / 32) * (it0 + k);
       ok[k] = r < m_rows;
       m[k] = m0 + r;
       ma[k] = __shfl_sync(0xffffffffu, meta_a, (it0 + k) & 31);
       mb[k] = __shfl_sync(0xffffffffu, meta_b, (it0 + k) & 31);
       const int rr = ok[k] ? r : 0;
-      if (ksplit == 1) {
-        const uint32_t ra = tile_saddr + (uint32_t)(rr * TILE_LD + 4 * j0) * 4u;
-        a[k] = add4(ld_shared_f4(ra), bA);
-        b[k] = has1 ? add4(ld_shared_f4(ra + 512u), bB) : f4z;
-      } else {
-        const uint32_t ra = tile_saddr + (uint32_t)(rr * TILE_LD + 4 * j0) * 4u;
-        float4 va = ld_peer_f4(ra, 0), vb = has1 ? ld_peer_f4(ra + 512u, 0) : f4z;
-        for (int c = 1; c < ksplit; ++c) {
-          va = add4(va, ld_peer_f4(ra, c));
-          if (has1) vb = add4(vb, ld_peer_f4(ra + 512u, c));
-        }
-        a[k] = add4(va, bA);
-        b[k] = has1 ? add4(vb, bB) : f4z;
-      }
+      const uint32_t ra = tile_saddr + (uint32_t)(rr * TILE_LD + 4 * j0) * 4u;
+      a[k] = add4(ld_shared_f4(ra), bA);
+      b[k] = has1 ? add4(ld_shared_f4(ra + 512u), bB) : f4z;
       hA[k] = hB[k] = 0.f;
       if (EPI == EPI_GRU && ok[k]) {
         const float *hrow = g.memory + (size_t)mb[k] * D;
@@ -377,12 +336,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   const int pw = grp ? warp - 6 : warp;   // producer warp within its group: tile rows pw*32 .. pw*32+31
   const int rsub = lane >> 3, f = lane & 7;
   const int w0 = g.a0.width, w1 = g.a1.width, Kd = g.Kd;
-  // split-K: CTA `crank` of the cluster (1,1,ksplit) takes k-blocks [kb_lo, kb_lo + nkb)
-  const int ksplit = g.ksplit > 1 ? g.ksplit : 1;
-  const int crank = ksplit > 1 ? (int)blockIdx.z : 0;
-  const int kb_per = (g.n_kblocks + ksplit - 1) / ksplit;
-  const int kb_lo = crank * kb_per;
-  const int nkb = max(0, min(g.n_kblocks, kb_lo + kb_per) - kb_lo);
+  const int nkb = g.n_kblocks;
 
   dep_trigger();
   int M = 0;   // live rows (known after the wait below)
@@ -405,7 +359,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
         if (g.row_valid != nullptr && g.zero_cols > 0 && g.row_valid[m] == 0) ri0 = -1;
       }
     }
-    const int r = crank + ksplit * (warp + (THREADS / 32) * lane);
+    const int r = warp + (THREADS / 32) * lane;
     const int m = m0 + r;
     if (r < BM && m < limit) {
       if (EPI == EPI_HIDDEN) meta_a = g.row_valid == nullptr ? 1 : g.row_valid[m];
@@ -433,7 +387,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   const float4 *zero = reinterpret_cast<const float4 *>(g_zero16);
   float4 x[16];
   auto load_stage = [&](int kb) {
-    const int col = (kb_lo + kb) * BK + f * 8;
+    const int col = kb * BK + f * 8;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int r0 = __shfl_sync(0xffffffffu, ri0, 4 * i + rsub);
@@ -456,7 +410,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   auto push_winners = [&](int m0) {
     if (EPI == EPI_LAYERNORM && g.push_table != nullptr && g.push_win == nullptr) {
       // winners by record; only for live rows: the id of a row past the live count is not a valid index
-      const int r = crank + ksplit * (warp + (THREADS / 32) * lane);
+      const int r = warp + (THREADS / 32) * lane;
       const int m = m0 + r;
       if (r < BM && m < M)
         meta_a = (m >= g.push_all_from || g.push_last_pos[meta_b] == (unsigned long long)(g.push_base + m)) ? 1 : 0;
@@ -493,19 +447,6 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   dep_wait();
   prefetch_rows(blockIdx.y * BM, g.m_cap);
   M = rows_of(g.m_cap, g.d_m);
-  if (tid == 0) {
-    TL(0);
-#ifdef ORCA_TC_TIMELINE
-    unsigned long long gt_;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_));
-    const int tb_ = min(blockIdx.y * gridDim.x + blockIdx.x, 1599) + EPI * 1600;
-    g_tl[tb_][28] = (long long)gt_;
-    unsigned smid_;
-    asm volatile("mov.u32 %0, %smid;" : "=r"(smid_));
-    g_tl[tb_][29] = smid_;
-#endif
-  }
-
   fix_rows(blockIdx.y * BM);
   if ((int)blockIdx.y * BM < M && producer && grp < nkb) load_stage(grp);   // in flight across the barrier
   push_winners(blockIdx.y * BM);
@@ -513,7 +454,6 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *slot_ptr;
-  if (tid == 0) TL(1);
   bool alive = true;
   float *tile = reinterpret_cast<float *>(raw + (base - raw_addr));
   __shared__ float s_dot[2][BM];   // scorer: partial dot products of the two column halves
@@ -536,7 +476,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
       const int u0 = t * (grp ? uses1 : uses0);
       const uint32_t st_off = (uint32_t)f * A_LBO + (uint32_t)(pw * 32 + rsub) * 16u;
       for (int kb = grp; kb < nkb; kb += 2) {
-        mbar_wait(empty(s), ((u0 + (kb >> 1)) & 1) ^ 1, g.status, 100 + s, alive);
+        mbar_wait(empty(s), ((u0 + (kb >> 1)) & 1) ^ 1, g.status, 100 + s, alive, g.wait_limit);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           uint4 hi, lo;
@@ -555,11 +495,11 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
       // ---------------------------------------------------------------- weight stages
       if (lane == 0) {
         const char *wsrc = reinterpret_cast<const char *>(g.w_packed) +
-                           ((size_t)nt * g.n_kblocks + kb_lo) * (2 * B_BYTES);
+                           (size_t)nt * g.n_kblocks * (2 * B_BYTES);
         for (int kb = 0; kb < nkb; ++kb) {
           const int s = kb & 1;
           const int u = t * (s ? uses1 : uses0) + (kb >> 1);
-          mbar_wait(empty(s), (u & 1) ^ 1, g.status, 200 + s, alive);
+          mbar_wait(empty(s), (u & 1) ^ 1, g.status, 200 + s, alive, g.wait_limit);
           mbar_expect_tx(full(s), 2 * B_BYTES);
           bulk_g2s(sm.b_hi(s), wsrc + (size_t)kb * (2 * B_BYTES), 2 * B_BYTES, full(s));
         }
@@ -574,9 +514,8 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
         for (int kb = 0; kb < nkb; ++kb) {
           const int s = kb & 1;
           const int u = t * (s ? uses1 : uses0) + (kb >> 1);
-          mbar_wait(full(s), u & 1, g.status, 300 + s, alive);
+          mbar_wait(full(s), u & 1, g.status, 300 + s, alive, g.wait_limit);
           tc_fence_after();
-          if (t == 0 && kb < 20) TL(2 + kb);
 #pragma unroll
           for (int ks = 0; ks < BK / 16; ++ks) {
             const uint64_t ah = make_desc(sm.a_hi(s) + ks * 2 * A_LBO, A_LBO, A_SBO);
@@ -591,7 +530,6 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
           mma_commit(empty(s));  // the stage may be refilled once these MMAs have read it
         }
         mma_commit(accbar);
-        if (t == 0) TL(22);
       }
       __syncwarp();
     }
@@ -603,9 +541,8 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     // idle stage ring, so that pass 2 can write whole rows with coalesced stores.
     const int m_rows = min(BM, M - m0);
     if (producer) {
-      mbar_wait(accbar, t & 1, g.status, 400, alive);
+      mbar_wait(accbar, t & 1, g.status, 400, alive, g.wait_limit);
       tc_fence_after();
-      if (tid == 0 && t == 0) TL(23);
       const int quarter = warp & 3;
       const int row = quarter * 32 + lane;
       const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
@@ -630,17 +567,14 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
       }
       if (EPI == EPI_SCORE) s_dot[grp][row] = dot;
     }
-    if (tid == 0 && t == 0) TL(24);
     tc_fence_before();
-    if (ksplit > 1) cluster_sync_all(); else __syncthreads();   // every partial tile of the cluster is complete
+    __syncthreads();
     tc_fence_after();
-    tile_output<EPI>(g, tile, s_bias, s_v1, s_v2, &s_dot[0][0], m0, m_rows, nt, warp, lane, meta_a, meta_b, ksplit,
-                     crank);
-    if (tid == 0 && t == 0) TL(25);
+    tile_output<EPI>(g, tile, s_bias, s_v1, s_v2, &s_dot[0][0], m0, m_rows, nt, warp, lane, meta_a, meta_b);
     // the tile lives in the stage ring: the next row block's bulk copies and stores may only land
-    // once every warp (of every CTA of the cluster) has read it
+    // once every warp has read it
     fence_async_smem();
-    if (ksplit > 1) cluster_sync_all(); else __syncthreads();
+    __syncthreads();
   }
   if (warp == 5) {
     tc_fence_after();
@@ -666,34 +600,29 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
 
 int launch(int epilogue, const Args &a, int n_tiles, cudaStream_t stream) {
   if (a.m_cap <= 0) return ORCA_OK;
+  Ctx *c = cur();
+  if (c == nullptr) return set_error(ORCA_E_CUDA, "tc::launch: no context for the current device");
   static thread_local int configured_device = -1;
-  int dev = 0;
-  ORCA_CUDA(cudaGetDevice(&dev));
-  if (configured_device != dev) {
+  if (configured_device != c->device) {
     ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_HIDDEN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_LAYERNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_GRU>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_SCORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    configured_device = dev;
-  }
-  // split-K only where every CTA of the cluster gets k-blocks and the epilogue is linear up to pass 2
-  int ksplit = a.ksplit > 1 ? a.ksplit : 1;
-  if (ksplit > 1) {
-    const int per = ceil_div(a.n_kblocks, ksplit);
-    if (epilogue == EPI_SCORE || (ksplit - 1) * per >= a.n_kblocks || ksplit > 8) ksplit = 1;
+    configured_device = c->device;
   }
   Args b = a;
-  b.ksplit = ksplit;
+  b.status = c->status_word;
+  b.wait_limit = c->wait_limit;
   // one wave: a CTA walks several row blocks when there are more tiles than SMs; CTAs past the live row
   // count (m_cap is a capacity) leave at once
-  dim3 grid(n_tiles, std::min(ceil_div(a.m_cap, BM), std::max(1, 148 / (n_tiles * ksplit))), ksplit);
+  dim3 grid(n_tiles, std::min(ceil_div(a.m_cap, BM), std::max(1, c->sm_count / n_tiles)), 1);
   switch (epilogue) {
-    case EPI_BIAS: ORCA_CUDA(launch_dep_cluster(tc_gemm_kernel<EPI_BIAS>, grid, THREADS, SMEM_BYTES, stream, ksplit, b)); break;
-    case EPI_HIDDEN: ORCA_CUDA(launch_dep_cluster(tc_gemm_kernel<EPI_HIDDEN>, grid, THREADS, SMEM_BYTES, stream, ksplit, b)); break;
-    case EPI_LAYERNORM: ORCA_CUDA(launch_dep_cluster(tc_gemm_kernel<EPI_LAYERNORM>, grid, THREADS, SMEM_BYTES, stream, ksplit, b)); break;
-    case EPI_GRU: ORCA_CUDA(launch_dep_cluster(tc_gemm_kernel<EPI_GRU>, grid, THREADS, SMEM_BYTES, stream, ksplit, b)); break;
-    case EPI_SCORE: ORCA_CUDA(launch_dep_cluster(tc_gemm_kernel<EPI_SCORE>, grid, THREADS, SMEM_BYTES, stream, ksplit, b)); break;
+    case EPI_BIAS: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_BIAS>, grid, THREADS, SMEM_BYTES, stream, b)); break;
+    case EPI_HIDDEN: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_HIDDEN>, grid, THREADS, SMEM_BYTES, stream, b)); break;
+    case EPI_LAYERNORM: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_LAYERNORM>, grid, THREADS, SMEM_BYTES, stream, b)); break;
+    case EPI_GRU: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_GRU>, grid, THREADS, SMEM_BYTES, stream, b)); break;
+    case EPI_SCORE: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_SCORE>, grid, THREADS, SMEM_BYTES, stream, b)); break;
     default: return set_error(ORCA_E_BADARG, "tc::launch: unknown epilogue %d", epilogue);
   }
   ORCA_COUNT_LAUNCH();
@@ -703,15 +632,3 @@ int launch(int epilogue, const Args &a, int n_tiles, cudaStream_t stream) {
 
 }  // namespace tc
 }  // namespace orca
-
-#ifdef ORCA_TC_TIMELINE
-extern "C" int orca_tc_timeline_read(long long *h_out, int n_ctas) {
-  if (n_ctas > 8192) n_ctas = 8192;
-  return (int)cudaMemcpyFromSymbol(h_out, orca::tc::g_tl, sizeof(long long) * 32 * n_ctas);
-}
-extern "C" int orca_tc_timeline_clear() {
-  void *p = nullptr;
-  cudaGetSymbolAddress(&p, orca::tc::g_tl);
-  return (int)cudaMemset(p, 0, sizeof(orca::tc::g_tl));
-}
-#endif

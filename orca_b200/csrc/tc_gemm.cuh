@@ -55,7 +55,6 @@ struct Args {
   int zero_cols;
   const void *w_packed;      // [n_tiles][n_kblocks][head | tail] bf16 stage images (weights.pack_tc)
   int n_kblocks;
-  int ksplit;                // > 1: the k-blocks are split over a cluster of this many CTAs (not with SCORE)
   int m_cap;
   const int32_t *d_m;
   const float *bias;         // [n_tiles * BN]
@@ -77,7 +76,8 @@ struct Args {
   // SCORE
   const float *w2;
   float b2;
-  int32_t *status;
+  int32_t *status;           // where a wait that gave up is reported (set by launch() from the context)
+  long long wait_limit;      // SM clocks a wait on an mbarrier may spin (set by launch() from the context)
   PeerOut peer;              // peer.world == 0: no fan-out
 };
 

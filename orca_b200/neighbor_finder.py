@@ -87,7 +87,7 @@ class NeighborFinder:
                                           nodes.data_ptr(), ts.data_ptr(), q, None, k, nbr.data_ptr(),
                                           eid.data_ptr(), et.data_ptr(), _lib.ptr(dt), status.data_ptr(),
                                           _lib.stream_ptr(self.device)))
-            _lib.check(L.orca_read_status(status.data_ptr(), None, _lib.stream_ptr(self.device)))
+            _lib.check(L.orca_read_status(None, status.data_ptr(), None, _lib.stream_ptr(self.device)))
         return nbr, eid, et, dt
 
 

@@ -195,7 +195,14 @@ class TGN(nn.Module):
         self._stage = _Staging()
         self._copy_stream = None       # created with the device ring on the first batch
         self._status = torch.zeros(4, dtype=torch.int32, device=self.device)
-        self._last_pos = torch.zeros(self.n_nodes, dtype=torch.int64, device=self.device)
+        # last-occurrence records: push winners of even / odd batches, message winners
+        self._last_pos = torch.zeros(3 * self.n_nodes, dtype=torch.int64, device=self.device)
+        # this model's context in the library: its auxiliary streams, switches and tracer
+        with torch.cuda.device(self.device):
+            ctx = C.c_void_p(0)
+            _lib.check(_lib.lib().orca_ctx_create(C.byref(ctx)))
+        self._ctx = ctx
+        self._input_stream = None      # stream the batch inputs are made ready on (None: the current stream)
         # candidate bitmap of the uncached set, followed by the candidate list (length word + entries)
         self._cand_bitmap = torch.zeros((self.n_nodes + 31) // 32 + 1 + _lib.CAND_CAP, dtype=torch.int32,
                                         device=self.device)
@@ -205,6 +212,29 @@ class TGN(nn.Module):
         self._rank, self._world, self._group = 0, 1, None
         self._exchange = None          # direct exchange buffers of the multi-GPU split (set_distributed)
         self._mode = MODE_BUDGET
+
+    def __del__(self):
+        ctx = getattr(self, "_ctx", None)
+        if ctx is not None and ctx.value:
+            try:
+                _lib.lib().orca_ctx_destroy(ctx)
+            except Exception:      # interpreter shutdown
+                pass
+            self._ctx = None
+
+    def set_option(self, option, value):
+        """Switch of this model's context (_lib.OPT_*: projection mode, overlap, dependent launch,
+        look-ahead, wait limit, trace)."""
+        _lib.check(_lib.lib().orca_ctx_set(self._ctx, int(option), int(value)))
+
+    def last_layer1_nodes(self, n_rows):
+        """Node ids of the last batch's layer-1 row list [src | dst | neg | uncached] (its first n_rows
+        entries), read back from the batch workspace.  Synchronises."""
+        L = _lib.lib()
+        b, u_cap, k = self._ws_key
+        off = L.orca_eval_workspace_row_list(b, u_cap, k, self.n_nodes, L.orca_ctx_last_parity(self._ctx))
+        torch.cuda.synchronize(self.device)
+        return self._ws[off: off + 4 * n_rows].view(torch.int32).cpu().numpy()
 
     def set_distributed(self, rank, world, group=None, exchange="direct"):
         """Shard every batch's attention rows and link scores over `world` GPUs of one node (one
@@ -220,9 +250,9 @@ class TGN(nn.Module):
         self._exchange = None
         if self._world > 1 and exchange == "direct":
             import torch.distributed as dist
-            cap = self.exchange_floats(int(self.args.bs), self._world)
-            # one allocation per rank: 2 * cap floats of rows, then 16 flag words
-            xbuf = torch.zeros(2 * cap + 16, dtype=torch.float32, device=self.device)
+            cap = self.exchange_floats(int(self.args.bs), self._world, int(self.args.n_degree), self.n_nodes)
+            # one allocation per rank: EXCHANGE_SLOTS * cap floats of rows, then 16 flag words
+            xbuf = torch.zeros(_lib.EXCHANGE_SLOTS * cap + 16, dtype=torch.float32, device=self.device)
             torch.cuda.synchronize(self.device)
             L = _lib.lib()
             rows, flags, keep, err = [], [], [xbuf], None
@@ -246,7 +276,7 @@ class TGN(nn.Module):
                             _lib.check(L.orca_ipc_open(h, handles[r][1], C.byref(out)))
                             base = out.value
                         rows.append(base)
-                        flags.append(base + 8 * cap)      # byte offset of the flag words: 2 * cap floats
+                        flags.append(base + 4 * _lib.EXCHANGE_SLOTS * cap)      # byte offset of the flag words
                 except _lib.OrcaError as e:
                     err = e
             else:
@@ -263,14 +293,15 @@ class TGN(nn.Module):
             dist.barrier(group=group)
 
     @staticmethod
-    def exchange_floats(bs, world):
-        """Floats per half of an exchange buffer for batches of up to `bs` edges: `world` slots of
-        rows_per_rank(3*bs + 3*bs) rows (the sharded path bounds the uncached set by 3*bs)."""
-        return world * shard.rows_per_rank(6 * bs, world) * _lib.DIM
+    def exchange_floats(bs, world, k, n_nodes):
+        """Floats per slot of an exchange buffer for batches of up to `bs` edges: `world` blocks of
+        rows_per_rank(3*bs + u_cap) rows, u_cap = min(3*bs*k, n_nodes) being the most uncached
+        neighbours a batch can have (a cold cache on the first batch reaches it)."""
+        return world * shard.rows_per_rank(3 * bs + min(3 * bs * k, n_nodes), world) * _lib.DIM
 
     def set_exchange(self, row_ptrs, flag_ptrs, cap, keep_alive=()):
-        """Device addresses, as seen by this process, of every rank's exchange buffer (2 * cap floats)
-        and flag words (int32[16], zeroed)."""
+        """Device addresses, as seen by this process, of every rank's exchange buffer (EXCHANGE_SLOTS *
+        cap floats) and flag words (int32[16], zeroed)."""
         self._exchange = (list(row_ptrs), list(flag_ptrs), int(cap), list(keep_alive))
         self._exchange_seq = np.zeros(1, dtype=np.int64)
         self._desc_ref = None
@@ -332,6 +363,7 @@ class TGN(nn.Module):
                 t.plan_cap = h.prev_plan.numel()
             t.rank, t.world = self._rank, self._world
             t.mode = self._mode
+            t.input_stream = self._input_stream
             return t
         t = _lib.TgnT()
         if getattr(self, "_exchange", None) is not None:
@@ -369,19 +401,28 @@ class TGN(nn.Module):
         t.rank, t.world = self._rank, self._world
         t.cand_bitmap = self._cand_bitmap.data_ptr()
         t.mode = self._mode
+        t.ctx = self._ctx
+        t.input_stream = self._input_stream
         return t
 
     def _workspace(self, b, k):
         u_cap = min(3 * b * k, self.n_nodes) if self.n_layers == 2 else 0
         if self.n_layers == 2 and self._mode == MODE_NO_REUSE:
             u_cap = 3 * b * k          # one layer-1 row per neighbour slot
-        if self._world > 1:
-            u_cap = min(u_cap, 3 * b)   # bounds the all-gather; a larger uncached set is reported as an error
         key = (b, u_cap, k)
-        if self._ws_key is None or self._ws_key[0] < b or self._ws_key[1] < u_cap or self._ws_key[2] != k:
-            nbytes = _lib.lib().orca_eval_workspace_bytes(b, u_cap, k, self.n_nodes)
-            self._ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
-            self._ws_key = key
+        if self._ws_key != key:
+            # the workspace layout follows (b, u_cap, k): batches of another size get a workspace of their own
+            # (kept, so that a stream whose last batch is short does not reallocate twice); the library's
+            # side streams may still be reading the old one, hence the synchronisation
+            cache = self.__dict__.setdefault("_ws_cache", {})
+            if self._ws is not None:
+                torch.cuda.synchronize(self.device)
+                cache[self._ws_key] = self._ws
+            ws = cache.get(key)
+            if ws is None:
+                nbytes = _lib.lib().orca_eval_workspace_bytes(b, u_cap, k, self.n_nodes)
+                ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            self._ws, self._ws_key = ws, key
         return self._ws, u_cap
 
     # ---- one eval batch ----------------------------------------------------------------------------
@@ -434,6 +475,7 @@ class TGN(nn.Module):
         self._ev_copied[ds].record(self._copy_stream)
         self._stage.mark(slot, self._copy_stream)
         cur.wait_event(self._ev_copied[ds])
+        self._input_stream = self._copy_stream.cuda_stream     # the library orders its side streams after the copy
         stream = cur.cuda_stream
         ws, u_cap = self._workspace(b, k)
         prob = torch.empty(2 * b, device=self.device)
@@ -468,16 +510,22 @@ class TGN(nn.Module):
         b_max = shard.rows_per_rank(b, world)
         s = _lib.stream_ptr(self.device)
         direct = getattr(self, "_exchange", None) is not None
-        emb1_local = None if direct else torch.empty(rpr, _lib.DIM, device=self.device)
-        _lib.check(L.orca_tgn_eval_batch_sharded(desc, 1, d_i32, d_ts, b, d_plan, n_plan, u_cap, ws.data_ptr(),
-                                                 ws.numel(), _lib.ptr(emb1_local), None, None, None,
-                                                 self._status.data_ptr(), s))
-        emb1_all = None if direct else shard.all_gather_rows(emb1_local, self._group)
         prob_local = torch.zeros(2 * b_max, device=self.device)
         emb2_local = torch.zeros(3 * b_max, _lib.DIM, device=self.device) if want_emb else None
-        _lib.check(L.orca_tgn_eval_batch_sharded(desc, 2, d_i32, d_ts, b, d_plan, n_plan, u_cap, ws.data_ptr(),
-                                                 ws.numel(), None, _lib.ptr(emb1_all), prob_local.data_ptr(),
-                                                 _lib.ptr(emb2_local), self._status.data_ptr(), s))
+        if direct:
+            # the library moves the layer-1 rows itself (peer stores): the whole batch is one call
+            _lib.check(L.orca_tgn_eval_batch_sharded(desc, 0, d_i32, d_ts, b, d_plan, n_plan, u_cap, ws.data_ptr(),
+                                                     ws.numel(), None, None, prob_local.data_ptr(),
+                                                     _lib.ptr(emb2_local), self._status.data_ptr(), s))
+        else:
+            emb1_local = torch.empty(rpr, _lib.DIM, device=self.device)
+            _lib.check(L.orca_tgn_eval_batch_sharded(desc, 1, d_i32, d_ts, b, d_plan, n_plan, u_cap, ws.data_ptr(),
+                                                     ws.numel(), emb1_local.data_ptr(), None, None, None,
+                                                     self._status.data_ptr(), s))
+            emb1_all = shard.all_gather_rows(emb1_local, self._group)
+            _lib.check(L.orca_tgn_eval_batch_sharded(desc, 2, d_i32, d_ts, b, d_plan, n_plan, u_cap, ws.data_ptr(),
+                                                     ws.numel(), None, emb1_all.data_ptr(), prob_local.data_ptr(),
+                                                     _lib.ptr(emb2_local), self._status.data_ptr(), s))
         prob = shard.assemble_edges(shard.all_gather_rows(prob_local, self._group), b, 2)
         emb = shard.assemble_edges(shard.all_gather_rows(emb2_local, self._group), b, 3) if want_emb else None
         return prob, emb
@@ -486,7 +534,8 @@ class TGN(nn.Module):
         """Synchronises and raises if a kernel reported an error since the last check; returns
         (rows at layer 1, unique positives, kernel launches) of the last batch."""
         h = np.zeros(4, dtype=np.int32)
-        _lib.check(_lib.lib().orca_read_status(self._status.data_ptr(), h.ctypes.data, _lib.stream_ptr(self.device)))
+        _lib.check(_lib.lib().orca_read_status(self._ctx, self._status.data_ptr(), h.ctypes.data,
+                                               _lib.stream_ptr(self.device)))
         self.last_counts = (int(h[1]), int(h[2]), int(h[3]))
         return self.last_counts
 

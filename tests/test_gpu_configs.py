@@ -33,10 +33,8 @@ def _batch(g, neg, b):
 
 
 def _uncached_rows(tgn, n, n1):
-    """The appended layer-1 rows of the last batch: entries [3n, n1) of the row list, which is the
-    first array of the batch workspace."""
-    torch.cuda.synchronize()
-    return tgn._ws[: 4 * n1].view(torch.int32)[3 * n:n1].cpu().numpy()
+    """The appended layer-1 rows of the last batch: entries [3n, n1) of its row list."""
+    return tgn.last_layer1_nodes(n1)[3 * n:]
 
 
 def _copy_state_to_oracle(tgn, orc):

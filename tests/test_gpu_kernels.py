@@ -118,7 +118,7 @@ def test_find_uncached(dev, n_nodes):
         _lib.check(L.orca_find_uncached(d_nbr.data_ptr(), nq, k, d_flag.data_ptr(),
                                         n_nodes, nodes_io.data_ptr(), ts_io.data_ptr(), u_cap, n_total.data_ptr(),
                                         scratch.data_ptr(), status.data_ptr(), _lib.stream_ptr(dev)))
-        _lib.check(L.orca_read_status(status.data_ptr(), None, _lib.stream_ptr(dev)))
+        _lib.check(L.orca_read_status(None, status.data_ptr(), None, _lib.stream_ptr(dev)))
         n = int(n_total.item())
         assert n == nq + len(want)
         assert np.array_equal(nodes_io[nq:n].cpu().numpy(), want)
@@ -143,7 +143,7 @@ def test_find_uncached_capacity_is_reported(dev):
                                     ts_io.data_ptr(), 5, n_total.data_ptr(), scratch.data_ptr(), status.data_ptr(),
                                     _lib.stream_ptr(dev)))
     with pytest.raises(_lib.OrcaError) as e:
-        _lib.check(L.orca_read_status(status.data_ptr(), None, _lib.stream_ptr(dev)))
+        _lib.check(L.orca_read_status(None, status.data_ptr(), None, _lib.stream_ptr(dev)))
     assert e.value.code == 4
     assert int(n_total.item()) == 15
     assert np.array_equal(nodes_io[10:].cpu().numpy(), np.arange(2, 7))   # first entry (1) is dropped
@@ -200,9 +200,9 @@ def _attention_case(seed, n, k, n_tab=400):
 def fp32_projections():
     """Runs the projections on the plain fp32 SIMT tiles (the debug reference of the tensor-core path)."""
     from orca_b200 import _lib
-    _lib.check(_lib.lib().orca_set_projection_mode(1))
+    _lib.check(_lib.lib().orca_ctx_set(None, _lib.OPT_PROJECTION_MODE, 1))
     yield
-    _lib.check(_lib.lib().orca_set_projection_mode(0))
+    _lib.check(_lib.lib().orca_ctx_set(None, _lib.OPT_PROJECTION_MODE, 0))
 
 
 def test_attention_layer_fp32_projections(dev, fp32_projections, capsys):
@@ -238,7 +238,7 @@ def test_attention_layer(dev, k, n, layer):
     out = torch.zeros(cap, D, device=dev)
     status = torch.zeros(4, dtype=torch.int32, device=dev)
     s = _lib.stream_ptr(dev)
-    _lib.check(L.orca_set_status_word(status.data_ptr()))
+    _lib.check(L.orca_ctx_set_status_word(None, status.data_ptr()))
     _lib.check(L.orca_attn_query(ws, t_tab.data_ptr(), d_src.data_ptr(), cap, n_dev.data_ptr(), qt.data_ptr(), s))
     _lib.check(L.orca_attn_gather(qt.data_ptr(), t_tab.data_ptr(), t_etab.data_ptr(), tw.data_ptr(), d_nbr.data_ptr(),
                                   d_eid.data_ptr(), d_dt.data_ptr(), k, cap, n_dev.data_ptr(), ctx.data_ptr(),
@@ -249,8 +249,8 @@ def test_attention_layer(dev, k, n, layer):
     _lib.check(L.orca_attn_output(ws, ctx.data_ptr(), valid.data_ptr(), t_tab.data_ptr(), d_src.data_ptr(), cap,
                                   n_dev.data_ptr(), out.data_ptr(), push_table.data_ptr(), d_src.data_ptr(),
                                   win.data_ptr(), hidden.data_ptr(), s))
-    _lib.check(L.orca_read_status(status.data_ptr(), None, s))
-    _lib.check(L.orca_set_status_word(None))
+    _lib.check(L.orca_read_status(None, status.data_ptr(), None, s))
+    _lib.check(L.orca_ctx_set_status_word(None, None))
     got = out[:n].cpu().numpy()
     err = max_rel(got, want, floor=0.05)
     print(f"attention layer k={k} n={n} layer={layer}: max rel err {err:.2e}")
@@ -418,7 +418,7 @@ def test_find_uncached_marked_by_sampler(dev, n_nodes):
                                            d_flag.data_ptr(), bitmap.data_ptr(), s))
         _lib.check(L.orca_find_uncached_marked(bitmap.data_ptr(), nq, n_nodes, nodes_io.data_ptr(), ts_io.data_ptr(),
                                                u_cap, n_total.data_ptr(), status.data_ptr(), s))
-        _lib.check(L.orca_read_status(status.data_ptr(), None, s))
+        _lib.check(L.orca_read_status(None, status.data_ptr(), None, s))
         n = int(n_total.item())
         assert np.array_equal(nbr.cpu().numpy(), nbr_want)
         assert n == nq + len(want)

@@ -211,30 +211,59 @@ def test_recursions_share_one_model():
         b.compute_edge_probabilities(src, dst, neg, ts, eidx, spec.n_degree, True, False, None)
 
 
-def test_dependent_launch_changes_nothing():
-    """Kernels enqueued with programmatic stream serialisation give bit-identical results to plain
-    stream-ordered launches (scores and state tables)."""
+@pytest.mark.parametrize("option", ["dependent_launch", "lookahead", "overlap"])
+def test_scheduling_switches_change_nothing(option):
+    """Programmatic dependent launch, the four-stream look-ahead of the batch pipeline and the side stream
+    of the raw-message / GRU chain only change WHEN kernels run: scores and state tables must be bit-identical
+    with each of them off."""
     from orca_b200 import _lib
     g = graph("t_nb2")
     spec = g.spec
     gold = golden("t_nb2")
     plan = unpack(gold[f"plan_{spec.strategy}_flat"], gold[f"plan_{spec.strategy}_off"])
+    opt = {"dependent_launch": _lib.OPT_DEPENDENT_LAUNCH, "lookahead": _lib.OPT_LOOKAHEAD,
+           "overlap": _lib.OPT_OVERLAP}[option]
     out = []
-    try:
-        for enable in (0, 1):
-            _lib.check(_lib.lib().orca_set_dependent_launch(enable))
-            tgn = make_model(g)
-            scores = []
-            for b, src, dst, ts, eidx in batches(g, 12):
-                p, q = tgn.compute_edge_probabilities(src, dst, np.roll(dst, 1), ts, eidx, spec.n_degree, True, False,
-                                                      plan[b])
-                scores.append(torch.cat([p, q]).clone())
-            tgn.check_status()
-            out.append((torch.cat(scores), tgn.memory.memory.clone(), tgn.embedding_module.histories[0].emb.clone()))
-    finally:
-        _lib.check(_lib.lib().orca_set_dependent_launch(1))
+    for enable in (0, 1):
+        tgn = make_model(g)
+        tgn.set_option(opt, enable)
+        scores = []
+        for b, src, dst, ts, eidx in batches(g, 12):
+            # no synchronisation between the batches: the lanes really run ahead of each other
+            p, q = tgn.compute_edge_probabilities(src, dst, np.roll(dst, 1), ts, eidx, spec.n_degree, True, False,
+                                                  plan[b])
+            scores.append(torch.cat([p, q]))
+        tgn.check_status()
+        out.append((torch.cat(scores).clone(), tgn.memory.memory.clone(), tgn.memory.messages.clone(),
+                    tgn.embedding_module.histories[0].emb.clone(),
+                    tgn.embedding_module.histories[0].cache_flag_dev.clone()))
     for a, b in zip(out[0], out[1]):
         assert torch.equal(a, b)
+
+
+def test_batches_of_changing_size_share_a_model():
+    """A stream whose batches differ in size (the short last batch of every stream) lays the workspace out
+    anew while the previous batch may still be in flight on the library's side streams."""
+    g = graph("t_nb2")
+    spec = g.spec
+    sizes = [200, 37, 200, 5, 163, 200]
+    ref, tgn = make_model(g), make_model(g)
+    from orca_b200 import _lib
+    ref.set_option(_lib.OPT_LOOKAHEAD, 0)
+    lo = 0
+    got, want = [], []
+    for n in sizes:
+        sl = slice(lo, lo + n)
+        a = (g.sources[sl], g.destinations[sl], np.roll(g.destinations[sl], 1), g.timestamps[sl], g.edge_idxs[sl])
+        plan = np.unique(np.r_[a[0], a[1]])[: spec.budget]
+        want.append(torch.cat(ref.compute_edge_probabilities(*a, spec.n_degree, True, False, plan)))
+        ref.check_status()        # the reference run is synchronised batch by batch, this one is not
+        got.append(torch.cat(tgn.compute_edge_probabilities(*a, spec.n_degree, True, False, plan)))
+        lo += n
+    tgn.check_status()
+    assert torch.equal(torch.cat(got), torch.cat(want))
+    assert torch.equal(tgn.memory.memory, ref.memory.memory)
+    assert torch.equal(tgn.embedding_module.histories[0].emb, ref.embedding_module.histories[0].emb)
 
 
 def test_unsupported_modes_fail_loudly():
@@ -262,12 +291,16 @@ def test_sharded_entry_points_with_emulated_ranks(world, direct):
     ranks = [make_model(g) for _ in range(world)]
     for r, m in enumerate(ranks):
         m._rank, m._world = r, world
+        # one stream for everything: the ranks share this GPU, and a rank's wait for its peers' rows must
+        # never be scheduled ahead of the kernels that deliver them
+        m.set_option(_lib.OPT_LOOKAHEAD, 0)
+        m.set_option(_lib.OPT_OVERLAP, 0)
     dev = ref.device
     if direct:
         # the ranks' exchange buffers and flag words; on one GPU a "peer" address is a plain device address
         from orca_b200.tgn import TGN
-        cap = TGN.exchange_floats(spec.bs, world)
-        bufs = [torch.zeros(2 * cap, device=dev) for _ in range(world)]
+        cap = TGN.exchange_floats(spec.bs, world, spec.n_degree, g.n_nodes)
+        bufs = [torch.zeros(_lib.EXCHANGE_SLOTS * cap, device=dev) for _ in range(world)]
         flags = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(world)]
         for m in ranks:
             m.set_exchange([x.data_ptr() for x in bufs], [f.data_ptr() for f in flags], cap, bufs + flags)
