@@ -45,6 +45,9 @@ def parse():
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="N > 1: strong = the workload's batch split over the GPUs (default); weak = a batch of "
                          "bs edges PER GPU, i.e. the same stream cut into batches of bs * N edges")
+    ap.add_argument("--min-seconds", type=float, default=1.0,
+                    help="the timed window of --steps steps is repeated until this much time has been timed; the "
+                         "median window is reported (0: one window, e.g. under a profiler)")
     ap.add_argument("--plan-batches", type=int, default=None,
                     help="plan only this many leading batches of the stream (quick runs)")
     return ap.parse_args()
@@ -241,11 +244,11 @@ def run_ours(a):
     sampler = ClockSampler(local)
     sampler.start()
 
-    def timed(fn_step, min_seconds=1.0, max_repeats=400):
+    def timed(fn_step, min_seconds=a.min_seconds, max_repeats=400):
         """W untimed + K timed steps from the same reset state, repeated until `min_seconds` of timed region
         have accumulated; returns (median ms of a K-step window, repeats, host ms per window)."""
         ms_all, host_all, total = [], [], 0.0
-        while total < min_seconds * 1e3 and len(ms_all) < max_repeats:
+        while (total < min_seconds * 1e3 or not ms_all) and len(ms_all) < max_repeats:
             reset_state(tgn, plan, first)
             for i in range(W):
                 fn_step(i, False)

@@ -24,54 +24,116 @@ constexpr int GA_WARPS = GA_THREADS / 32;
 //   pass 1  every lane owns a fixed set of key columns -- 16-byte pieces l, l+32, l+64 of the
 //           gathered [neighbour | edge feature] part, loaded straight from the tables into registers
 //           with 128-bit loads (the next slot's pieces are requested before the current slot is
-//           processed), and columns l, l+32, ... of the time-encoding part, which is computed
-//           (cos of delta * w) and parked in shared memory.  The lane's partial dot products with
+//           processed), and column PAIRS l, l+32, l+64 of the time-encoding part, which is computed
+//           (cos of delta * w) two columns at a time with the packed two-wide fp32 instructions of this
+//           architecture (fma.rn.f32x2: half the issue slots for the range reduction, the dot products
+//           and the weighted sums) and parked in shared memory.  The lane's partial dot products with
 //           the two query heads are parked too; no cross-lane work happens inside the slot loop.
 //   softmax the 2 * slots partial-sum rows are reduced by 2 * slots lanes at once, the two heads'
 //           softmax runs across lanes;
 //   pass 2  the gathered pieces are loaded again (they sit in L1/L2 now), the time encodings come back
 //           from shared memory, and the weighted key sum is accumulated in registers.
 // Keeping the reductions and the exponentials out of the slot loops matters: with one row per warp
-// the kernel is bound by the length of each warp's dependent instruction chain, not by bandwidth.
+// the kernel is bound by the length of each warp's dependent instruction chain, not by bandwidth (a
+// single pass with a running softmax needs a warp-wide reduction per slot and measured 15 % slower).
 // (The 688-byte rows are not moved by cp.async.bulk: an SM retires only about one small bulk copy
 // per ~130 cycles, which capped an earlier version at 1.5 TB/s whatever else it did.)
 //
-// Rows are handed out by ticket (one atomic per row on a counter the launch leaves at zero again), not
-// by a fixed stride: rows differ tenfold in cost (0 to k valid slots) and a launch holds only two to
-// four rows per resident warp, so a static split ends with most warps idle behind the unlucky ones.
-// A warp draws its next ticket and loads that row's slot indices before it works on the current row,
-// and -- between the two passes -- asks for the next row's neighbour and edge-feature rows to be
-// brought into L2 (prefetch.global.L2, one 32-byte sector per lane): the gathers are random 688-byte
-// reads over gigabytes, each a DRAM access behind a TLB miss, and without the prefetch a row's five
-// double-buffered load rounds each pay that latency in full.
-// The multiply-adds are the packed two-wide form (fma.rn.f32x2 of this architecture): half the issue
-// slots for the dot products and the weighted sums.
+// Work distribution.  Rows differ tenfold in cost (0 to k valid slots, 1 to 14 us) and a launch holds
+// only two to three rows per resident warp, so WHO gets WHICH row decides the length of the launch:
+//   - rows are handed out by ticket (one atomic per row on a counter the launch leaves at zero again);
+//   - a warp draws its next ticket only when it enters pass 2 of the current row: drawing it a whole
+//     row ahead commits slow warps to one more row while fast warps run dry (measured: 38 -> 33 us);
+//   - tickets walk the rows in the order of `order` (rows sorted by falling number of valid slots,
+//     made by row_order_kernel beside the sampling), so that the launch ends on its lightest rows.
+// The projected query of the next row (4.2 KB) is staged in shared memory with cp.async during pass 2,
+// its slot indices are loaded then too: a row starts with everything but its gathers at hand.
 // No block-level synchronisation; a block is eight independent warps.
 constexpr int GA_MEM_F4 = 2 * D / 4;            // 86 sixteen-byte pieces of [neighbour | edge feature]
 constexpr int GA_ROW_F4 = D / 4;                // 43 pieces per table row
-constexpr int GA_T_ITERS = (D + 31) / 32;       // 6 time columns per lane (the last one partial)
+constexpr int GA_P_ITERS = 3;                   // pieces / time-column pairs per lane (the third for lanes 0..21)
 constexpr int GA_TE_LD = 172;                   // floats per parked time encoding
 constexpr int GA_PART_LD = 33;                  // 32 partial sums + 1 pad (conflict-free column reads)
-constexpr int GA_ROW_SECTORS = 22;              // 32-byte sectors a 688-byte row can touch, minus none: a row
-                                                // that starts 16 bytes into a sector ends 16 bytes into its 22nd
-__host__ __device__ constexpr int ga_warp_floats(int k) { return k * GA_TE_LD + 2 * k * GA_PART_LD; }
+constexpr int GA_Q_FLOATS = QT_LD;              // staged query: head h at h * 528, 516 floats used
+constexpr int GA_Q_CHUNKS = KEY / 4;            // 129 sixteen-byte chunks per head
+// (a multiple of four floats: the staged query of every warp starts on a 16-byte boundary, as its 16-byte
+// asynchronous copies and 128-bit reads need)
+__host__ __device__ constexpr int ga_warp_floats(int k) {
+  return (GA_Q_FLOATS + k * GA_TE_LD + 2 * k * GA_PART_LD + 3) & ~3;
+}
 
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 dup2(float v) { return make_float2(v, v); }
 __device__ __forceinline__ float2 lo2(const float4 &v) { return make_float2(v.x, v.y); }
 __device__ __forceinline__ float2 hi2(const float4 &v) { return make_float2(v.z, v.w); }
-__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+               "l"(gsrc)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
 
-// Time encodings of one slot for this lane's columns lane, lane+32, ...: the first NL column groups
-// hold large arguments (fixed-point reduction), the others small ones (fp32 reduction).  w decreases
-// with the column, so "large" groups are always a prefix; NL is uniform over the warp and the body is
-// branch free, which lets the six cosines of a lane overlap.
+// cos of two arguments below 2^15 at once: the Cody-Waite reduction of cos_small in packed arithmetic;
+// the nearest integer of x / 2pi comes from adding and subtracting 1.5 * 2^23
+__device__ __forceinline__ float2 cos_small2(float2 x) {
+  const float2 t = mul2(x, dup2(0.15915494309189535f));
+  const float2 kk = add2(add2(t, dup2(12582912.f)), dup2(-12582912.f));
+  float2 r = fma2(kk, dup2(-6.28125f), x);
+  r = fma2(kk, dup2(-0.0019350051879882812f), r);
+  r = fma2(kk, dup2(-3.019916050561733e-07f), r);
+  return make_float2(__cosf(r.x), __cosf(r.y));
+}
+
+// Time encodings of one slot for this lane's column pairs: the first NL pair groups (64 columns each) hold
+// large arguments (fixed-point reduction), the others small ones (packed fp32 reduction).  w decreases with
+// the column, so "large" groups are always a prefix; NL is uniform over the warp and the body is branch free.
 template <int NL>
-__device__ __forceinline__ void time_terms(float dt, const float (&wt)[6], float (&te)[6]) {
+__device__ __forceinline__ void time_terms(float dt, const float2 (&wt)[GA_P_ITERS], float2 (&te)[GA_P_ITERS]) {
 #pragma unroll
-  for (int i = 0; i < 6; ++i) {
-    const float x = dt * wt[i];
-    te[i] = i < NL ? cos_fixed(x) : cos_small(x);
+  for (int i = 0; i < GA_P_ITERS; ++i) {
+    const float2 x = mul2(dup2(dt), wt[i]);
+    te[i] = i < NL ? make_float2(cos_fixed(x.x), cos_fixed(x.y)) : cos_small2(x);
   }
+}
+
+// Rows sorted by falling number of valid slots (counting sort, one block): order[0 .. n) = row ids.  The
+// tables are right-aligned (padding first), so a row's count is k minus the position of its first neighbour.
+__global__ void __launch_bounds__(1024)
+row_order_kernel(const int32_t *__restrict__ nbr_a, int n_cap_a, const int32_t *__restrict__ d_n_a,
+                 int32_t *__restrict__ order_a, const int32_t *__restrict__ nbr_b, int n_cap_b,
+                 const int32_t *__restrict__ d_n_b, int32_t *__restrict__ order_b, int k) {
+  __shared__ int s_bin[ORCA_MAX_K + 1];
+  dep_trigger();
+  dep_wait();
+  // block 0 orders table a, block 1 table b
+  const int32_t *nbr = blockIdx.x == 0 ? nbr_a : nbr_b;
+  int32_t *order = blockIdx.x == 0 ? order_a : order_b;
+  const int n = blockIdx.x == 0 ? rows_of(n_cap_a, d_n_a) : rows_of(n_cap_b, d_n_b);
+  const int tid = threadIdx.x;
+  if (tid <= ORCA_MAX_K) s_bin[tid] = 0;
+  __syncthreads();
+  auto count = [&](int r) {
+    const int32_t *row = nbr + (size_t)r * k;
+    int c = 0;
+    for (int j = 0; j < k; ++j) c += row[j] != 0 ? 1 : 0;
+    return c;
+  };
+  for (int r = tid; r < n; r += 1024) atomicAdd(&s_bin[count(r)], 1);
+  __syncthreads();
+  if (tid == 0) {   // bins -> first position, heaviest bin first
+    int pos = 0;
+    for (int c = k; c >= 0; --c) {
+      const int m = s_bin[c];
+      s_bin[c] = pos;
+      pos += m;
+    }
+  }
+  __syncthreads();
+  for (int r = tid; r < n; r += 1024) order[atomicAdd(&s_bin[count(r)], 1)] = r;
 }
 
 __global__ void __launch_bounds__(GA_THREADS, 2)
@@ -79,73 +141,73 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
                    const float *__restrict__ edge_table, const float *__restrict__ time_w,
                    const int32_t *__restrict__ nbr, const int32_t *__restrict__ eid,
                    const float *__restrict__ delta, int k, int n_cap, const int32_t *__restrict__ d_n,
-                   float *__restrict__ ctx, uint8_t *__restrict__ valid_out, int32_t *__restrict__ ticket,
-                   unsigned long long *__restrict__ prof) {
+                   const int32_t *__restrict__ order, float *__restrict__ ctx, uint8_t *__restrict__ valid_out,
+                   int32_t *__restrict__ ticket, unsigned long long *__restrict__ prof) {
   extern __shared__ __align__(128) float smem[];
   constexpr unsigned FULL = 0xffffffffu;
   dep_trigger();
   dep_wait();
   const int n = rows_of(n_cap, d_n);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float *s_te = smem + warp * ga_warp_floats(k);  // [k][172]
+  float *s_q = smem + warp * ga_warp_floats(k);   // staged query of the coming row
+  float *s_te = s_q + GA_Q_FLOATS;                // [k][172]
   float *s_part = s_te + k * GA_TE_LD;            // [2k][33]
-  // this lane's time-encoding frequencies
-  float wt[GA_T_ITERS];
+  const bool third = lane + 64 < GA_MEM_F4;       // lanes 0..21 own a third piece / pair
+  // this lane's time-encoding frequencies, as column pairs, and the largest frequency of each pair group
+  float2 wt[GA_P_ITERS];
 #pragma unroll
-  for (int i = 0; i < GA_T_ITERS; ++i) wt[i] = (lane + 32 * i < D) ? __ldg(time_w + lane + 32 * i) : 0.f;
-  const bool third = lane + 64 < GA_MEM_F4;       // lanes 0..21 own a third 16-byte piece
-  const bool tail_col = lane + 32 * (GA_T_ITERS - 1) < D;   // lanes 0..11 own a sixth time column
+  for (int i = 0; i < GA_P_ITERS; ++i)
+    wt[i] = (i < 2 || third) ? __ldg(reinterpret_cast<const float2 *>(time_w) + lane + 32 * i) : make_float2(0.f, 0.f);
+  const float wg0 = __ldg(time_w), wg1 = __ldg(time_w + 64), wg2 = __ldg(time_w + 128);
   unsigned long long prof_rows = 0, prof_slots = 0;
 
-  auto draw = [&]() -> int {
-    int r = 0;
-    if (lane == 0) r = atomicAdd(&ticket[0], 1);
-    return __shfl_sync(FULL, r, 0);
+  auto row_of_ticket = [&](int t) -> int { return order != nullptr ? order[t] : t; };
+  auto load_indices = [&](int r, int &o_nbr, int &o_eid, float &o_dt) {
+    o_nbr = 0, o_eid = 0, o_dt = 0.f;
+    if (lane < k) {
+      const size_t o = (size_t)r * k + lane;
+      o_nbr = nbr[o];
+      o_eid = eid[o];
+      o_dt = delta[o];
+    }
   };
-  int row = draw();
+  // stages the projected query of row r (both heads) in this warp's buffer
+  auto stage_query = [&](int r) {
+    const float4 *src = reinterpret_cast<const float4 *>(qt + (size_t)r * QT_LD);
+    float4 *dst = reinterpret_cast<float4 *>(s_q);
+    for (int c = lane; c < 2 * GA_Q_CHUNKS; c += 32) {
+      const int h = c >= GA_Q_CHUNKS ? 1 : 0;
+      const int o = h * (QT_HEAD / 4) + (c - h * GA_Q_CHUNKS);
+      cp_async16(dst + o, src + o);
+    }
+  };
+
+  int tkt = 0;
+  if (lane == 0) tkt = atomicAdd(&ticket[0], 1);
+  tkt = __shfl_sync(FULL, tkt, 0);
+  int row = tkt < n ? row_of_ticket(tkt) : -1;
   int my_nbr = 0, my_eid = 0;
   float my_dt = 0.f;
-  if (row < n && lane < k) {
-    const size_t o = (size_t)row * k + lane;
-    my_nbr = nbr[o];
-    my_eid = eid[o];
-    my_dt = delta[o];
+  if (row >= 0) {
+    load_indices(row, my_nbr, my_eid, my_dt);
+    stage_query(row);
   }
-  while (row < n) {
-    // the next row of this warp: the ticket is requested now and read (with that row's slot indices) once
-    // the first loads of the current row are under way
-    int tkt = 0;
-    if (lane == 0) tkt = atomicAdd(&ticket[0], 1);
-    int next = 0, nx_nbr = 0, nx_eid = 0;
+  while (row >= 0) {
+    int next = -1, nx_nbr = 0, nx_eid = 0;
     float nx_dt = 0.f;
-    auto fetch_next = [&]() {
-      next = __shfl_sync(FULL, tkt, 0);
-      if (next < n && lane < k) {
-        const size_t o = (size_t)next * k + lane;
-        nx_nbr = nbr[o];
-        nx_eid = eid[o];
-        nx_dt = delta[o];
-      }
-    };
-    // asks for the table rows of the next row's valid slots to be brought into L2
-    auto prefetch_next = [&]() {
-      unsigned nm = __ballot_sync(FULL, nx_nbr != 0);
-      while (nm) {
-        const int j = __ffs(nm) - 1;
-        nm &= nm - 1;
-        const int nb = __shfl_sync(FULL, nx_nbr, j), ei = __shfl_sync(FULL, nx_eid, j);
-        const char *nrow = reinterpret_cast<const char *>(nbr_table + (size_t)nb * D);
-        const char *erow = reinterpret_cast<const char *>(edge_table + (size_t)ei * D);
-        prefetch_l2(lane < GA_ROW_SECTORS ? nrow + 32 * lane : erow + 32 * (lane - GA_ROW_SECTORS));
-        if (lane < 2 * GA_ROW_SECTORS - 32) prefetch_l2(erow + 32 * (lane + 32 - GA_ROW_SECTORS));
-      }
-    };
     const unsigned vmask = __ballot_sync(FULL, my_nbr != 0);
     if (vmask == 0) {
       // every slot is padding: the layer ignores the attention term for this row
       if (lane == 0) valid_out[row] = 0;
-      fetch_next();
-      prefetch_next();
+      cp_async_wait_all();     // (the staged query is not used: let it land before the buffer is refilled)
+      __syncwarp();
+      if (lane == 0) tkt = atomicAdd(&ticket[0], 1);
+      tkt = __shfl_sync(FULL, tkt, 0);
+      if (tkt < n) {
+        next = row_of_ticket(tkt);
+        load_indices(next, nx_nbr, nx_eid, nx_dt);
+        stage_query(next);
+      }
     } else {
       const int n_valid = __popc(vmask);
       // this lane's pieces of a slot: piece l of the neighbour row; piece l+32 of the concatenation
@@ -169,39 +231,33 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
       int j0 = __ffs(todo) - 1;
       todo &= todo - 1;
       load_slot(j0, xa);
-      // which column groups of this lane's slot need the fixed-point cosine (see time_terms)
-      int my_nl = 0;
+      // which pair groups of this lane's slot need the fixed-point cosine (see time_terms)
+      int my_nl;
       {
         const float adt = fabsf(my_dt);
-#pragma unroll
-        for (int i = 0; i < GA_T_ITERS; ++i) my_nl += adt * __ldg(time_w + 32 * i) >= 32768.f ? 1 : 0;
-        if (!(adt * __ldg(time_w) < 1073741824.f)) my_nl = -1;   // beyond the fixed-point range (or not finite)
+        my_nl = (adt * wg0 >= 32768.f ? 1 : 0) + (adt * wg1 >= 32768.f ? 1 : 0) + (adt * wg2 >= 32768.f ? 1 : 0);
+        if (!(adt * wg0 < 1073741824.f)) my_nl = -1;   // beyond the fixed-point range (or not finite)
       }
-      // the lane's pieces of the two query heads (head h starts at h * 528 in the projected query);
-      // the time part is kept as (head 0, head 1) pairs for the two-wide multiply-adds
-      const float *qrow = qt + (size_t)row * QT_LD;
+      // the lane's pieces of the two query heads, from the staged copy (requested during the previous row)
+      cp_async_wait_all();
+      __syncwarp();
       float4 qa[3], qb[3];
-      float2 qtt[GA_T_ITERS];
+      float2 qta[GA_P_ITERS], qtb[GA_P_ITERS];
 #pragma unroll
-      for (int i = 0; i < 3; ++i) {
+      for (int i = 0; i < GA_P_ITERS; ++i) {
         const int f = (i < 2 || third) ? lane + 32 * i : 0;
-        qa[i] = __ldg(reinterpret_cast<const float4 *>(qrow) + f);
-        qb[i] = __ldg(reinterpret_cast<const float4 *>(qrow + QT_HEAD) + f);
+        qa[i] = reinterpret_cast<const float4 *>(s_q)[f];
+        qb[i] = reinterpret_cast<const float4 *>(s_q + QT_HEAD)[f];
+        qta[i] = reinterpret_cast<const float2 *>(s_q + 2 * D)[f];
+        qtb[i] = reinterpret_cast<const float2 *>(s_q + QT_HEAD + 2 * D)[f];
       }
-#pragma unroll
-      for (int i = 0; i < GA_T_ITERS; ++i) {
-        const bool in = i < GA_T_ITERS - 1 || tail_col;
-        const int c = in ? lane + 32 * i : 0;
-        const float a = __ldg(qrow + 2 * D + c), b = __ldg(qrow + QT_HEAD + 2 * D + c);
-        qtt[i] = in ? make_float2(a, b) : make_float2(0.f, 0.f);   // a column past the end contributes nothing
-      }
-      fetch_next();
+      __syncwarp();   // every lane holds its pieces: the buffer may be refilled
 
       // ---- pass 1: time encodings and partial logits, slot by slot
       auto pass1_slot = [&](int it, int j, const float4(&x)[3]) {
         const float dt = __shfl_sync(FULL, my_dt, j);
         const int nl = __shfl_sync(FULL, my_nl, j);
-        float te[GA_T_ITERS];
+        float2 te[GA_P_ITERS];
         switch (nl) {
           case 0: time_terms<0>(dt, wt, te); break;
           case 1: time_terms<1>(dt, wt, te); break;
@@ -209,26 +265,23 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
           case 3: time_terms<3>(dt, wt, te); break;
           default:
 #pragma unroll
-            for (int i = 0; i < GA_T_ITERS; ++i) te[i] = cos_any(dt * wt[i]);
-        }
-        float2 st = make_float2(0.f, 0.f);             // (head 0, head 1) over the time columns
-#pragma unroll
-        for (int i = 0; i < GA_T_ITERS; ++i) {
-          if (i < GA_T_ITERS - 1 || tail_col) s_te[it * GA_TE_LD + lane + 32 * i] = te[i];
-          st = fma2(make_float2(te[i], te[i]), qtt[i], st);
+            for (int i = 0; i < GA_P_ITERS; ++i) te[i] = make_float2(cos_any(dt * wt[i].x), cos_any(dt * wt[i].y));
         }
         float2 a0 = make_float2(0.f, 0.f), a1 = make_float2(0.f, 0.f);   // head 0 / head 1, two partial sums each
 #pragma unroll
-        for (int i = 0; i < 3; ++i) {
+        for (int i = 0; i < GA_P_ITERS; ++i) {
           if (i < 2 || third) {
+            reinterpret_cast<float2 *>(s_te + it * GA_TE_LD)[lane + 32 * i] = te[i];
+            a0 = fma2(te[i], qta[i], a0);
+            a1 = fma2(te[i], qtb[i], a1);
             a0 = fma2(lo2(x[i]), lo2(qa[i]), a0);
             a0 = fma2(hi2(x[i]), hi2(qa[i]), a0);
             a1 = fma2(lo2(x[i]), lo2(qb[i]), a1);
             a1 = fma2(hi2(x[i]), hi2(qb[i]), a1);
           }
         }
-        s_part[(2 * it) * GA_PART_LD + lane] = a0.x + a0.y + st.x;
-        s_part[(2 * it + 1) * GA_PART_LD + lane] = a1.x + a1.y + st.y;
+        s_part[(2 * it) * GA_PART_LD + lane] = a0.x + a0.y;
+        s_part[(2 * it + 1) * GA_PART_LD + lane] = a1.x + a1.y;
       };
       for (int it = 0; it < n_valid; it += 2) {
         int j1 = -1;
@@ -247,11 +300,11 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
         pass1_slot(it + 1, j1, xb);
       }
       __syncwarp();
-      // pass 2's first slot goes out before the softmax, the next row's prefetches behind it
+      // the next ticket is drawn now, not a row ahead; pass 2's first slot goes out before the softmax
+      if (lane == 0) tkt = atomicAdd(&ticket[0], 1);
       todo = vmask;
       load_slot(__ffs(todo) - 1, xa);
       todo &= todo - 1;
-      prefetch_next();
 
       // ---- softmax: lane p reduces partial row p = 2 * slot + head; heads live on even / odd lanes
       // (k <= 16 keeps all 2k rows on the 32 lanes; for larger k a lane takes rows p and p + 32)
@@ -259,16 +312,22 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
       {
         float lg_lo = -INFINITY, lg_hi = -INFINITY;
         if (lane < 2 * n_valid) {
-          float a = 0.f;
+          float a = 0.f, b = 0.f;
 #pragma unroll 8
-          for (int t = 0; t < 32; ++t) a += s_part[lane * GA_PART_LD + t];
-          lg_lo = a;
+          for (int t = 0; t < 32; t += 2) {
+            a += s_part[lane * GA_PART_LD + t];
+            b += s_part[lane * GA_PART_LD + t + 1];
+          }
+          lg_lo = a + b;
         }
         if (lane + 32 < 2 * n_valid) {
-          float a = 0.f;
+          float a = 0.f, b = 0.f;
 #pragma unroll 8
-          for (int t = 0; t < 32; ++t) a += s_part[(lane + 32) * GA_PART_LD + t];
-          lg_hi = a;
+          for (int t = 0; t < 32; t += 2) {
+            a += s_part[(lane + 32) * GA_PART_LD + t];
+            b += s_part[(lane + 32) * GA_PART_LD + t + 1];
+          }
+          lg_hi = a + b;
         }
         float m = fmaxf(lg_lo, lg_hi);               // lanes of equal parity hold the same head
 #pragma unroll
@@ -282,19 +341,26 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
         prob_lo = e_lo * inv;
         prob_hi = e_hi * inv;
       }
+      // the next row of this warp: its indices and its query are requested now and land during pass 2
+      tkt = __shfl_sync(FULL, tkt, 0);
+      if (tkt < n) {
+        next = row_of_ticket(tkt);
+        load_indices(next, nx_nbr, nx_eid, nx_dt);
+        stage_query(next);
+      }
 
       // ---- pass 2: weighted key sum
       float4 am0[3], am1[3];                         // gathered part, heads 0 / 1
-      float2 at[GA_T_ITERS];                         // time part, (head 0, head 1)
+      float2 at0[GA_P_ITERS], at1[GA_P_ITERS];       // time part
 #pragma unroll
       for (int i = 0; i < 3; ++i) am0[i] = am1[i] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int i = 0; i < GA_T_ITERS; ++i) at[i] = make_float2(0.f, 0.f);
+      for (int i = 0; i < GA_P_ITERS; ++i) at0[i] = at1[i] = make_float2(0.f, 0.f);
       auto pass2_slot = [&](int it, const float4(&x)[3]) {
         const int p = 2 * it;
         const float p0 = p < 32 ? __shfl_sync(FULL, prob_lo, p) : __shfl_sync(FULL, prob_hi, p - 32);
         const float p1 = p < 32 ? __shfl_sync(FULL, prob_lo, p + 1) : __shfl_sync(FULL, prob_hi, p - 31);
-        const float2 P0 = make_float2(p0, p0), P1 = make_float2(p1, p1), P01 = make_float2(p0, p1);
+        const float2 P0 = dup2(p0), P1 = dup2(p1);
 #pragma unroll
         for (int i = 0; i < 3; ++i) {
           float2 r;
@@ -304,10 +370,11 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
           r = fma2(P1, hi2(x[i]), hi2(am1[i])); am1[i].z = r.x; am1[i].w = r.y;
         }
 #pragma unroll
-        for (int i = 0; i < GA_T_ITERS; ++i) {
-          if (i < GA_T_ITERS - 1 || tail_col) {
-            const float te = s_te[it * GA_TE_LD + lane + 32 * i];
-            at[i] = fma2(P01, make_float2(te, te), at[i]);
+        for (int i = 0; i < GA_P_ITERS; ++i) {
+          if (i < 2 || third) {
+            const float2 te = reinterpret_cast<const float2 *>(s_te + it * GA_TE_LD)[lane + 32 * i];
+            at0[i] = fma2(P0, te, at0[i]);
+            at1[i] = fma2(P1, te, at1[i]);
           }
         }
       };
@@ -332,13 +399,8 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
         if (i < 2 || third) {
           reinterpret_cast<float4 *>(out)[lane + 32 * i] = am0[i];
           reinterpret_cast<float4 *>(out + KEY)[lane + 32 * i] = am1[i];
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < GA_T_ITERS; ++i) {
-        if (i < GA_T_ITERS - 1 || tail_col) {
-          out[2 * D + lane + 32 * i] = at[i].x;
-          out[KEY + 2 * D + lane + 32 * i] = at[i].y;
+          reinterpret_cast<float2 *>(out + 2 * D)[lane + 32 * i] = at0[i];
+          reinterpret_cast<float2 *>(out + KEY + 2 * D)[lane + 32 * i] = at1[i];
         }
       }
       if (lane == 0) valid_out[row] = 1;
@@ -369,8 +431,8 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
 // need words of their own
 int launch_attn_gather(const float *d_qt, const float *d_nbr_table, const float *d_edge_table,
                        const float *d_time_w, const int32_t *d_nbr, const int32_t *d_eid, const float *d_delta,
-                       int k, int n_rows_cap, const int32_t *d_n_rows, int rows_hint, float *d_ctx,
-                       uint8_t *d_valid, int32_t *d_ticket, cudaStream_t stream) {
+                       int k, int n_rows_cap, const int32_t *d_n_rows, int rows_hint, const int32_t *d_order,
+                       float *d_ctx, uint8_t *d_valid, int32_t *d_ticket, cudaStream_t stream) {
   ORCA_CHECK_ARG(d_qt && d_nbr_table && d_edge_table && d_time_w && d_nbr && d_eid && d_delta && d_ctx &&
                  d_valid && d_ticket);
   ORCA_CHECK_ARG(k >= 1 && k <= ORCA_MAX_K && n_rows_cap >= 0);
@@ -379,8 +441,9 @@ int launch_attn_gather(const float *d_qt, const float *d_nbr_table, const float 
   if (n_rows_cap == 0) return ORCA_OK;
   Ctx *c = cur();
   if (c == nullptr) return set_error(ORCA_E_CUDA, "orca_attn_gather: no context for the current device");
-  // two blocks per SM share its shared memory: as many warps per block as fit into half of it
-  const int warps = std::max(1, std::min(GA_WARPS, GA_SMEM_LIMIT / 2 / (ga_warp_floats(k) * (int)sizeof(float))));
+  // two blocks per SM share its shared memory (1 KB per block is the system's): as many warps per block as
+  // fit into half of it
+  const int warps = std::max(1, std::min(GA_WARPS, (GA_SMEM_LIMIT / 2 - 1024) / (ga_warp_floats(k) * (int)sizeof(float))));
   const size_t smem = (size_t)warps * ga_warp_floats(k) * sizeof(float);
   static thread_local int configured_device = -1;
   if (configured_device != c->device) {
@@ -405,16 +468,30 @@ int launch_attn_gather(const float *d_qt, const float *d_nbr_table, const float 
   // (the profiling events would sit between this kernel and its neighbours: plain launch then)
   if (pf.on)
     attn_gather_kernel<<<grid, warps * 32, smem, stream>>>(d_qt, d_nbr_table, d_edge_table, d_time_w, d_nbr, d_eid,
-                                                           d_delta, k, n_rows_cap, d_n_rows, d_ctx, d_valid, d_ticket,
-                                                           pf.d_counters);
+                                                           d_delta, k, n_rows_cap, d_n_rows, d_order, d_ctx, d_valid,
+                                                           d_ticket, pf.d_counters);
   else
     ORCA_CUDA(launch_dep(attn_gather_kernel, grid, warps * 32, smem, stream, d_qt, d_nbr_table, d_edge_table,
-                         d_time_w, d_nbr, d_eid, d_delta, (int)k, (int)n_rows_cap, d_n_rows, d_ctx, d_valid, d_ticket,
+                         d_time_w, d_nbr, d_eid, d_delta, (int)k, (int)n_rows_cap, d_n_rows, d_order, d_ctx, d_valid, d_ticket,
                          (unsigned long long *)nullptr));
   if (pf.on) {
     ORCA_CUDA(cudaEventRecord(pf.ev[pf.used + 1], stream));
     pf.used += 2;
   }
+  ORCA_COUNT_LAUNCH();
+  ORCA_LAUNCH_CHECK();
+  return ORCA_OK;
+}
+
+// rows of two neighbour tables (the two attention layers of a batch) in the order the gather kernel should
+// take them: heaviest first
+int launch_row_order(const int32_t *d_nbr_a, int n_cap_a, const int32_t *d_n_a, int32_t *d_order_a,
+                     const int32_t *d_nbr_b, int n_cap_b, const int32_t *d_n_b, int32_t *d_order_b, int k,
+                     cudaStream_t stream) {
+  ORCA_CHECK_ARG(d_nbr_a && d_order_a && d_nbr_b && d_order_b && k >= 1 && k <= ORCA_MAX_K && n_cap_a >= 0 &&
+                 n_cap_b >= 0);
+  ORCA_CUDA(launch_dep(row_order_kernel, 2, 1024, 0, stream, d_nbr_a, (int)n_cap_a, d_n_a, d_order_a, d_nbr_b,
+                       (int)n_cap_b, d_n_b, d_order_b, (int)k));
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;
@@ -433,5 +510,5 @@ extern "C" int orca_attn_gather(const float *d_qt, const float *d_nbr_table, con
   Ctx *c = cur();
   if (c == nullptr) return set_error(ORCA_E_CUDA, "orca_attn_gather: no context for the current device");
   return launch_attn_gather(d_qt, d_nbr_table, d_edge_table, d_time_w, d_nbr, d_eid, d_delta, k, n_rows_cap,
-                            d_n_rows, 0, d_ctx, d_valid, c->d_words + CTX_TICKET_MAIN, (cudaStream_t)stream);
+                            d_n_rows, 0, nullptr, d_ctx, d_valid, c->d_words + CTX_TICKET_MAIN, (cudaStream_t)stream);
 }

@@ -25,11 +25,16 @@ int launch_last_occ_compact(const int32_t *d_ids, int n, int64_t n_nodes, int64_
 
 // the fused gather-attention kernel (attention.cu); d_ticket: two zeroed device words that the launch
 // leaves at zero (launches that may overlap on the GPU need words of their own); rows_hint > 0: the live
-// row count the caller expects (n_rows_cap is a capacity)
+// row count the caller expects (n_rows_cap is a capacity); d_order (optional): the row ids in the order the
+// warps should take them (launch_row_order)
 int launch_attn_gather(const float *d_qt, const float *d_nbr_table, const float *d_edge_table,
                        const float *d_time_w, const int32_t *d_nbr, const int32_t *d_eid, const float *d_delta,
-                       int k, int n_rows_cap, const int32_t *d_n_rows, int rows_hint, float *d_ctx,
-                       uint8_t *d_valid, int32_t *d_ticket, cudaStream_t stream);
+                       int k, int n_rows_cap, const int32_t *d_n_rows, int rows_hint, const int32_t *d_order,
+                       float *d_ctx, uint8_t *d_valid, int32_t *d_ticket, cudaStream_t stream);
+// rows of two neighbour tables sorted by falling number of valid slots (one launch, one block per table)
+int launch_row_order(const int32_t *d_nbr_a, int n_cap_a, const int32_t *d_n_a, int32_t *d_order_a,
+                     const int32_t *d_nbr_b, int n_cap_b, const int32_t *d_n_b, int32_t *d_order_b, int k,
+                     cudaStream_t stream);
 
 // the two halves of orca_gru_update (gemm.cu): the projection + gates into d_scratch_h reads the tables
 // only; the scatter writes memory / last_update and clears the message flags

@@ -38,6 +38,7 @@ struct IdxBuf {
   int32_t *cat_dst; int32_t *win_pos; int32_t *n_win; int32_t *win_nodes;
   int32_t *loc_nodes; double *loc_ts; int32_t *n1_loc;               // sharded layer 1
   int32_t *feat_idx; int32_t *nbr2_loc, *eid2_loc; float *dt2_loc;  // sharded layer 2 / no-reuse index
+  int32_t *order1, *order2;                    // rows of the two gather launches, heaviest first
 };
 // projection / gather buffers of one attention layer in flight (one set per compute lane)
 struct LaneBuf {
@@ -83,6 +84,8 @@ static Workspace carve(void *base, int b_cap, int u_cap, int k, int64_t n_nodes)
     x.nbr2_loc = (int32_t *)take(N * k * 4);
     x.eid2_loc = (int32_t *)take(N * k * 4);
     x.dt2_loc = (float *)take(N * k * 4);
+    x.order1 = (int32_t *)take(R1 * 4);
+    x.order2 = (int32_t *)take(N * 4);
   }
   for (int q = 0; q < 2; ++q) {
     const size_t rows = q == 0 ? R1 : N;   // lane 0: layer 1 (and the one-lane modes), lane 1: layer 2
@@ -339,7 +342,7 @@ static int eval_serial(const orca_tgn_t *m, Ctx *c, const int32_t *d_batch_i32, 
     ORCA_TRY(orca_attn_query(&m->attn[0], m->mem.memory, x.nodes1, N, nullptr, l.qt, s));
     ORCA_TRY(tr.mark(PH_QUERY_L2, s));
     ORCA_TRY(launch_attn_gather(l.qt, m->mem.memory, m->edge_table, m->time_w, x.nbr1, x.eid1, x.dt1, k, N, nullptr,
-                                0, l.ctx, l.valid, tk, s));
+                                0, nullptr, l.ctx, l.valid, tk, s));
     ORCA_TRY(tr.mark(PH_GATHER_L2, s));
     ORCA_TRY(orca_attn_output(&m->attn[0], l.ctx, l.valid, m->mem.memory, x.nodes1, N, nullptr, emb_top,
                               nullptr, nullptr, nullptr, l.hidden, s));
@@ -381,7 +384,7 @@ static int eval_serial(const orca_tgn_t *m, Ctx *c, const int32_t *d_batch_i32, 
     ORCA_TRY(orca_attn_query(&m->attn[0], m->mem.memory, x.nodes1, R1, d_n1, l.qt, s));
     ORCA_TRY(tr.mark(PH_QUERY_L1, s));
     ORCA_TRY(launch_attn_gather(l.qt, m->mem.memory, m->edge_table, m->time_w, nbr1, eid1, dt1, k, R1, d_n1,
-                                mode == ORCA_MODE_NO_REUSE ? R1 : N, l.ctx, l.valid, tk, s));
+                                mode == ORCA_MODE_NO_REUSE ? R1 : N, nullptr, l.ctx, l.valid, tk, s));
     ORCA_TRY(tr.mark(PH_GATHER_L1, s));
     ORCA_TRY(attn_output_impl(&m->attn[0], l.ctx, l.valid, m->mem.memory, x.nodes1, R1, d_n1, w.emb1[0],
                               push1 ? m->hist_emb : nullptr, push1 ? x.nodes1 : nullptr, push1 ? w.win1 : nullptr,
@@ -396,7 +399,7 @@ static int eval_serial(const orca_tgn_t *m, Ctx *c, const int32_t *d_batch_i32, 
     ORCA_TRY(orca_attn_query(&m->attn[1], w.emb1[0], nullptr, N, nullptr, l.qt, s));
     ORCA_TRY(tr.mark(PH_QUERY_L2, s));
     ORCA_TRY(launch_attn_gather(l.qt, table2, m->edge_table, m->time_w, gather2, x.eid2, x.dt2, k, N, nullptr, 0,
-                                l.ctx, l.valid, tk, s));
+                                nullptr, l.ctx, l.valid, tk, s));
     ORCA_TRY(tr.mark(PH_GATHER_L2, s));
     ORCA_TRY(orca_attn_output(&m->attn[1], l.ctx, l.valid, w.emb1[0], nullptr, N, nullptr, emb_top, nullptr,
                               nullptr, nullptr, l.hidden, s));
@@ -507,6 +510,11 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
                                 u_cap, x.n_unc, k, x.nbr1 + (size_t)N * k, x.eid1 + (size_t)N * k, nullptr,
                                 x.dt1 + (size_t)N * k, d_status, si));
     }
+    // the order in which the two gather launches hand out their rows (heaviest first)
+    if (sharded)
+      ORCA_TRY(launch_row_order(x.nbr1, rpr, x.n1_loc, x.order1, x.nbr2_loc, 3 * b_loc, nullptr, x.order2, k, si));
+    else
+      ORCA_TRY(launch_row_order(x.nbr1, R1, x.n1, x.order1, x.nbr1, N, nullptr, x.order2, k, si));
     ORCA_TRY(tr.mark(PH_SAMPLE_L1, s));
     // winners of the raw messages: last occurrence per node in [src|dst] (model/tgn_model.py:172-176)
     ORCA_TRY(launch_last_occ_compact(d_batch_i32, 2 * b, m->n_nodes, lp_msg, c->base_msg, x.win_pos, x.n_win,
@@ -554,7 +562,7 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
     ORCA_TRY(orca_attn_query(&m->attn[0], m->mem.memory, rows1, cap1, d_n1, l1.qt, sa));
     ORCA_TRY(tr.mark(PH_QUERY_L1, s));
     ORCA_TRY(launch_attn_gather(l1.qt, m->mem.memory, m->edge_table, m->time_w, x.nbr1, x.eid1, x.dt1, k, cap1, d_n1,
-                                sharded ? rpr : N, l1.ctx, l1.valid, c->d_words + CTX_TICKET_MAIN, sa));
+                                sharded ? rpr : N, x.order1, l1.ctx, l1.valid, c->d_words + CTX_TICKET_MAIN, sa));
     ORCA_TRY(tr.mark(PH_GATHER_L1, s));
     if (!sharded) {
       // the push into the history table waits for the previous batch's top layer to have read it
@@ -641,7 +649,7 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
       ORCA_TRY(orca_attn_query(&m->attn[1], feat2, feat2_idx, rows2, nullptr, l2.qt, s));
       ORCA_TRY(tr.mark(PH_QUERY_L2, s));
       ORCA_TRY(launch_attn_gather(l2.qt, m->hist_emb, m->edge_table, m->time_w, nbr2, eid2, dt2, k, rows2, nullptr, 0,
-                                  l2.ctx, l2.valid, c->d_words + CTX_TICKET_SIDE, s));
+                                  x.order2, l2.ctx, l2.valid, c->d_words + CTX_TICKET_SIDE, s));
       ORCA_TRY(tr.mark(PH_GATHER_L2, s));
       if (!sharded && sa != s) {
         ORCA_CUDA(cudaEventRecord(c->ev_g2, s));

@@ -214,13 +214,13 @@ class TGN(nn.Module):
         self._mode = MODE_BUDGET
 
     def __del__(self):
-        ctx = getattr(self, "_ctx", None)
+        ctx = self.__dict__.get("_ctx")
         if ctx is not None and ctx.value:
+            self.__dict__["_ctx"] = None
             try:
                 _lib.lib().orca_ctx_destroy(ctx)
             except Exception:      # interpreter shutdown
                 pass
-            self._ctx = None
 
     def set_option(self, option, value):
         """Switch of this model's context (_lib.OPT_*: projection mode, overlap, dependent launch,
