@@ -435,6 +435,34 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
                                 float *d_emb1_local, const float *d_emb1_all, float *d_prob_local,
                                 float *d_emb2_local, int32_t *d_status, void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * A whole stream of batches in one call: the loop of evaluation/evaluation.py:18-37 (one
+ * compute_edge_probabilities per batch, scores brought back to the host) without a host round trip per
+ * batch.  The batches lie packed in PINNED host memory; the call enqueues, per batch, the host-to-device
+ * copy of its arrays (on a copy stream of the model's context, into a ring of 4 staging slots, ahead of the
+ * kernels), the batch itself (orca_tgn_eval_batch, or both phases of orca_tgn_eval_batch_sharded when
+ * m->world > 1 with the direct exchange) and the device-to-host copy of its scores.  Nothing is
+ * synchronised: the scores are complete in `stream` order.
+ *   h_i32 + off_i32[i]  [src | dst | neg | eidx | plan] of batch i: 4*b[i] + max(n_plan[i], 0) int32
+ *   h_ts + off_ts[i]    b[i] float64
+ *   n_plan[i] < 0       batch i has no plan (the cumulative flag rule of modules/history.py:29-30)
+ *   off_prob[i]         where batch i's scores go in d_prob / h_prob (floats): [pos | neg], 2*b[i] of them, or
+ *                       2*b_local of this rank's edges when sharded (edge e belongs to rank e % world)
+ * d_stage: device memory for the staging ring, 4 slots of stage_bytes/4 each (a slot holds one batch:
+ * 16*b + 4*n_plan + 8*b bytes, rounded up to 256).  d_prob: device floats; h_prob (pinned, may be NULL):
+ * the same layout on the host.  The workspace must be sized for the largest batch.
+ */
+typedef struct {
+  const int32_t *h_i32;
+  const double *h_ts;
+  const int64_t *off_i32, *off_ts, *off_prob;
+  const int32_t *b, *n_plan;
+  int64_t n_batches;
+} orca_epoch_t;
+int orca_tgn_eval_epoch(const orca_tgn_t *m, const orca_epoch_t *e, int32_t u_cap, void *d_workspace,
+                        int64_t workspace_bytes, void *d_stage, int64_t stage_bytes, float *d_prob, float *h_prob,
+                        int32_t *d_status, void *stream);
+
 /* Sharing the exchange buffer of the multi-GPU split between the processes of one node (no counterpart
  * in the reference).  orca_ipc_export: the 64-byte CUDA IPC handle of the allocation that holds d_ptr and
  * d_ptr's offset inside it; orca_ipc_open (in another process, on its own GPU): the address of the same

@@ -70,6 +70,11 @@ class TgnT(C.Structure):
     ]
 
 
+class EpochT(C.Structure):
+    _fields_ = [("h_i32", C.c_void_p), ("h_ts", C.c_void_p), ("off_i32", C.c_void_p), ("off_ts", C.c_void_p),
+                ("off_prob", C.c_void_p), ("b", C.c_void_p), ("n_plan", C.c_void_p), ("n_batches", C.c_int64)]
+
+
 # every symbol the header declares: name -> (restype, argtypes)
 _V, _I32, _I64 = C.c_void_p, C.c_int32, C.c_int64
 SYMBOLS = {
@@ -107,6 +112,7 @@ SYMBOLS = {
     "orca_tgn_eval_batch": (C.c_int, [C.POINTER(TgnT), _V, _V, _I32, _V, _I32, _I32, _V, _I64, _V, _V, _V, _V]),
     "orca_tgn_eval_batch_sharded": (C.c_int, [C.POINTER(TgnT), _I32, _V, _V, _I32, _V, _I32, _I32, _V, _I64, _V, _V,
                                               _V, _V, _V, _V]),
+    "orca_tgn_eval_epoch": (C.c_int, [C.POINTER(TgnT), C.POINTER(EpochT), _I32, _V, _I64, _V, _I64, _V, _V, _V, _V]),
     "orca_stage_h2d": (C.c_int, [_V, _V, C.c_int64, _V]),
     "orca_ipc_export": (C.c_int, [_V, _V, C.POINTER(C.c_int64)]),
     "orca_ipc_open": (C.c_int, [_V, C.c_int64, C.POINTER(C.c_void_p)]),

@@ -16,6 +16,8 @@ static int create_ctx(Ctx **out) {
   ORCA_CUDA(cudaStreamCreateWithFlags(&c->aux, cudaStreamNonBlocking));
   ORCA_CUDA(cudaStreamCreateWithFlags(&c->idx, cudaStreamNonBlocking));
   ORCA_CUDA(cudaStreamCreateWithFlags(&c->lane1, cudaStreamNonBlocking));
+  ORCA_CUDA(cudaStreamCreateWithFlags(&c->copy, cudaStreamNonBlocking));
+  for (int q = 0; q < Ctx::kStageSlots; ++q) ORCA_CUDA(cudaEventCreateWithFlags(&c->ev_slot[q], cudaEventDisableTiming));
   cudaEvent_t *evs[] = {&c->fork, &c->join, &c->ev_in, &c->ev_flags, &c->ev_o1, &c->ev_g2, &c->ev_state,
                         &c->ev_idx[0], &c->ev_idx[1], &c->ev_done[0], &c->ev_done[1]};
   for (cudaEvent_t *e : evs) ORCA_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
@@ -33,6 +35,9 @@ static void destroy_ctx(Ctx *c) {
   if (c->aux) cudaStreamSynchronize(c->aux);
   if (c->idx) cudaStreamSynchronize(c->idx);
   if (c->lane1) cudaStreamSynchronize(c->lane1);
+  if (c->copy) cudaStreamSynchronize(c->copy);
+  for (cudaEvent_t e : c->ev_slot)
+    if (e) cudaEventDestroy(e);
   cudaEvent_t evs[] = {c->fork, c->join, c->ev_in, c->ev_flags, c->ev_o1, c->ev_g2, c->ev_state, c->ev_idx[0],
                        c->ev_idx[1], c->ev_done[0], c->ev_done[1]};
   for (cudaEvent_t e : evs)
@@ -42,6 +47,7 @@ static void destroy_ctx(Ctx *c) {
   if (c->aux) cudaStreamDestroy(c->aux);
   if (c->idx) cudaStreamDestroy(c->idx);
   if (c->lane1) cudaStreamDestroy(c->lane1);
+  if (c->copy) cudaStreamDestroy(c->copy);
   if (c->d_words) cudaFree(c->d_words);
   if (prev >= 0) cudaSetDevice(prev);
   delete c;

@@ -45,7 +45,11 @@ struct Ctx {
   long long wait_limit = 2000000000ll;    // SM clocks a device-side wait may spin before it gives up
   int32_t *status_word = nullptr;         // where the projection kernels report a wait that gave up
   // streams and events of the batch pipeline (created with the context)
-  cudaStream_t aux = nullptr, idx = nullptr, lane1 = nullptr;
+  static constexpr int kStageSlots = 4;   // batches the staging ring of orca_tgn_eval_epoch holds
+  cudaStream_t aux = nullptr, idx = nullptr, lane1 = nullptr, copy = nullptr;
+  cudaEvent_t ev_slot[kStageSlots] = {nullptr, nullptr, nullptr, nullptr};
+  bool slot_used[kStageSlots] = {false, false, false, false};
+  long long stage_seq = 0;
   cudaEvent_t fork = nullptr, join = nullptr, ev_in = nullptr, ev_flags = nullptr;
   cudaEvent_t ev_o1 = nullptr, ev_g2 = nullptr, ev_state = nullptr;
   cudaEvent_t ev_idx[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr};

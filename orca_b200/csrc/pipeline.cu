@@ -326,6 +326,8 @@ static int eval_serial(const orca_tgn_t *m, Ctx *c, const int32_t *d_batch_i32, 
   int32_t *tk = c->d_words + CTX_TICKET_MAIN;
   int64_t *lp_push = m->last_pos, *lp_msg = m->last_pos + 2 * m->n_nodes;
   c->last_parity = 0;
+  // the batch arrays may have been made ready on another stream
+  if (m->input_stream != nullptr) ORCA_TRY(link((cudaStream_t)m->input_stream, s, c->ev_in));
 
   ORCA_TRY(tr.mark(-1, s));
   batch_prep_kernel<<<ceil_div(N, 256), 256, 0, s>>>(d_batch_i32, d_batch_ts, b, x.nodes1, x.ts1, x.cat_dst, x.n1);
@@ -761,6 +763,59 @@ int orca_tgn_eval_batch_sharded(const orca_tgn_t *m, int32_t phase, const int32_
   c->status_word = saved_status;
   if (phase != 1) c->last_batch_launches = launch_counter();
   return rc;
+}
+
+int orca_tgn_eval_epoch(const orca_tgn_t *m, const orca_epoch_t *e, int32_t u_cap, void *d_workspace,
+                        int64_t workspace_bytes, void *d_stage, int64_t stage_bytes, float *d_prob, float *h_prob,
+                        int32_t *d_status, void *stream) {
+  ORCA_CHECK_ARG(m && e && d_workspace && d_stage && d_prob && d_status);
+  ORCA_CHECK_ARG(e->n_batches >= 0 && (e->n_batches == 0 || (e->h_i32 && e->h_ts && e->off_i32 && e->off_ts && e->b &&
+                                                             e->n_plan && e->off_prob)));
+  Ctx *c = ctx_of(m);
+  if (c == nullptr) return set_error(ORCA_E_CUDA, "orca_tgn_eval_epoch: no context for the current device");
+  const bool sharded = m->world > 1;
+  if (sharded && m->peer_rows[m->rank] == nullptr)
+    return set_error(ORCA_E_UNSUPPORTED, "orca_tgn_eval_epoch: the multi-GPU split needs the direct exchange");
+  cudaStream_t s = (cudaStream_t)stream;
+  constexpr int kSlots = Ctx::kStageSlots;
+  const int64_t slot_bytes = (stage_bytes / kSlots) & ~(int64_t)255;
+  orca_tgn_t mm = *m;
+  mm.input_stream = c->copy;
+  for (int64_t i = 0; i < e->n_batches; ++i) {
+    const int b = e->b[i], n_plan = e->n_plan[i];
+    ORCA_CHECK_ARG(b > 0);
+    const int64_t bytes_i32 = ((int64_t)4 * b + (n_plan > 0 ? n_plan : 0)) * 4;
+    const int64_t off_ts = (bytes_i32 + 15) & ~(int64_t)15;
+    if (off_ts + 8ll * b > slot_bytes)
+      return set_error(ORCA_E_CAPACITY, "orca_tgn_eval_epoch: staging slot of %lld bytes, batch %lld needs %lld",
+                       (long long)slot_bytes, (long long)i, (long long)(off_ts + 8ll * b));
+    const int slot = (int)(c->stage_seq++ % kSlots);   // (the ring carries over from call to call)
+    char *d_slot = (char *)d_stage + slot * slot_bytes;
+    // the copy of batch i runs on the copy stream, ahead of the kernels of the batches before it; a slot is
+    // refilled once the batch that read it has completed
+    if (c->slot_used[slot]) ORCA_CUDA(cudaStreamWaitEvent(c->copy, c->ev_slot[slot], 0));
+    ORCA_CUDA(cudaMemcpyAsync(d_slot, e->h_i32 + e->off_i32[i], (size_t)bytes_i32, cudaMemcpyHostToDevice, c->copy));
+    ORCA_CUDA(cudaMemcpyAsync(d_slot + off_ts, e->h_ts + e->off_ts[i], (size_t)8 * b, cudaMemcpyHostToDevice, c->copy));
+    const int32_t *d_i32 = reinterpret_cast<const int32_t *>(d_slot);
+    const double *d_ts = reinterpret_cast<const double *>(d_slot + off_ts);
+    const int32_t *d_plan = n_plan >= 0 ? d_i32 + 4 * (size_t)b : nullptr;
+    float *prob = d_prob + e->off_prob[i];
+    int n_scores;
+    if (sharded) {
+      ORCA_TRY(orca_tgn_eval_batch_sharded(&mm, 0, d_i32, d_ts, b, d_plan, n_plan > 0 ? n_plan : 0, u_cap, d_workspace,
+                                           workspace_bytes, nullptr, nullptr, prob, nullptr, d_status, stream));
+      n_scores = 2 * ((b - m->rank + m->world - 1) / m->world);
+    } else {
+      ORCA_TRY(orca_tgn_eval_batch(&mm, d_i32, d_ts, b, d_plan, n_plan > 0 ? n_plan : 0, u_cap, d_workspace,
+                                   workspace_bytes, prob, nullptr, d_status, stream));
+      n_scores = 2 * b;
+    }
+    if (h_prob != nullptr && n_scores > 0)
+      ORCA_CUDA(cudaMemcpyAsync(h_prob + e->off_prob[i], prob, (size_t)n_scores * 4, cudaMemcpyDeviceToHost, s));
+    ORCA_CUDA(cudaEventRecord(c->ev_slot[slot], s));
+    c->slot_used[slot] = true;
+  }
+  return ORCA_OK;
 }
 
 int orca_ipc_export(const void *d_ptr, void *h_handle, int64_t *h_offset) {

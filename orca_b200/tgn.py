@@ -575,6 +575,128 @@ class TGN(nn.Module):
                                    n_neighbors, cache_plan, want_emb=False)
         return prob[:b].unsqueeze(1), prob[b:].unsqueeze(1)
 
+    # ---- a whole stream of batches in one library call (the loop of evaluation/evaluation.py:18-37)
+    @torch.no_grad()
+    def eval_epoch(self, sources, destinations, negatives, timestamps, edge_idxs, n_neighbors, batch_size,
+                   cache_plan=None, reuse=True):
+        """Scores every batch of the stream (edges [i*batch_size, (i+1)*batch_size)) exactly as one
+        compute_edge_probabilities call per batch would, without a Python call or a host round trip per
+        batch: the batches are packed into pinned host memory, and the library copies each batch to the
+        device, runs it and copies its scores back, batch after batch, asynchronously.
+        cache_plan: list with one id array per batch (or None: the plan-less flag rule).
+        Returns (pos, neg): float32 numpy arrays with one score per edge."""
+        L = _lib.lib()
+        E = len(sources)
+        bs, k = int(batch_size), int(n_neighbors)
+        nb = (E + bs - 1) // bs
+        if nb == 0:
+            return np.zeros(0, np.float32), np.zeros(0, np.float32)
+        self._enter(reuse, False)
+        self.batch_counter += nb - 1
+        if self._mode != MODE_BUDGET:
+            cache_plan = None
+        world, rank = self._world, self._rank
+        if world > 1 and getattr(self, "_exchange", None) is None:
+            raise NotImplementedError("eval_epoch on several GPUs needs the direct exchange (set_distributed)")
+        b = np.full(nb, bs, dtype=np.int32)
+        b[-1] = E - (nb - 1) * bs
+        n_plan = np.full(nb, -1, dtype=np.int32)
+        if cache_plan is not None:
+            n_plan[:] = [len(cache_plan[i]) for i in range(nb)]
+        ints = 4 * b.astype(np.int64) + np.maximum(n_plan, 0)
+        off_i32 = np.zeros(nb, dtype=np.int64)
+        np.cumsum(ints[:-1], out=off_i32[1:])
+        off_ts = np.arange(nb, dtype=np.int64) * bs
+        b_loc = (b.astype(np.int64) - rank + world - 1) // world if world > 1 else b.astype(np.int64)
+        off_prob = np.zeros(nb, dtype=np.int64)
+        np.cumsum(2 * b_loc[:-1], out=off_prob[1:])
+        n_scores = int(2 * b_loc.sum())
+        # pinned host images of the stream (kept and grown: pinning is slow)
+        pin = self.__dict__.setdefault("_epoch_pin", {})
+
+        def pinned(name, n, dtype):
+            t = pin.get(name)
+            if t is None or t.numel() < n or t.dtype != dtype:
+                t = torch.empty(max(n, 1), dtype=dtype, pin_memory=True)
+                pin[name] = t
+            return t
+
+        n_ints = int(ints.sum())
+        h_i32 = pinned("i32", n_ints, torch.int32)
+        h_ts = pinned("ts", E, torch.float64)
+        h_prob = pinned("prob", n_scores, torch.float32)
+        hi = h_i32.numpy()
+        h_ts.numpy()[:E] = timestamps
+        if self.n_layers == 2 and cache_plan is not None:
+            h = self.embedding_module.histories[0]
+            most = int(n_plan.max())
+            if most > h.prev_plan.numel():
+                h.prev_plan = torch.zeros(most, dtype=torch.int32, device=self.device)
+                h.n_prev[0] = -1
+        slot = (24 * bs + 4 * int(max(n_plan.max(), 0)) + 16 + 255) // 256 * 256
+        dev = self.__dict__.setdefault("_epoch_dev", {})
+        if dev.get("stage") is None or dev["stage"].numel() < 4 * slot:
+            torch.cuda.synchronize(self.device)
+            dev["stage"] = torch.empty(4 * slot, dtype=torch.uint8, device=self.device)
+        if dev.get("prob") is None or dev["prob"].numel() < n_scores:
+            torch.cuda.synchronize(self.device)
+            dev["prob"] = torch.empty(max(n_scores, 1), dtype=torch.float32, device=self.device)
+        ws, u_cap = self._workspace(bs, k)
+        desc = self._descriptor(k)
+        stream = torch.cuda.current_stream(self.device)
+        # The stream goes to the library in chunks of a few batches: while the GPU works on one chunk the next
+        # one is packed into its own part of the pinned image (the library never waits for the host).
+        chunk = 8
+        for i0 in range(0, nb, chunk):
+            i1 = min(nb, i0 + chunk)
+            if int(b[-1]) == bs and cache_plan is None:
+                lo, up = i0 * bs, i1 * bs
+                v = hi[int(off_i32[i0]):int(off_i32[i0]) + 4 * (up - lo)].reshape(i1 - i0, 4, bs)
+                v[:, 0], v[:, 1], v[:, 2], v[:, 3] = (np.asarray(a[lo:up]).reshape(i1 - i0, bs) for a in
+                                                       (sources, destinations, negatives, edge_idxs))
+            else:
+                for i in range(i0, i1):
+                    o, n, lo = int(off_i32[i]), int(b[i]), i * bs
+                    hi[o:o + n] = sources[lo:lo + n]
+                    hi[o + n:o + 2 * n] = destinations[lo:lo + n]
+                    hi[o + 2 * n:o + 3 * n] = negatives[lo:lo + n]
+                    hi[o + 3 * n:o + 4 * n] = edge_idxs[lo:lo + n]
+                    if n_plan[i] > 0:
+                        hi[o + 4 * n:o + 4 * n + n_plan[i]] = cache_plan[i]
+            ep = _lib.EpochT(h_i32.data_ptr(), h_ts.data_ptr(), off_i32[i0:].ctypes.data, off_ts[i0:].ctypes.data,
+                             off_prob[i0:].ctypes.data, b[i0:].ctypes.data, n_plan[i0:].ctypes.data, i1 - i0)
+            _lib.check(L.orca_tgn_eval_epoch(desc, C.byref(ep), u_cap, ws.data_ptr(), ws.numel(),
+                                             dev["stage"].data_ptr(), dev["stage"].numel(), dev["prob"].data_ptr(),
+                                             h_prob.data_ptr(), self._status.data_ptr(), stream.cuda_stream))
+        stream.synchronize()
+        local = h_prob.numpy()[:n_scores]
+        pos = np.empty(E, dtype=np.float32)
+        neg = np.empty(E, dtype=np.float32)
+        if world == 1:
+            if int(b[-1]) == bs:
+                v = local.reshape(nb, 2, bs)
+                pos[:], neg[:] = v[:, 0].reshape(-1), v[:, 1].reshape(-1)
+            else:
+                for i in range(nb):
+                    o, n, lo = int(off_prob[i]), int(b[i]), i * bs
+                    pos[lo:lo + n], neg[lo:lo + n] = local[o:o + n], local[o + n:o + 2 * n]
+            return pos, neg
+        # every rank holds the scores of its edges (edge e of a batch: rank e % world): one exchange per epoch
+        import torch.distributed as dist
+        most = 2 * int(((b.astype(np.int64) + world - 1) // world).sum())
+        mine = torch.zeros(most, dtype=torch.float32, device=self.device)
+        mine[:n_scores] = dev["prob"][:n_scores]
+        every = shard.all_gather_rows(mine, self._group).cpu().numpy()
+        for r in range(world):
+            bl = (b.astype(np.int64) - r + world - 1) // world
+            o = 0
+            for i in range(nb):
+                n, lo = int(bl[i]), i * bs
+                pos[lo + r:lo + int(b[i]):world] = every[r, o:o + n]
+                neg[lo + r:lo + int(b[i]):world] = every[r, o + n:o + 2 * n]
+                o += 2 * n
+        return pos, neg
+
     def update_memory(self, memory, positives):
         self.memory_updater.update_memory(memory, positives)
 

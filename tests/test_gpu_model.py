@@ -266,6 +266,61 @@ def test_batches_of_changing_size_share_a_model():
     assert torch.equal(tgn.embedding_module.histories[0].emb, ref.embedding_module.histories[0].emb)
 
 
+@pytest.mark.parametrize("case", ["t_nb2", "t_lru"])
+def test_eval_epoch_equals_per_batch_calls(case):
+    """One library call for the whole stream (TGN.eval_epoch) gives the bits of one
+    compute_edge_probabilities call per batch: scores and every state table; the stream's last batch is
+    short, a few batches run without a plan."""
+    gold = golden(case)
+    g = graph(str(gold["spec"]))
+    spec = g.spec
+    plan = unpack(gold[f"plan_{spec.strategy}_flat"], gold[f"plan_{spec.strategy}_off"])
+    neg = gold["neg"]
+    E = (len(plan) - 1) * spec.bs - 37           # a short last batch
+    nb = -(-E // spec.bs)
+    a, b = make_model(g), make_model(g)
+    pos, ngs = [], []
+    for i in range(nb):
+        sl = slice(i * spec.bs, min(E, (i + 1) * spec.bs))
+        p, q = a.compute_edge_probabilities(g.sources[sl], g.destinations[sl], neg[sl], g.timestamps[sl],
+                                            g.edge_idxs[sl], spec.n_degree, True, False, plan[i])
+        pos.append(p.cpu().numpy().ravel()), ngs.append(q.cpu().numpy().ravel())
+    a.check_status()
+    p2, q2 = b.eval_epoch(g.sources[:E], g.destinations[:E], neg[:E], g.timestamps[:E], g.edge_idxs[:E],
+                          spec.n_degree, spec.bs, plan[:nb])
+    b.check_status()
+    assert np.array_equal(np.concatenate(pos), p2) and np.array_equal(np.concatenate(ngs), q2)
+    assert torch.equal(a.memory.memory, b.memory.memory) and torch.equal(a.memory.messages, b.memory.messages)
+    assert torch.equal(a.embedding_module.histories[0].emb, b.embedding_module.histories[0].emb)
+    assert torch.equal(a.embedding_module.histories[0].cache_flag_dev, b.embedding_module.histories[0].cache_flag_dev)
+    # a second epoch on the same model (staging ring and pinned buffers reused), without plans
+    p3, _ = b.eval_epoch(g.sources[:E], g.destinations[:E], neg[:E], g.timestamps[:E], g.edge_idxs[:E],
+                         spec.n_degree, spec.bs, None)
+    b.check_status()
+    assert p3.shape == (E,) and np.all((p3 > 0) & (p3 < 1))
+
+
+def test_eval_edge_prediction_reproduces_reference_ap():
+    """The reference's evaluation entry point (evaluation/evaluation.py:6-47) on the whole c1 stream: the
+    mean average precision of the fixture the reference produced, to 3 decimals."""
+    import types
+    from orca_b200.evaluation import RandEdgeSampler, eval_edge_prediction
+    gold = golden("c1")
+    g = graph(str(gold["spec"]))
+    spec = g.spec
+    plan = unpack(gold[f"plan_{spec.strategy}_flat"], gold[f"plan_{spec.strategy}_off"])
+    nb = gold["scores"].shape[0]
+    n = min(g.n_edges, nb * spec.bs)
+    data = types.SimpleNamespace(sources=g.sources, destinations=g.destinations, timestamps=g.timestamps,
+                                 edge_idxs=g.edge_idxs, n_interactions=n)
+    sampler = RandEdgeSampler(g.sources, g.destinations, seed=0)
+    tgn = make_model(g)
+    ap, auc, acc = eval_edge_prediction(tgn, sampler, data, spec.n_degree, spec.bs, True, plan)
+    tgn.check_status()
+    assert round(float(ap), 3) == round(float(gold["ap"]), 3)
+    assert 0.0 <= auc <= 1.0 and 0.0 <= acc <= 1.0
+
+
 def test_unsupported_modes_fail_loudly():
     g = graph("t_nb2")
     tgn = make_model(g)
