@@ -39,6 +39,9 @@ extern "C" {
 #define ORCA_HEADS 2
 #define ORCA_MAX_K 32
 #define ORCA_MAX_WORLD 8   /* GPUs of one node */
+#define ORCA_FLAG_WORDS 32    /* flag words of one rank's exchange buffer: [0,8) layer-1 rows posted by rank q, [8]
+                                 check-out counter of the layer-1 kernel, [16,24) memory rows posted by rank q,
+                                 [24] check-out counter of the memory-update kernel */
 #define ORCA_EXCHANGE_SLOTS 4 /* batches whose layer-1 rows an exchange buffer holds: with the lanes of the
                                  batch pipeline a rank's layer 1 may be two batches ahead of a peer's layer 2 */
 #define ORCA_CAND_CAP 2048 /* listed candidates of the uncached set; more fall back to a bitmap scan */
@@ -381,11 +384,17 @@ typedef struct {
   /* Direct exchange of the layer-1 rows between the GPUs of one node (orca_tgn_eval_batch_sharded; all
    * NULL / 0: the caller all-gathers).  peer_rows[r] / peer_flags[r]: rank r's exchange buffer
    * (ORCA_EXCHANGE_SLOTS slots of exchange_cap floats, used in turn) and flag words
-   * (int32[ORCA_MAX_WORLD + 1], zero-initialised) as mapped into THIS process (own rank included, peers
+   * (int32[ORCA_FLAG_WORDS], zero-initialised) as mapped into THIS process (own rank included, peers
    * through CUDA IPC). */
   float *peer_rows[ORCA_MAX_WORLD];
-  int32_t *peer_flags[ORCA_MAX_WORLD];
+  int32_t *peer_flags[ORCA_MAX_WORLD];   /* int32[ORCA_FLAG_WORDS] per rank */
   int64_t exchange_cap;
+  /* The same for the memory update, which is split by node: of the batch's unique positive nodes (in list
+   * order) rank r computes every world-th from r and stores the new memory rows into every rank's buffer
+   * peer_gru[q] (2 halves of gru_cap floats, used alternately; gru_cap >= 2 * b * 172); all ranks then write
+   * all rows into their replica of the memory table.  All NULL: every rank computes every row. */
+  float *peer_gru[ORCA_MAX_WORLD];
+  int64_t gru_cap;
   int64_t *exchange_seq;    /* host-resident batch sequence counter owned by the caller (starts at 0) */
   orca_ctx_t *ctx;          /* context of this model; NULL = default context of the current device   */
   void *input_stream;       /* cudaStream_t on which the batch arrays (and the plan) of a call were made */

@@ -19,6 +19,7 @@ QT_LD = 1056
 MSG_DIM = 688
 CAND_CAP = 2048   # ORCA_CAND_CAP
 EXCHANGE_SLOTS = 4  # ORCA_EXCHANGE_SLOTS
+FLAG_WORDS = 32     # ORCA_FLAG_WORDS
 # options of orca_ctx_set
 OPT_PROJECTION_MODE, OPT_OVERLAP, OPT_DEPENDENT_LAUNCH, OPT_LOOKAHEAD, OPT_WAIT_LIMIT, OPT_TRACE = range(6)
 
@@ -64,6 +65,8 @@ class TgnT(C.Structure):
         ("peer_rows", C.c_void_p * 8),
         ("peer_flags", C.c_void_p * 8),
         ("exchange_cap", C.c_int64),
+        ("peer_gru", C.c_void_p * 8),
+        ("gru_cap", C.c_int64),
         ("exchange_seq", C.POINTER(C.c_int64)),
         ("ctx", C.c_void_p),
         ("input_stream", C.c_void_p),

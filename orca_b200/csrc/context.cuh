@@ -56,7 +56,8 @@ struct Ctx {
   bool done_recorded[2] = {false, false}, state_recorded = false, g2_recorded = false;
   long long seq = 0;                      // budgeted two-layer batches enqueued through this context
   int parity = 0;                         // buffer parity of the batch being enqueued (kept between the
-  long long base1 = 0, base_msg = 0;      // two phases of a sharded batch, like its record bases)
+  long long base1 = 0, base_msg = 0;      // two phases of a sharded batch, like its record bases
+  long long xseq = 0;                     // and its sequence number in the ranks' flag words)
   int last_parity = 0;
   int layout_b = 0, layout_u = 0, layout_k = 0;   // workspace layout of the last budgeted batch
   const void *layout_ws = nullptr;

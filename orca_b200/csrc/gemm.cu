@@ -359,9 +359,11 @@ __global__ void __launch_bounds__(F2_THREADS) score_kernel(ScoreArgs g) {
 // without a pending message is left alone)
 __global__ void gru_scatter_kernel(const float *__restrict__ hnew, orca_memory_t mem,
                                    const int32_t *__restrict__ nodes, int n_cap, const int32_t *d_n,
-                                   int clear_flags) {
+                                   int clear_flags, const int32_t *__restrict__ status) {
   dep_trigger();
   dep_wait();
+  // (multi-GPU: rows that the peers did not deliver in time must not reach the memory table)
+  if (status != nullptr && *status != 0) return;
   const int n = rows_of(n_cap, d_n);
   const int row = blockIdx.x * (blockDim.x / 64) + threadIdx.x / 64;
   const int t = threadIdx.x % 64;
@@ -562,7 +564,7 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
 namespace orca {
 
 int gru_project(const orca_gru_weights_t *w, const orca_memory_t *mem, const int32_t *d_nodes, int32_t n_cap,
-                const int32_t *d_n, float *d_scratch_h, cudaStream_t s) {
+                const int32_t *d_n, float *d_scratch_h, cudaStream_t s, const tc::PeerOut *peer) {
   ORCA_CHECK_ARG(w && w->Wg && w->bg && mem && mem->memory && mem->last_update && mem->messages &&
                  mem->msg_ts && mem->msg_flag && d_nodes && d_scratch_h && n_cap >= 0);
   if (n_cap == 0) return ORCA_OK;
@@ -580,8 +582,15 @@ int gru_project(const orca_gru_weights_t *w, const orca_memory_t *mem, const int
     a.out = d_scratch_h;
     a.memory = mem->memory;
     a.nodes = d_nodes;
+    if (peer != nullptr) {
+      // one rank of the multi-GPU split: every world-th listed node from `rank`, rows delivered to all ranks
+      a.peer = *peer;
+      a.row_stride = peer->world, a.row_off = peer->rank, a.idx_limit = n_cap;
+      a.m_cap = ceil_div(n_cap, peer->world);
+    }
     return tc::launch(tc::EPI_GRU, a, 4, s);
   }
+  if (peer != nullptr) return set_error(ORCA_E_UNSUPPORTED, "gru_project: the node split needs the tensor-core path");
   F1Args g{};
   g.a0 = RowSrc{mem->messages, d_nodes, MSG, 0, 0};
   g.a1 = RowSrc{mem->memory, d_nodes, D, 0, 0};
@@ -602,12 +611,12 @@ int gru_project(const orca_gru_weights_t *w, const orca_memory_t *mem, const int
 }
 
 int gru_scatter(const orca_memory_t *mem, const int32_t *d_nodes, int32_t n_cap, const int32_t *d_n,
-                int32_t clear_flags, const float *d_scratch_h, cudaStream_t s) {
+                int32_t clear_flags, const float *d_scratch_h, cudaStream_t s, const int32_t *d_skip_if_set) {
   ORCA_CHECK_ARG(mem && mem->memory && mem->last_update && mem->msg_ts && mem->msg_flag && d_nodes && d_scratch_h &&
                  n_cap >= 0);
   if (n_cap == 0) return ORCA_OK;
   ORCA_CUDA(launch_dep(gru_scatter_kernel, ceil_div(n_cap, 4), 256, 0, s, d_scratch_h, *mem, d_nodes, n_cap, d_n,
-                       (int)clear_flags));
+                       (int)clear_flags, d_skip_if_set));
   ORCA_COUNT_LAUNCH();
   ORCA_LAUNCH_CHECK();
   return ORCA_OK;

@@ -453,7 +453,12 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
                        (long long)m->exchange_cap, (long long)world * rpr * D);
   }
 
+  const bool gru_split = direct && m->peer_gru[rank] != nullptr && projections_on_tensor_cores();
+  if (gru_split && (int64_t)2 * b * D > m->gru_cap)
+    return set_error(ORCA_E_CAPACITY, "orca_tgn_eval_batch_sharded: memory-row buffer of %lld floats, %lld needed",
+                     (long long)m->gru_cap, (long long)2 * b * D);
   if (phases & 1) {
+    if (direct) c->xseq = ++*m->exchange_seq;   // sequence number of this batch in the ranks' flag words
     c->parity = (int)(c->seq++ & 1);
     c->base1 = *m->epoch_base;
     *m->epoch_base += R1;
@@ -552,7 +557,22 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
     ORCA_TRY(orca_message_store(&m->mem, m->edge_table, m->time_w, d_batch_i32, x.cat_dst, d_batch_ts,
                                 d_batch_i32 + 3 * b, b, x.win_pos, 2 * b, x.n_win, x.win_nodes, sx));
     ORCA_TRY(tr.mark(PH_MESSAGE, s));
-    ORCA_TRY(gru_project(&m->gru, &m->mem, x.win_nodes, 2 * b, x.n_win, w.gru_h, sx));
+    if (gru_split) {
+      // the memory update is split by node: this rank computes every world-th unique positive and stores the
+      // new rows into every rank's buffer; the scatter (phase 2) waits for all ranks' rows
+      tc::PeerOut po{};
+      for (int q = 0; q < world; ++q) {
+        ORCA_CHECK_ARG(m->peer_gru[q] != nullptr && m->peer_flags[q] != nullptr);
+        po.rows[q] = m->peer_gru[q];
+        po.flags[q] = m->peer_flags[q] + 16;
+      }
+      po.counter = m->peer_flags[rank] + 24;
+      po.off = (c->xseq & 1) * m->gru_cap;
+      po.world = world, po.rank = rank, po.seq = (int)c->xseq;
+      ORCA_TRY(gru_project(&m->gru, &m->mem, x.win_nodes, 2 * b, x.n_win, w.gru_h, sx, &po));
+    } else {
+      ORCA_TRY(gru_project(&m->gru, &m->mem, x.win_nodes, 2 * b, x.n_win, w.gru_h, sx));
+    }
     ORCA_TRY(tr.mark(PH_GRU, s));
 
     // ------------------------------------------------------------------ layer-1 lane
@@ -575,7 +595,7 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
                                 x.nodes1, w.win1, lp_push, base1, N, l1.hidden, N, sa));
     } else if (direct && projections_on_tensor_cores()) {
       // the LayerNorm epilogue of layer 1 delivers the rows itself: one kernel computes and exchanges
-      const long long seq = ++*m->exchange_seq;
+      const long long seq = c->xseq;
       tc::PeerOut po{};
       for (int q = 0; q < world; ++q) {
         ORCA_CHECK_ARG(m->peer_rows[q] != nullptr && m->peer_flags[q] != nullptr);
@@ -592,7 +612,7 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
                                 nullptr, nullptr, nullptr, l1.hidden, sa));
       if (direct) {
         // (fp32 debug projections: a separate kernel fans the rows out)
-        const long long seq = ++*m->exchange_seq;
+        const long long seq = c->xseq;
         Peers pr{};
         for (int q = 0; q < world; ++q) {
           ORCA_CHECK_ARG(m->peer_rows[q] != nullptr && m->peer_flags[q] != nullptr);
@@ -609,16 +629,31 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
     if (sa != s || sx != s) ORCA_CUDA(cudaEventRecord(c->ev_o1, sa));
 
     // ------------------------------------------------------------------ side lane: the memory table is written
-    ORCA_TRY(wait_on(sx, sa, c->ev_o1));
-    ORCA_TRY(gru_scatter(&m->mem, x.win_nodes, 2 * b, x.n_win, 1, w.gru_h, sx));
-    if (sx != s) {
-      ORCA_CUDA(cudaEventRecord(c->ev_state, sx));
-      c->state_recorded = true;
+    if (!gru_split) {
+      ORCA_TRY(wait_on(sx, sa, c->ev_o1));
+      ORCA_TRY(gru_scatter(&m->mem, x.win_nodes, 2 * b, x.n_win, 1, w.gru_h, sx));
+      if (sx != s) {
+        ORCA_CUDA(cudaEventRecord(c->ev_state, sx));
+        c->state_recorded = true;
+      }
     }
     // the caller's stream carries on after layer 1 (the caller may exchange the rows between the phases)
     ORCA_TRY(wait_on(s, sa, c->ev_o1));
   }
 
+  if ((phases & 2) && gru_split) {
+    // ------------------------------------------------------------------ side lane: all ranks' memory rows
+    ORCA_TRY(wait_on(sx, sa, c->ev_o1));
+    ORCA_CUDA(launch_dep(exchange_wait_kernel, 1, 32, 0, sx, (const int32_t *)(m->peer_flags[rank] + 16), world,
+                         (int)c->xseq, d_status, c->wait_limit));
+    ORCA_COUNT_LAUNCH();
+    ORCA_TRY(gru_scatter(&m->mem, x.win_nodes, 2 * b, x.n_win, 1, m->peer_gru[rank] + (c->xseq & 1) * m->gru_cap, sx,
+                         d_status));
+    if (sx != s) {
+      ORCA_CUDA(cudaEventRecord(c->ev_state, sx));
+      c->state_recorded = true;
+    }
+  }
   if (phases & 2) {
     // ------------------------------------------------------------------ caller's stream: layer 2 and the scores
     const float *feat2 = emb1;
@@ -628,7 +663,7 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
     int rows2 = N, b2 = b;
     if (sharded) {
       if (direct) {
-        const long long seq = *m->exchange_seq;
+        const long long seq = c->xseq;
         ORCA_CUDA(launch_dep(exchange_wait_kernel, 1, 32, 0, s, (const int32_t *)m->peer_flags[rank], world, (int)seq,
                              d_status, c->wait_limit));
         ORCA_COUNT_LAUNCH();

@@ -313,13 +313,19 @@ __device__ __forceinline__ void tile_output(const Args &g, const float *tile, co
 #pragma unroll
       for (int k = 0; k < RB; ++k)
         if (ok[k]) {
+          // (row of the whole list; with the multi-GPU split the row also goes to every rank's buffer)
+          const size_t orow = (size_t)(g.row_stride > 1 ? m[k] * g.row_stride + g.row_off : m[k]) * D;
           if (uA < D) {
             const float rg = 1.f / (1.f + expf(-a[k].x)), z = 1.f / (1.f + expf(-a[k].y));
-            g.out[(size_t)m[k] * D + uA] = (1.f - z) * tanhf(a[k].z + rg * a[k].w) + z * hA[k];
+            const float h = (1.f - z) * tanhf(a[k].z + rg * a[k].w) + z * hA[k];
+            if (g.peer.world == 0) g.out[orow + uA] = h;
+            for (int q = 0; q < g.peer.world; ++q) g.peer.rows[q][g.peer.off + orow + uA] = h;
           }
           if (has1 && uB < D) {
             const float rg = 1.f / (1.f + expf(-b[k].x)), z = 1.f / (1.f + expf(-b[k].y));
-            g.out[(size_t)m[k] * D + uB] = (1.f - z) * tanhf(b[k].z + rg * b[k].w) + z * hB[k];
+            const float h = (1.f - z) * tanhf(b[k].z + rg * b[k].w) + z * hB[k];
+            if (g.peer.world == 0) g.out[orow + uB] = h;
+            for (int q = 0; q < g.peer.world; ++q) g.peer.rows[q][g.peer.off + orow + uB] = h;
           }
         }
     }
@@ -336,6 +342,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   const int pw = grp ? warp - 6 : warp;   // producer warp within its group: tile rows pw*32 .. pw*32+31
   const int rsub = lane >> 3, f = lane & 7;
   const int w0 = g.a0.width, w1 = g.a1.width, Kd = g.Kd;
+  const int rstride = g.row_stride > 1 ? g.row_stride : 1;
   const int nkb = g.n_kblocks;
 
   dep_trigger();
@@ -352,8 +359,10 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     if (producer) {
       const int m = m0 + pw * 32 + lane;
       if (m < limit) {
-        ri0 = g.a0.idx ? g.a0.idx[m] : (g.a0.mod > 0 ? m % g.a0.mod : m) + g.a0.add;
-        if (w1) ri1 = g.a1.idx ? g.a1.idx[m] : (g.a1.mod > 0 ? m % g.a1.mod : m) + g.a1.add;
+        // (row_stride > 1: this launch covers every row_stride-th row of the index lists, from row_off)
+        const int mi = rstride > 1 ? min(m * rstride + g.row_off, g.idx_limit - 1) : m;
+        ri0 = g.a0.idx ? g.a0.idx[mi] : (g.a0.mod > 0 ? m % g.a0.mod : m) + g.a0.add;
+        if (w1) ri1 = g.a1.idx ? g.a1.idx[mi] : (g.a1.mod > 0 ? m % g.a1.mod : m) + g.a1.add;
         // an invalid row reads zeros for its first zero_cols columns: with zero_cols == a0.width (the
         // only use) that is the whole first source
         if (g.row_valid != nullptr && g.zero_cols > 0 && g.row_valid[m] == 0) ri0 = -1;
@@ -367,7 +376,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
         meta_b = g.push_ids[m];
         if (g.push_win != nullptr) meta_a = g.push_win[m];
       }
-      if (EPI == EPI_GRU) meta_b = g.nodes[m];
+      if (EPI == EPI_GRU) meta_b = g.nodes[rstride > 1 ? min(m * rstride + g.row_off, g.idx_limit - 1) : m];
     }
   };
 
@@ -447,6 +456,10 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   dep_wait();
   prefetch_rows(blockIdx.y * BM, g.m_cap);
   M = rows_of(g.m_cap, g.d_m);
+  if (rstride > 1) {   // d_m counts the rows of the whole list: this launch's share of them
+    const int all = g.d_m != nullptr ? *g.d_m : g.idx_limit;
+    M = min(g.m_cap, all > g.row_off ? (all - g.row_off + rstride - 1) / rstride : 0);
+  }
   fix_rows(blockIdx.y * BM);
   if ((int)blockIdx.y * BM < M && producer && grp < nkb) load_stage(grp);   // in flight across the barrier
   push_winners(blockIdx.y * BM);
@@ -580,7 +593,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
   }
-  if (EPI == EPI_LAYERNORM && g.peer.world > 0) {
+  if ((EPI == EPI_LAYERNORM || EPI == EPI_GRU) && g.peer.world > 0) {
     // every CTA (with or without rows) checks out; the last one posts the batch's sequence number to all
     // ranks, after every CTA's peer stores have been fenced system-wide
     __threadfence_system();

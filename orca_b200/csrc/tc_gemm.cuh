@@ -34,7 +34,7 @@ struct RowSrc {
   int add;
 };
 
-// LAYERNORM epilogue that also delivers the rows to the other GPUs of the node (the exchange of the
+// LAYERNORM / GRU epilogue that also delivers the rows to the other GPUs of the node (the exchange of the
 // multi-GPU split): row m goes to rows[q] + off + m * 172 floats for every rank q (peer stores over
 // NVLink; the own buffer is one of them), and the last CTA to finish posts `seq` in word `rank` of every
 // rank's flag array.  counter: a zeroed word of the own flag array.
@@ -57,6 +57,9 @@ struct Args {
   int n_kblocks;
   int m_cap;
   const int32_t *d_m;
+  // optional row map: tile row m stands for entry m * row_stride + row_off of the index lists (a0.idx,
+  // a1.idx, nodes; idx_limit entries) and d_m counts the entries of the whole lists; row_stride <= 1: off
+  int row_stride, row_off, idx_limit;
   const float *bias;         // [n_tiles * BN]
   float *out;                // BIAS: [m, out_ld]; HIDDEN / LAYERNORM: [m, 172]; GRU: [m, 172]; SCORE: [m]
   int out_ld;

@@ -251,11 +251,14 @@ class TGN(nn.Module):
         if self._world > 1 and exchange == "direct":
             import torch.distributed as dist
             cap = self.exchange_floats(int(self.args.bs), self._world, int(self.args.n_degree), self.n_nodes)
-            # one allocation per rank: EXCHANGE_SLOTS * cap floats of rows, then 16 flag words
-            xbuf = torch.zeros(_lib.EXCHANGE_SLOTS * cap + 16, dtype=torch.float32, device=self.device)
+            gcap = 2 * int(self.args.bs) * _lib.DIM
+            # one allocation per rank: EXCHANGE_SLOTS * cap floats of layer-1 rows, 2 * gcap floats of memory
+            # rows, then the flag words
+            xbuf = torch.zeros(_lib.EXCHANGE_SLOTS * cap + 2 * gcap + _lib.FLAG_WORDS, dtype=torch.float32,
+                               device=self.device)
             torch.cuda.synchronize(self.device)
             L = _lib.lib()
-            rows, flags, keep, err = [], [], [xbuf], None
+            rows, flags, grus, keep, err = [], [], [], [xbuf], None
             try:
                 handle = (C.c_ubyte * 64)()
                 off = C.c_int64(0)
@@ -276,7 +279,8 @@ class TGN(nn.Module):
                             _lib.check(L.orca_ipc_open(h, handles[r][1], C.byref(out)))
                             base = out.value
                         rows.append(base)
-                        flags.append(base + 4 * _lib.EXCHANGE_SLOTS * cap)      # byte offset of the flag words
+                        grus.append(base + 4 * _lib.EXCHANGE_SLOTS * cap)
+                        flags.append(base + 4 * (_lib.EXCHANGE_SLOTS * cap + 2 * gcap))
                 except _lib.OrcaError as e:
                     err = e
             else:
@@ -289,7 +293,7 @@ class TGN(nn.Module):
                 warnings.warn(f"orca_b200: peer exchange buffers could not be shared ({err}); the layer-1 rows "
                               "are all-gathered with NCCL instead")
                 return
-            self.set_exchange(rows, flags, cap, keep)
+            self.set_exchange(rows, flags, cap, keep, grus, gcap)
             dist.barrier(group=group)
 
     @staticmethod
@@ -299,10 +303,12 @@ class TGN(nn.Module):
         neighbours a batch can have (a cold cache on the first batch reaches it)."""
         return world * shard.rows_per_rank(3 * bs + min(3 * bs * k, n_nodes), world) * _lib.DIM
 
-    def set_exchange(self, row_ptrs, flag_ptrs, cap, keep_alive=()):
+    def set_exchange(self, row_ptrs, flag_ptrs, cap, keep_alive=(), gru_ptrs=None, gru_cap=0):
         """Device addresses, as seen by this process, of every rank's exchange buffer (EXCHANGE_SLOTS *
-        cap floats) and flag words (int32[16], zeroed)."""
-        self._exchange = (list(row_ptrs), list(flag_ptrs), int(cap), list(keep_alive))
+        cap floats), flag words (int32[FLAG_WORDS], zeroed) and -- optional, for the node-split memory
+        update -- memory-row buffer (2 * gru_cap floats)."""
+        self._exchange = (list(row_ptrs), list(flag_ptrs), int(cap), list(keep_alive),
+                          list(gru_ptrs) if gru_ptrs else None, int(gru_cap))
         self._exchange_seq = np.zeros(1, dtype=np.int64)
         self._desc_ref = None
 
@@ -367,11 +373,14 @@ class TGN(nn.Module):
             return t
         t = _lib.TgnT()
         if getattr(self, "_exchange", None) is not None:
-            rows, flags, cap, _ = self._exchange
+            rows, flags, cap, _, grus, gcap = self._exchange
             for r in range(len(rows)):
                 t.peer_rows[r] = rows[r]
                 t.peer_flags[r] = flags[r]
+                if grus:
+                    t.peer_gru[r] = grus[r]
             t.exchange_cap = cap
+            t.gru_cap = gcap if grus else 0
             t.exchange_seq = self._exchange_seq.ctypes.data_as(C.POINTER(C.c_int64))
         self._desc_ref, self._desc = (nf, w, gw, k), t
         t.indptr, t.adj_nbr, t.adj_eid, t.adj_ts = (nf.indptr.data_ptr(), nf.adj_nbr.data_ptr(),

@@ -140,4 +140,15 @@ def prepare_time(sd):
     if np.any(np.asarray(sd["time_encoder.w.bias"]) != 0):
         raise ValueError("the time encoder's bias is frozen at zero in the reference "
                          "(model/time_encoding.py:19-21); a nonzero bias is not supported")
-    return np.ascontiguousarray(np.asarray(sd["time_encoder.w.weight"], dtype=np.float32).reshape(-1))
+    w = np.ascontiguousarray(np.asarray(sd["time_encoder.w.weight"], dtype=np.float32).reshape(-1))
+    # The gather kernel picks the cosine variant of a whole group of 64 columns from the group's first
+    # frequency: that is only right for the reference's frozen frequencies (positive, falling) and for
+    # groups whose frequencies stay within a factor 2^23 of each other (fixed-point reduction needs
+    # arguments above 2^-8 when the group's largest argument is below 2^30).
+    if np.any(w <= 0) or np.any(np.diff(w) > 0):
+        raise ValueError("the time encoder's frequencies must be positive and non-increasing, as the reference "
+                         "freezes them (model/time_encoding.py:18); other frequencies are not supported")
+    for lo in range(0, len(w), 64):
+        if w[lo] / w[min(lo + 63, len(w) - 1)] >= 2.0 ** 23:
+            raise ValueError("the time encoder's frequencies fall too fast within a group of 64 columns")
+    return w

@@ -329,7 +329,7 @@ def test_unsupported_modes_fail_loudly():
         tgn.compute_edge_probabilities(src, dst, dst, ts, eidx, 10, True, True, None)
 
 
-@pytest.mark.parametrize("world,direct", [(4, False), (8, False), (2, True), (8, True)])
+@pytest.mark.parametrize("world,direct", [(4, False), (8, False), (2, True), (8, True), (3, "split")])
 def test_sharded_entry_points_with_emulated_ranks(world, direct):
     """The row/edge split of the multi-GPU path for more ranks than GPUs at hand: every rank is a model
     replica of its own on this GPU, the two phases are called rank after rank through the C ABI (all ranks'
@@ -356,9 +356,14 @@ def test_sharded_entry_points_with_emulated_ranks(world, direct):
         from orca_b200.tgn import TGN
         cap = TGN.exchange_floats(spec.bs, world, spec.n_degree, g.n_nodes)
         bufs = [torch.zeros(_lib.EXCHANGE_SLOTS * cap, device=dev) for _ in range(world)]
-        flags = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(world)]
+        flags = [torch.zeros(_lib.FLAG_WORDS, dtype=torch.int32, device=dev) for _ in range(world)]
+        # "split": the memory update is split by node as well, its rows exchanged the same way
+        gcap = 2 * spec.bs * 172
+        grus = [torch.zeros(2 * gcap, device=dev) for _ in range(world)] if direct == "split" else None
         for m in ranks:
-            m.set_exchange([x.data_ptr() for x in bufs], [f.data_ptr() for f in flags], cap, bufs + flags)
+            m.set_exchange([x.data_ptr() for x in bufs], [f.data_ptr() for f in flags], cap, bufs + flags,
+                           [x.data_ptr() for x in grus] if grus else None, gcap)
+            m._keep_gru = grus
     stream = _lib.stream_ptr(dev)
     k = spec.n_degree
     worst = 0.0
@@ -404,3 +409,56 @@ def test_sharded_entry_points_with_emulated_ranks(world, direct):
         assert torch.equal(m.memory.memory, ref.memory.memory)
         assert torch.equal(m.embedding_module.histories[0].emb, ref.embedding_module.histories[0].emb)
         assert np.array_equal(m.embedding_module.histories[0].cache_flag, ref.embedding_module.histories[0].cache_flag)
+
+
+def test_wait_for_peers_gives_up_and_leaves_the_tables_alone():
+    """A rank whose peer never delivers its rows: the bounded waits of phase 2 run out (the limit is set to
+    about a millisecond), the status word reports ORCA_E_TIMEOUT, the kernels return, and neither the history
+    replica nor the memory table receives rows from the incomplete exchange.  Nothing faults or hangs: the
+    wait is a poll of a flag word that is never set."""
+    from orca_b200 import _lib, shard
+    from orca_b200.tgn import TGN
+    L = _lib.lib()
+    g = graph("t_nb2")
+    spec = g.spec
+    gold = golden("t_nb2")
+    plan = unpack(gold[f"plan_{spec.strategy}_flat"], gold[f"plan_{spec.strategy}_off"])
+    world = 2
+    m = make_model(g)
+    m._rank, m._world = 0, world
+    m.set_option(_lib.OPT_LOOKAHEAD, 0)
+    m.set_option(_lib.OPT_OVERLAP, 0)
+    m.set_option(_lib.OPT_WAIT_LIMIT, 2_000_000)
+    dev = m.device
+    cap = TGN.exchange_floats(spec.bs, world, spec.n_degree, g.n_nodes)
+    gcap = 2 * spec.bs * 172
+    bufs = [torch.zeros(_lib.EXCHANGE_SLOTS * cap, device=dev) for _ in range(world)]
+    flags = [torch.zeros(_lib.FLAG_WORDS, dtype=torch.int32, device=dev) for _ in range(world)]
+    grus = [torch.zeros(2 * gcap, device=dev) for _ in range(world)]
+    m.set_exchange([x.data_ptr() for x in bufs], [f.data_ptr() for f in flags], cap, bufs + flags + grus,
+                   [x.data_ptr() for x in grus], gcap)
+    _, src, dst, ts, eidx = next(iter(batches(g, 1)))
+    n, k = len(src), spec.n_degree
+    pl = np.asarray(plan[0], dtype=np.int32)
+    ints = torch.from_numpy(np.concatenate([src, dst, np.roll(dst, 3), eidx, pl]).astype(np.int32)).to(dev)
+    tsd = torch.from_numpy(np.ascontiguousarray(ts, dtype=np.float64)).to(dev)
+    desc = m._descriptor(k)
+    ws, u_cap = m._workspace(n, k)
+    hist_before = m.embedding_module.histories[0].emb.clone()
+    mem_before = m.memory.memory.clone()
+    prob = torch.zeros(2 * shard.rows_per_rank(n, world), device=dev)
+    stream = _lib.stream_ptr(dev)
+    for phase in (1, 2):        # rank 1 never runs: its flag words stay zero
+        _lib.check(L.orca_tgn_eval_batch_sharded(desc, phase, ints.data_ptr(), tsd.data_ptr(), n,
+                                                 ints.data_ptr() + 16 * n, len(pl), u_cap, ws.data_ptr(), ws.numel(),
+                                                 None, None, prob.data_ptr(), None, m._status.data_ptr(), stream))
+    with pytest.raises(_lib.OrcaError) as err:
+        m.check_status()
+    assert err.value.code == 6          # ORCA_E_TIMEOUT
+    assert torch.equal(m.embedding_module.histories[0].emb, hist_before)
+    assert torch.equal(m.memory.memory, mem_before)
+    # the context is still usable: an unsharded model on the same GPU runs a batch
+    ok = make_model(g)
+    p, q = ok.compute_edge_probabilities(src, dst, np.roll(dst, 3), ts, eidx, k, True, False, plan[0])
+    ok.check_status()
+    assert torch.isfinite(p).all() and torch.isfinite(q).all()
