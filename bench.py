@@ -449,10 +449,11 @@ def parity_vs_single(a, g, neg, plan, tgn, first, device, rank, world, n_batches
     return out
 
 
-# DRAM traffic of attn_gather_kernel: (dram__bytes_read.sum + dram__bytes_write.sum) of one launch captured
-# with ncu on workload c4 (15.25 MB read + 0 written) over the algorithmic bytes of that launch (30.68 MB),
-# applied to the algorithmic bytes of this run's launches; the counter cannot be read while timing
-GATHER_TRAFFIC_RATIO = 15.246848 / 30.683416
+# DRAM traffic of attn_gather_kernel: (dram__bytes_read.sum + dram__bytes_write.sum) of two consecutive
+# launches captured with ncu on workload c4 (17.01 + 16.65 MB read, 0 written) over the algorithmic bytes of
+# those launches (2 x 30.68 MB), applied to the algorithmic bytes of this run's launches; the counter cannot
+# be read while timing
+GATHER_TRAFFIC_RATIO = (17.011200 + 16.645632) / (2 * 30.683416)
 
 
 def oracle_sample(g, neg, plan, first, n_batches, sub_bs, threads, min_seconds=0.0):
