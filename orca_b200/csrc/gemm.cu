@@ -514,11 +514,13 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
     a.bias = w->b1;
     a.bias2 = w->g;
     a.out = d_scratch_hidden;
-    // (19 k-blocks on a single column tile and only ~47 row blocks per batch.  Splitting K over a cluster
-    // of 3 CTAs was measured slower at 6000 rows -- 47 clusters of three 157-KB CTAs do not all fit at
-    // once and the summing pass over distributed shared memory takes 5 us instead of 2 -- and was removed.)
+    // (19 k-blocks per row block and only ~47-61 row blocks per batch: the projection runs as two tiles of 96
+    // columns -- G is packed for that width -- so that twice as many SMs take part, each with half the tensor
+    // time and half the weight bytes per k-block.  Splitting K over a cluster of 3 CTAs instead was measured
+    // slower and removed: the clusters do not all fit at once and the summing pass over distributed shared
+    // memory takes 5 us.)
     (void)rows_hint;
-    int rc = tc::launch(tc::EPI_HIDDEN, a, 1, (cudaStream_t)stream);
+    int rc = tc::launch(tc::EPI_HIDDEN2, a, 2, (cudaStream_t)stream);
     if (rc) return rc;
     tc::Args b{};
     b.a0 = tc::RowSrc{d_scratch_hidden, nullptr, D, 0, 0};

@@ -197,6 +197,11 @@ __device__ __align__(16) float g_zero16[4] = {0.f, 0.f, 0.f, 0.f};
 // memory, lanes along the columns (two 16-byte pieces per lane); four rows are in flight per warp so
 // that their load / shuffle / store chains overlap.  meta_a / meta_b: lane i of warp w holds the
 // per-row inputs of row w + 10*i (validity, push winner and id, GRU node).
+// columns of a tile: the hidden projection of the merger may run as two tiles of 96 columns (EPI_HIDDEN2),
+// which halves the tensor time and the weight bytes per CTA and doubles the CTAs
+template <int EPI>
+constexpr int tile_bn() { return EPI == EPI_HIDDEN2 ? 96 : BN; }
+
 template <int EPI>
 __device__ __forceinline__ void tile_output(const Args &g, const float *tile, const float *s_bias, const float *s_v1,
                                             const float *s_v2, const float *s_dot, int m0, int m_rows, int nt,
@@ -207,9 +212,12 @@ __device__ __forceinline__ void tile_output(const Args &g, const float *tile, co
     return;
   }
   constexpr int RB = 4;   // (2 measured the same, 8 spills)
-  const int c0 = nt * BN;
+  constexpr int BNv = tile_bn<EPI>();
+  constexpr bool kHidden = EPI == EPI_HIDDEN || EPI == EPI_HIDDEN2;
+  const int c0 = nt * BNv;
   const int j0 = lane, j1 = lane + 32;
-  const int nj = (EPI == EPI_BIAS || EPI == EPI_GRU) ? BN / 4 : D / 4;
+  const int nj = (EPI == EPI_BIAS || EPI == EPI_GRU) ? BNv / 4 : (EPI == EPI_HIDDEN2 ? min(BNv, D - c0) / 4 : D / 4);
+  const bool has0 = j0 < nj;      // (only a 96-column tile leaves lanes without a first piece)
   const bool has1 = j1 < nj;
   const float4 f4z = make_float4(0.f, 0.f, 0.f, 0.f);
   const float4 bA = *reinterpret_cast<const float4 *>(&s_bias[4 * j0]);
@@ -219,7 +227,7 @@ __device__ __forceinline__ void tile_output(const Args &g, const float *tile, co
   const float4 lA = *reinterpret_cast<const float4 *>(&s_v2[4 * j0]);
   const float4 lB = has1 ? *reinterpret_cast<const float4 *>(&s_v2[4 * j1]) : f4z;
   auto add4 = [](float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); };
-  const int uA = nt * (BN / 4) + j0, uB = nt * (BN / 4) + j1;   // GRU units of this lane
+  const int uA = nt * (BNv / 4) + j0, uB = nt * (BNv / 4) + j1;   // GRU units of this lane
   const uint32_t tile_saddr = smem_addr(tile);
   for (int it0 = 0; warp + (THREADS / 32) * it0 < m_rows; it0 += RB) {
     float4 a[RB], b[RB];
@@ -252,12 +260,12 @@ __device__ __forceinline__ void tile_output(const Args &g, const float *tile, co
           *reinterpret_cast<float4 *>(o + 4 * j0) = a[k];
           if (has1) *reinterpret_cast<float4 *>(o + 4 * j1) = b[k];
         }
-    } else if (EPI == EPI_HIDDEN) {
+    } else if (kHidden) {
 #pragma unroll
       for (int k = 0; k < RB; ++k)
-        if (ok[k]) {
+        if (ok[k] && has0) {
           const float rvf = ma[k] != 0 ? 1.f : 0.f;
-          float *o = g.out + (size_t)m[k] * D;
+          float *o = g.out + (size_t)m[k] * D + c0;
           *reinterpret_cast<float4 *>(o + 4 * j0) =
               make_float4(fmaxf(a[k].x + rvf * vA.x, 0.f), fmaxf(a[k].y + rvf * vA.y, 0.f),
                           fmaxf(a[k].z + rvf * vA.z, 0.f), fmaxf(a[k].w + rvf * vA.w, 0.f));
@@ -342,6 +350,8 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   const int pw = grp ? warp - 6 : warp;   // producer warp within its group: tile rows pw*32 .. pw*32+31
   const int rsub = lane >> 3, f = lane & 7;
   const int w0 = g.a0.width, w1 = g.a1.width, Kd = g.Kd;
+  constexpr int BNv = tile_bn<EPI>();
+  constexpr uint32_t BvLBO = BNv * 16, BvBYTES = CHUNKS * BvLBO;   // weight images of this tile width
   const int rstride = g.row_stride > 1 ? g.row_stride : 1;
   const int nkb = g.n_kblocks;
 
@@ -371,7 +381,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     const int r = warp + (THREADS / 32) * lane;
     const int m = m0 + r;
     if (r < BM && m < limit) {
-      if (EPI == EPI_HIDDEN) meta_a = g.row_valid == nullptr ? 1 : g.row_valid[m];
+      if (EPI == EPI_HIDDEN || EPI == EPI_HIDDEN2) meta_a = g.row_valid == nullptr ? 1 : g.row_valid[m];
       if (EPI == EPI_LAYERNORM && g.push_table != nullptr) {
         meta_b = g.push_ids[m];
         if (g.push_win != nullptr) meta_a = g.push_win[m];
@@ -443,12 +453,13 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   // an L2 round trip into every step of the epilogue)
   __shared__ __align__(16) float s_bias[BN], s_v1[BN], s_v2[BN];
   if (warp == 4 || warp == 5) {
-    const int lim = (EPI == EPI_BIAS || EPI == EPI_GRU) ? BN : D;
+    const int lim = (EPI == EPI_BIAS || EPI == EPI_GRU) ? BNv : D - nt * BNv;   // columns of this tile that exist
     for (int i = tid - 128; i < BN; i += 64) {
-      const bool in = i < lim;
-      s_bias[i] = in ? g.bias[nt * BN + i] : 0.f;
-      const float *v1 = EPI == EPI_HIDDEN ? g.bias2 : EPI == EPI_LAYERNORM ? g.ln_w : EPI == EPI_SCORE ? g.w2 : nullptr;
-      s_v1[i] = (v1 != nullptr && in) ? v1[i] : 0.f;
+      const bool in = i < lim && i < BNv;
+      s_bias[i] = in ? g.bias[nt * BNv + i] : 0.f;
+      const float *v1 = (EPI == EPI_HIDDEN || EPI == EPI_HIDDEN2) ? g.bias2
+                        : EPI == EPI_LAYERNORM ? g.ln_w : EPI == EPI_SCORE ? g.w2 : nullptr;
+      s_v1[i] = (v1 != nullptr && in) ? v1[nt * BNv + i] : 0.f;
       s_v2[i] = (EPI == EPI_LAYERNORM && in) ? g.ln_b[i] : 0.f;
     }
   }
@@ -508,21 +519,21 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
       // ---------------------------------------------------------------- weight stages
       if (lane == 0) {
         const char *wsrc = reinterpret_cast<const char *>(g.w_packed) +
-                           (size_t)nt * g.n_kblocks * (2 * B_BYTES);
+                           (size_t)nt * g.n_kblocks * (2 * BvBYTES);
         for (int kb = 0; kb < nkb; ++kb) {
           const int s = kb & 1;
           const int u = t * (s ? uses1 : uses0) + (kb >> 1);
           mbar_wait(empty(s), (u & 1) ^ 1, g.status, 200 + s, alive, g.wait_limit);
-          mbar_expect_tx(full(s), 2 * B_BYTES);
-          bulk_g2s(sm.b_hi(s), wsrc + (size_t)kb * (2 * B_BYTES), 2 * B_BYTES, full(s));
+          mbar_expect_tx(full(s), 2 * BvBYTES);
+          bulk_g2s(sm.b_hi(s), wsrc + (size_t)kb * (2 * BvBYTES), 2 * BvBYTES, full(s));
         }
       }
       __syncwarp();
     } else {
       // ---------------------------------------------------------------- MMA issue
       if (lane == 0) {
-        // fp32 accumulate, bf16 x bf16, both K-major, N = 176, M = 128
-        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+        // fp32 accumulate, bf16 x bf16, both K-major, N = 176 (96), M = 128
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BNv >> 3) << 17) |
                                    ((uint32_t)(BM >> 4) << 24);
         for (int kb = 0; kb < nkb; ++kb) {
           const int s = kb & 1;
@@ -533,8 +544,9 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
           for (int ks = 0; ks < BK / 16; ++ks) {
             const uint64_t ah = make_desc(sm.a_hi(s) + ks * 2 * A_LBO, A_LBO, A_SBO);
             const uint64_t al = make_desc(sm.a_lo(s) + ks * 2 * A_LBO, A_LBO, A_SBO);
-            const uint64_t bh = make_desc(sm.b_hi(s) + ks * 2 * B_LBO, B_LBO, B_SBO);
-            const uint64_t bl = make_desc(sm.b_lo(s) + ks * 2 * B_LBO, B_LBO, B_SBO);
+            // (the tail image follows the head image of the stage copy directly)
+            const uint64_t bh = make_desc(sm.b_hi(s) + ks * 2 * BvLBO, BvLBO, B_SBO);
+            const uint64_t bl = make_desc(sm.b_hi(s) + BvBYTES + ks * 2 * BvLBO, BvLBO, B_SBO);
             const uint32_t first = (kb > 0 || ks > 0) ? 1u : 0u;
             mma_bf16(tmem, ah, bh, idesc, first);
             mma_bf16(tmem + TMEM_SMALL, al, bh, idesc, first);
@@ -561,7 +573,8 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
       const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
       const uint32_t trow_sa = base + (uint32_t)(row * TILE_LD) * 4u;   // the tile starts at the stage ring
       float dot = 0.f;
-      const int ch0 = grp ? 6 : 0, ch1 = grp ? BN / 16 : 6;
+      constexpr int kSplit = (BNv / 16 + 1) / 2;   // accumulator chunks of 16 columns: first half / second half
+      const int ch0 = grp ? kSplit : 0, ch1 = grp ? BNv / 16 : kSplit;
       for (int ch = ch0; ch < ch1; ++ch) {
         float v[16];
         tmem_ld16_sum(trow + ch * 16, v);
@@ -622,6 +635,7 @@ int launch(int epilogue, const Args &a, int n_tiles, cudaStream_t stream) {
     ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_LAYERNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_GRU>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_SCORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_HIDDEN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     configured_device = c->device;
   }
   Args b = a;
@@ -636,6 +650,7 @@ int launch(int epilogue, const Args &a, int n_tiles, cudaStream_t stream) {
     case EPI_LAYERNORM: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_LAYERNORM>, grid, THREADS, SMEM_BYTES, stream, b)); break;
     case EPI_GRU: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_GRU>, grid, THREADS, SMEM_BYTES, stream, b)); break;
     case EPI_SCORE: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_SCORE>, grid, THREADS, SMEM_BYTES, stream, b)); break;
+    case EPI_HIDDEN2: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_HIDDEN2>, grid, THREADS, SMEM_BYTES, stream, b)); break;
     default: return set_error(ORCA_E_BADARG, "tc::launch: unknown epilogue %d", epilogue);
   }
   ORCA_COUNT_LAUNCH();

@@ -46,7 +46,8 @@ struct PeerOut {
   int world, rank, seq;
 };
 
-enum Epilogue { EPI_BIAS = 0, EPI_HIDDEN = 1, EPI_LAYERNORM = 2, EPI_GRU = 3, EPI_SCORE = 4 };
+// (EPI_HIDDEN2: the HIDDEN epilogue on tiles of 96 columns, weights packed for that width)
+enum Epilogue { EPI_BIAS = 0, EPI_HIDDEN = 1, EPI_LAYERNORM = 2, EPI_GRU = 3, EPI_SCORE = 4, EPI_HIDDEN2 = 5 };
 
 struct Args {
   RowSrc a0, a1;             // a1.width == 0 when unused

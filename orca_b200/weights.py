@@ -23,6 +23,7 @@ D = 172
 HEADS = 2
 QT_HEAD = 528     # column stride of one head of the projected query (516 used)
 TC_BN, TC_BK = 176, 64
+TC_BN_HIDDEN = 96   # tile width of the merger's hidden projection (two tiles cover its 172 columns)
 
 
 def _bf16_round(x):
@@ -31,26 +32,27 @@ def _bf16_round(x):
     return ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32).view(np.float32)
 
 
-def pack_tc(W):
+def pack_tc(W, bn=None):
     """Packs a row-major [K, N] matrix for the tensor-core kernel (csrc/tc_gemm.cu).
 
-    N is cut into tiles of 176 columns and K into blocks of 64 rows (both zero padded).  One
-    (tile, block) stage image is [head | tail], each [8 chunks][176 columns][8 bf16]: element
+    N is cut into tiles of `bn` (default 176) columns and K into blocks of 64 rows (both zero padded).
+    One (tile, block) stage image is [head | tail], each [8 chunks][bn columns][8 bf16]: element
     (k, n) of the block sits at chunk k // 8, column n, position k % 8 -- the K-major, no-swizzle
     core-matrix layout the MMA reads from shared memory -- so that a stage is one contiguous bulk
     copy.  head = the value rounded to bf16, tail = the remainder rounded to bf16 (16 significant
-    bits together).  Returned as uint16 [n_tiles, n_kblocks, 2, 8, 176, 8]."""
+    bits together).  Returned as uint16 [n_tiles, n_kblocks, 2, 8, bn, 8]."""
     W = np.asarray(W, dtype=np.float32)
     K, N = W.shape
-    nkb, nt = -(-K // TC_BK), -(-N // TC_BN)
-    P = np.zeros((nkb * TC_BK, nt * TC_BN), dtype=np.float32)
+    bn = bn or TC_BN
+    nkb, nt = -(-K // TC_BK), -(-N // bn)
+    P = np.zeros((nkb * TC_BK, nt * bn), dtype=np.float32)
     P[:K, :N] = W
     head = _bf16_round(P)
     tail = _bf16_round(P - head)
 
     def image(X):  # [nkb*64, nt*176] -> [nt, nkb, 8, 176, 8] of bf16 bit patterns
         bits = (X.view(np.uint32) >> 16).astype(np.uint16)
-        return bits.reshape(nkb, TC_BK // 8, 8, nt, TC_BN).transpose(3, 0, 1, 4, 2)
+        return bits.reshape(nkb, TC_BK // 8, 8, nt, bn).transpose(3, 0, 1, 4, 2)
 
     return np.ascontiguousarray(np.stack([image(head), image(tail)], axis=2))
 
@@ -97,7 +99,7 @@ def prepare_attention(sd, layer: int, dim: int = D, heads: int = HEADS):
     }
     out = {k: np.ascontiguousarray(v, dtype=np.float32) for k, v in out.items()}
     for k in ("Mq", "G", "W2t"):
-        out[k + "_tc"] = pack_tc(out[k])
+        out[k + "_tc"] = pack_tc(out[k], bn=TC_BN_HIDDEN if k == "G" else None)
     return out
 
 
