@@ -153,9 +153,9 @@ def build_setup(a, device, quiet=True):
             m = min(g.n_edges, a.plan_batches * spec.bs)
             sub = types.SimpleNamespace(sources=g.sources[:m], destinations=g.destinations[:m],
                                         timestamps=g.timestamps[:m])
-            plan = get_cache_plan(ns, sub, nf, g.n_nodes, spec.strategy)
+            plan = get_cache_plan(ns, sub, nf, g.n_nodes, spec.strategy, broadcast_from=0)
         else:
-            plan = get_cache_plan(ns, g, nf, g.n_nodes, spec.strategy)
+            plan = get_cache_plan(ns, g, nf, g.n_nodes, spec.strategy, broadcast_from=0)
     t2 = time.time()
     tgn = TGN(neighbor_finder=nf, node_features=None, edge_features=g.edge_features, device=device,
               n_layers=spec.n_layers, n_heads=2, dropout=0.1, use_memory=True, node_dimension=172,

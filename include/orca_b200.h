@@ -337,6 +337,21 @@ int orca_plan_host(int32_t strategy, const int64_t *h_src, const int64_t *h_dst,
                    uint32_t seed, int32_t *h_plan_flat, int64_t plan_cap, int64_t *h_plan_off,
                    double *h_stats);
 
+/* The MRD plan computed on the device (utils/cache.py:19-89 and 92-166, one call for both).
+ * d_nodes: the query list described above ([2*n_edges] int32, batch b = its sources, then its
+ * destinations); d_nbr: the neighbour table sampled for it ([2*n_edges, k] int32).  Two kernels walk
+ * the batches, one backwards (next use of every node at every batch) and one forwards (candidates from
+ * bitmaps in ascending order, keys, the first `budget` places of numba's argsort with its order among
+ * equal keys, statistics).  Outputs, all on the device: d_plan_flat / d_plan_off as in orca_plan_host
+ * (plan_cap >= n_batches * budget always suffices), d_stats = int64 {n_reuse, n_recompute, sum of
+ * reuse distances}, d_status (int32[4], ORCA_E_CAPACITY when d_plan_flat is too small).
+ * Enqueues on `stream`; the workspace (256-byte aligned) is sized by orca_plan_mrd_workspace_bytes. */
+int64_t orca_plan_mrd_workspace_bytes(int64_t n_edges, int32_t bs, int32_t k, int64_t n_nodes, int32_t budget);
+int orca_plan_mrd(const int32_t *d_nodes, int64_t n_edges, int32_t bs, int32_t k, const int32_t *d_nbr,
+                  int64_t n_nodes, int32_t budget, int32_t *d_plan_flat, int64_t plan_cap,
+                  int64_t *d_plan_off, int64_t *d_stats, int32_t *d_status, void *d_workspace,
+                  int64_t workspace_bytes, void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * One whole eval batch: TGN.compute_edge_probabilities(..., reuse=True, train=False, cache_plan)
  * with budget != 0 (model/tgn_model.py:95-157 over modules/embedding_module.py:215-285), enqueued

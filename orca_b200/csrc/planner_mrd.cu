@@ -1,0 +1,443 @@
+// MRD cache planning on the device (utils/cache.py:19-89 read_batches + :92-166 MRD_numba).
+//
+// Input: the query list of all batches (batch b = its sources, then its destinations) and the neighbour
+// table the sampling kernel produced for it.  Two persistent single-CTA kernels walk the batches:
+//
+//   next_use_kernel   backwards.  Keeps, per node, the code of its nearest LATER use
+//                     (2 * batch + 1 if that use is as an out-of-batch neighbour, 2 * batch if as a
+//                     target, 2 * n_batches if none) and stores, beside every entry of the query list
+//                     and of the neighbour table, the code its node has at that batch.  This replaces
+//                     the reference's per-node occurrence lists and their cursors: the key of a
+//                     candidate at batch b is (code & 1) ? (code >> 1) - b : 1e8 + 1.
+//   mrd_kernel        forwards.  Per batch: targets and uncached out-of-batch neighbours are marked in
+//                     a bitmap of fresh nodes (and counted for the reuse statistics), the candidates
+//                     cached | fresh are listed in ascending order from the bitmaps, their keys are read
+//                     from the codes, and the first `budget` positions of numba's argsort become the
+//                     new cache.
+//
+// numba's nopython np.argsort is an unstable quicksort (median of three, pivot parked at the right
+// end, Hoare scans that stop on equal keys, ranges of fewer than 16 finished by insertion), and with
+// most keys tied at 1e8 + 1 WHICH tied nodes stay below the budget line depends on every swap it makes.
+// The kernel reproduces its result without walking it serially.  One partition step moves elements
+// only by swapping the m-th position from the left whose key is >= pivot with the m-th position from
+// the right whose key is <= pivot, for as long as the former lies left of the latter; both position
+// lists follow from prefix counts, so a step is a block-wide scan plus independent swaps, and all
+// ranges of one recursion depth are partitioned in the same step.  Ranges that start at or after the
+// budget line are left alone.  The final insertion sort is stable, so a position's place in its range is
+// its rank by (key, position).
+#include "common.cuh"
+
+namespace orca {
+namespace mrd {
+
+constexpr int T = 1024;
+constexpr int NW = T / 32;
+constexpr int32_t FAR_KEY = 100000001;  // MAX_DISTANCE + 1 of utils/cache.py:95,147-149
+
+struct Work {
+  int32_t *nx_query;  // [2E]     code of the next use, per query-list entry
+  int32_t *nx_table;  // [2E*k]   the same per neighbour-table entry (out-of-batch entries only)
+  int32_t *code;      // [n_nodes] backward pass: nearest later use; forward pass: next use
+  int32_t *stamp;     // [n_nodes] last batch in which the node was a target
+  int32_t *since;     // [n_nodes] batch in which the cached embedding was computed (time_flag)
+  uint32_t *cached;   // [words]
+  uint32_t *fresh;    // [words]  uncached out-of-batch neighbours and targets of the batch (new_computed)
+  int32_t *cand;      // [cap] candidate ids, ascending
+  uint64_t *e;        // [cap] key << 32 | index into cand, in sort order
+  int2 *seg;          // [cap] range (lo, hi) a position belongs to
+  int2 *pre;          // [cap] prefix counts (left list, right list) before the position
+  int32_t *lpos, *rpos;        // [cap] positions of a range's left / right list, stored from its lo
+  int32_t *pivot;     // [cap] per range, at index lo
+  int32_t *swaps;     // [2][cap] per range, at index lo: pair swaps of its step; the halves alternate by
+                      // depth, because a step's count is still read while the next pivots are parked
+};
+
+__host__ __device__ inline int64_t words_of(int64_t n_nodes) { return (n_nodes + 31) / 32; }
+__host__ __device__ inline int64_t cand_cap(int32_t bs, int32_t k, int32_t budget) {
+  return (int64_t)budget + 2ll * bs * (k + 1);
+}
+
+__device__ __forceinline__ int32_t key_of(uint64_t x) { return (int32_t)(x >> 32); }
+
+// ------------------------------------------------------------------------------ backward pass
+__global__ void __launch_bounds__(T) next_use_kernel(const int32_t *nodes, const int32_t *nbr, int64_t n_edges,
+                                                     int32_t bs, int32_t k, int64_t n_nodes, Work w) {
+  const int tid = threadIdx.x;
+  const int64_t nb = (n_edges + bs - 1) / bs;
+  for (int64_t v = tid; v < n_nodes; v += T) {
+    w.code[v] = (int32_t)(2 * nb);
+    w.stamp[v] = -1;
+  }
+  __syncthreads();
+  for (int64_t b = nb - 1; b >= 0; --b) {
+    const int64_t s = b * bs;
+    const int m2 = 2 * (int)(min(n_edges, s + bs) - s);
+    const int32_t *q = nodes + 2 * s;
+    const int32_t *tab = nbr + 2 * s * k;
+    int32_t *nq = w.nx_query + 2 * s;
+    int32_t *nt = w.nx_table + 2 * s * k;
+    for (int i = tid; i < m2; i += T) {
+      const int32_t v = q[i];
+      nq[i] = w.code[v];
+      w.stamp[v] = (int32_t)b;
+    }
+    __syncthreads();
+    for (int i = tid; i < m2 * k; i += T) {
+      const int32_t v = tab[i];
+      if (v != 0 && w.stamp[v] != (int32_t)b) nt[i] = w.code[v];
+    }
+    __syncthreads();
+    for (int i = tid; i < m2; i += T) w.code[q[i]] = (int32_t)(2 * b);
+    for (int i = tid; i < m2 * k; i += T) {
+      const int32_t v = tab[i];
+      if (v != 0 && w.stamp[v] != (int32_t)b) w.code[v] = (int32_t)(2 * b + 1);
+    }
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------------------ forward pass
+// median of three on (lo, mid, hi), pivot parked at hi (the head of numba's partition step)
+__device__ __forceinline__ void park_pivot(const Work &w, int lo, int hi, int32_t *swaps) {
+  const int mid = (lo + hi) >> 1;
+  uint64_t a = w.e[lo], c = w.e[mid], d = w.e[hi];
+  uint64_t t;
+  if (key_of(c) < key_of(a)) { t = a; a = c; c = t; }
+  if (key_of(d) < key_of(c)) { t = d; d = c; c = t; }
+  if (key_of(c) < key_of(a)) { t = a; a = c; c = t; }
+  w.e[lo] = a;
+  w.e[mid] = d;
+  w.e[hi] = c;
+  w.pivot[lo] = key_of(c);
+  swaps[lo] = 0;
+}
+
+__device__ __forceinline__ bool live(int lo, int hi, int keep) { return hi - lo >= 15 && lo < keep; }
+
+// where the pivot of range (lo, hi) ends up once its pair swaps are done
+__device__ __forceinline__ int pivot_place(const Work &w, int lo, int hi, const int32_t *swaps) {
+  const int2 a = w.pre[lo], z = w.pre[hi];
+  const int n_left = z.x - a.x;
+  const int m = swaps[lo];
+  const int from_left = m < n_left ? w.lpos[lo + m] : hi;
+  const int from_right = m > 0 ? w.rpos[lo + m - 1] : hi;
+  return min(from_left, from_right);
+}
+
+__global__ void __launch_bounds__(T) mrd_kernel(const int32_t *nodes, const int32_t *nbr, int64_t n_edges, int32_t bs,
+                                                int32_t k, int64_t n_nodes, int32_t budget, Work w,
+                                                int32_t *plan, int64_t plan_cap, int64_t *plan_off,
+                                                int64_t *stats, int32_t *status) {
+  __shared__ int s_l[NW], s_r[NW];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  const int64_t nb = (n_edges + bs - 1) / bs;
+  const int64_t words = words_of(n_nodes);
+  for (int64_t v = tid; v < n_nodes; v += T) {
+    w.stamp[v] = -1;
+    w.since[v] = 0;
+  }
+  for (int64_t i = tid; i < words; i += T) {
+    w.cached[i] = 0;
+    w.fresh[i] = 0;
+  }
+  __syncthreads();
+  long long reuse = 0, recompute = 0, dist = 0;
+  int64_t used = 0;
+  const int wchunk = (int)(((words + NW - 1) / NW + 31) & ~31ll);  // bitmap words per warp
+  const int64_t cap = cand_cap(bs, k, budget);
+  for (int64_t b = 0; b < nb; ++b) {
+    const int64_t s = b * bs;
+    const int m2 = 2 * (int)(min(n_edges, s + bs) - s);
+    const int32_t *q = nodes + 2 * s;
+    const int32_t *tab = nbr + 2 * s * k;
+    const int32_t *nq = w.nx_query + 2 * s;
+    const int32_t *nt = w.nx_table + 2 * s * k;
+    // targets
+    for (int i = tid; i < m2; i += T) {
+      const int32_t v = q[i];
+      w.stamp[v] = (int32_t)b;
+      w.code[v] = nq[i];
+      atomicOr(&w.fresh[v >> 5], 1u << (v & 31));
+    }
+    __syncthreads();
+    // out-of-batch neighbour occurrences: reuse statistics, uncached ones become fresh
+    for (int i = tid; i < m2 * k; i += T) {
+      const int32_t v = tab[i];
+      if (v == 0 || w.stamp[v] == (int32_t)b) continue;
+      w.code[v] = nt[i];
+      if ((__ldcg(&w.cached[v >> 5]) >> (v & 31)) & 1u) {
+        ++reuse;
+        dist += b - w.since[v];
+      } else {
+        ++recompute;
+        atomicOr(&w.fresh[v >> 5], 1u << (v & 31));
+      }
+    }
+    __syncthreads();
+    // candidates = cached | fresh in ascending order, with their keys
+    {
+      int cnt = 0;
+      for (int j = lane; j < wchunk; j += 32) {
+        const int64_t wi = (int64_t)warp * wchunk + j;
+        if (wi < words) cnt += __popc(__ldcg(&w.cached[wi]) | __ldcg(&w.fresh[wi]));
+      }
+      for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+      if (lane == 0) s_l[warp] = cnt;
+    }
+    __syncthreads();
+    int n = 0, base = 0;
+    for (int i = 0; i < NW; ++i) {
+      const int c = s_l[i];
+      if (i < warp) base += c;
+      n += c;
+    }
+    for (int j = 0; j < wchunk; j += 32) {
+      const int64_t wi = (int64_t)warp * wchunk + j + lane;
+      uint32_t bits = 0;
+      if (wi < words) {
+        bits = __ldcg(&w.cached[wi]) | __ldcg(&w.fresh[wi]);
+        w.cached[wi] = 0;
+      }
+      const int c = __popc(bits);
+      int incl = c;
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      int pos = base + incl - c;
+      base += __shfl_sync(0xffffffffu, incl, 31);
+      while (bits) {
+        const int bit = __ffs(bits) - 1;
+        bits &= bits - 1;
+        const int32_t v = (int32_t)(wi * 32 + bit);
+        const int32_t code = w.code[v];
+        const int32_t key = (code & 1) ? (code >> 1) - (int32_t)b : FAR_KEY;
+        w.cand[pos] = v;
+        w.e[pos] = ((uint64_t)(uint32_t)key << 32) | (uint32_t)pos;
+        w.seg[pos] = make_int2(0, n - 1);
+        ++pos;
+      }
+    }
+    const int keep = min(n, budget);
+    if (used + keep > plan_cap) {  // uniform over the block
+      if (tid == 0) report(status, ORCA_E_CAPACITY, (int)b);
+      break;
+    }
+    __syncthreads();
+    // ---- the first `keep` positions of numba's argsort
+    bool any = live(0, n - 1, keep);
+    int32_t *swaps = w.swaps, *swaps_next = w.swaps + cap;
+    if (any && tid == 0) park_pivot(w, 0, n - 1, swaps);
+    __syncthreads();
+    const int chunk = ((n + NW - 1) / NW + 31) & ~31;  // positions per warp in the scan
+    while (any) {
+      // prefix counts of the left list (key >= pivot) and the right list (key <= pivot) over [lo, hi)
+      int cl = 0, cr = 0;
+      for (int j = 0; j < chunk; j += 32) {
+        const int pos = warp * chunk + j + lane;
+        bool is_l = false, is_r = false;
+        if (pos < n) {
+          const int2 sg = w.seg[pos];
+          if (live(sg.x, sg.y, keep) && pos < sg.y) {
+            const int32_t kv = key_of(w.e[pos]), pv = w.pivot[sg.x];
+            is_l = kv >= pv;
+            is_r = kv <= pv;
+          }
+        }
+        cl += __popc(__ballot_sync(0xffffffffu, is_l));
+        cr += __popc(__ballot_sync(0xffffffffu, is_r));
+      }
+      if (lane == 0) {
+        s_l[warp] = cl;
+        s_r[warp] = cr;
+      }
+      __syncthreads();
+      int bl = 0, br = 0;
+      for (int i = 0; i < warp; ++i) {
+        bl += s_l[i];
+        br += s_r[i];
+      }
+      for (int j = 0; j < chunk; j += 32) {
+        const int pos = warp * chunk + j + lane;
+        bool is_l = false, is_r = false;
+        if (pos < n) {
+          const int2 sg = w.seg[pos];
+          if (live(sg.x, sg.y, keep) && pos < sg.y) {
+            const int32_t kv = key_of(w.e[pos]), pv = w.pivot[sg.x];
+            is_l = kv >= pv;
+            is_r = kv <= pv;
+          }
+        }
+        const uint32_t ml = __ballot_sync(0xffffffffu, is_l), mr = __ballot_sync(0xffffffffu, is_r);
+        if (pos < n) w.pre[pos] = make_int2(bl + __popc(ml & lt_mask), br + __popc(mr & lt_mask));
+        bl += __popc(ml);
+        br += __popc(mr);
+      }
+      __syncthreads();
+      // the two position lists of every range
+      for (int pos = tid; pos < n; pos += T) {
+        const int2 sg = w.seg[pos];
+        if (!live(sg.x, sg.y, keep) || pos >= sg.y) continue;
+        const int32_t kv = key_of(w.e[pos]), pv = w.pivot[sg.x];
+        const int2 me = w.pre[pos];
+        if (kv >= pv) w.lpos[sg.x + me.x - w.pre[sg.x].x] = pos;
+        if (kv <= pv) w.rpos[sg.x + w.pre[sg.y].y - me.y - 1] = pos;
+      }
+      __syncthreads();
+      // pair m swaps while its left position is left of its right position
+      for (int pos = tid; pos < n; pos += T) {
+        const int2 sg = w.seg[pos];
+        if (!live(sg.x, sg.y, keep) || pos >= sg.y) continue;
+        const int2 a = w.pre[sg.x], z = w.pre[sg.y];
+        const int pairs = min(z.x - a.x, z.y - a.y);
+        const int m = pos - sg.x;
+        if (m >= pairs) continue;
+        const int pl = w.lpos[pos], pr = w.rpos[pos];
+        if (pl >= pr) continue;
+        const uint64_t x = w.e[pl], y = w.e[pr];
+        w.e[pl] = y;
+        w.e[pr] = x;
+        if (m + 1 >= pairs || w.lpos[pos + 1] >= w.rpos[pos + 1]) swaps[sg.x] = m + 1;
+      }
+      __syncthreads();
+      // pivot into place, ranges split, next pivots parked
+      bool more = false;
+      for (int pos = tid; pos < n; pos += T) {
+        int2 sg = w.seg[pos];
+        if (!live(sg.x, sg.y, keep)) continue;
+        const int p = pivot_place(w, sg.x, sg.y, swaps);
+        if (pos == p + 1) {
+          // the first position right of the pivot's place moves the pivot there (nobody else reads
+          // either slot in this phase: hi belongs to the right part, p to no part)
+          const uint64_t x = w.e[p], y = w.e[sg.y];
+          w.e[p] = y;
+          w.e[sg.y] = x;
+        }
+        if (pos < p) sg.y = p - 1;
+        else if (pos > p) sg.x = p + 1;
+        else sg.x = sg.y = p;
+        w.seg[pos] = sg;
+        if (live(sg.x, sg.y, keep)) {
+          more = true;
+          if (pos == sg.x) park_pivot(w, sg.x, sg.y, swaps_next);
+        }
+      }
+      any = __syncthreads_or(more);
+      int32_t *t = swaps;
+      swaps = swaps_next;
+      swaps_next = t;
+    }
+    // ranges shorter than 16: stable order by key; the first `keep` places are the new cache
+    if (tid == 0) plan_off[b] = used;
+    for (int pos = tid; pos < n; pos += T) {
+      const int2 sg = w.seg[pos];
+      if (sg.x >= keep) continue;
+      const uint64_t me = w.e[pos];
+      const int32_t kv = key_of(me);
+      int place = sg.x;
+      for (int qpos = sg.x; qpos <= sg.y; ++qpos) {
+        const int32_t ko = key_of(w.e[qpos]);
+        place += (ko < kv || (ko == kv && qpos < pos)) ? 1 : 0;
+      }
+      if (place >= keep) continue;
+      const int32_t v = w.cand[(uint32_t)me];
+      plan[used + place] = v;
+      atomicOr(&w.cached[v >> 5], 1u << (v & 31));
+      if ((__ldcg(&w.fresh[v >> 5]) >> (v & 31)) & 1u) w.since[v] = (int32_t)b;
+    }
+    used += keep;
+    __syncthreads();
+    for (int64_t i = tid; i < words; i += T) w.fresh[i] = 0;
+    __syncthreads();
+  }
+  // totals
+  for (int o = 16; o > 0; o >>= 1) {
+    reuse += __shfl_xor_sync(0xffffffffu, reuse, o);
+    recompute += __shfl_xor_sync(0xffffffffu, recompute, o);
+    dist += __shfl_xor_sync(0xffffffffu, dist, o);
+  }
+  if (lane == 0) {
+    atomicAdd((unsigned long long *)&stats[0], (unsigned long long)reuse);
+    atomicAdd((unsigned long long *)&stats[1], (unsigned long long)recompute);
+    atomicAdd((unsigned long long *)&stats[2], (unsigned long long)dist);
+  }
+  if (tid == 0) plan_off[nb] = used;
+}
+
+struct Layout {
+  int64_t off[16];
+  int64_t total;
+};
+
+static Layout layout(int64_t n_edges, int32_t bs, int32_t k, int64_t n_nodes, int32_t budget) {
+  Layout L;
+  const int64_t cap = cand_cap(bs, k, budget), words = words_of(n_nodes);
+  const int64_t sizes[16] = {2 * n_edges * 4,   2 * n_edges * k * 4, n_nodes * 4, n_nodes * 4, n_nodes * 4, words * 4,
+                             words * 4,         cap * 4,             cap * 8,     cap * 8,     cap * 8,     cap * 4,
+                             cap * 4,           cap * 4,             2 * cap * 4, 0};
+  int64_t at = 0;
+  for (int i = 0; i < 16; ++i) {
+    L.off[i] = at;
+    at += (sizes[i] + 255) & ~255ll;
+  }
+  L.total = at;
+  return L;
+}
+
+}  // namespace mrd
+}  // namespace orca
+
+using namespace orca;
+
+extern "C" int64_t orca_plan_mrd_workspace_bytes(int64_t n_edges, int32_t bs, int32_t k, int64_t n_nodes,
+                                                 int32_t budget) {
+  if (n_edges < 0 || bs <= 0 || k < 1 || n_nodes <= 0 || budget <= 0) return -1;
+  return mrd::layout(n_edges, bs, k, n_nodes, budget).total;
+}
+
+extern "C" int orca_plan_mrd(const int32_t *d_nodes, int64_t n_edges, int32_t bs, int32_t k, const int32_t *d_nbr,
+                             int64_t n_nodes, int32_t budget, int32_t *d_plan_flat, int64_t plan_cap,
+                             int64_t *d_plan_off, int64_t *d_stats, int32_t *d_status, void *d_workspace,
+                             int64_t workspace_bytes, void *stream) {
+  ORCA_CHECK_ARG(d_nodes && d_nbr && d_plan_flat && d_plan_off && d_stats && d_status && d_workspace);
+  ORCA_CHECK_ARG(n_edges >= 0 && bs > 0 && k >= 1 && k <= ORCA_MAX_K && n_nodes > 0 && budget > 0);
+  ORCA_CHECK_ARG(n_nodes < (1ll << 31) && (n_edges + bs - 1) / bs < (1ll << 29));
+  ORCA_CHECK_ARG(mrd::cand_cap(bs, k, budget) < (1ll << 31));
+  const mrd::Layout L = mrd::layout(n_edges, bs, k, n_nodes, budget);
+  if (workspace_bytes < L.total)
+    return set_error(ORCA_E_CAPACITY, "orca_plan_mrd: workspace of %lld bytes, %lld needed", (long long)workspace_bytes,
+                     (long long)L.total);
+  ORCA_CHECK_ARG(((uintptr_t)d_workspace & 255) == 0);
+  char *base = (char *)d_workspace;
+  mrd::Work w;
+  w.nx_query = (int32_t *)(base + L.off[0]);
+  w.nx_table = (int32_t *)(base + L.off[1]);
+  w.code = (int32_t *)(base + L.off[2]);
+  w.stamp = (int32_t *)(base + L.off[3]);
+  w.since = (int32_t *)(base + L.off[4]);
+  w.cached = (uint32_t *)(base + L.off[5]);
+  w.fresh = (uint32_t *)(base + L.off[6]);
+  w.cand = (int32_t *)(base + L.off[7]);
+  w.e = (uint64_t *)(base + L.off[8]);
+  w.seg = (int2 *)(base + L.off[9]);
+  w.pre = (int2 *)(base + L.off[10]);
+  w.lpos = (int32_t *)(base + L.off[11]);
+  w.rpos = (int32_t *)(base + L.off[12]);
+  w.pivot = (int32_t *)(base + L.off[13]);
+  w.swaps = (int32_t *)(base + L.off[14]);
+  cudaStream_t s = (cudaStream_t)stream;
+  ORCA_CUDA(cudaMemsetAsync(d_stats, 0, 3 * sizeof(int64_t), s));
+  if (n_edges == 0) {
+    ORCA_CUDA(cudaMemsetAsync(d_plan_off, 0, sizeof(int64_t), s));
+    return ORCA_OK;
+  }
+  mrd::next_use_kernel<<<1, mrd::T, 0, s>>>(d_nodes, d_nbr, n_edges, bs, k, n_nodes, w);
+  ORCA_COUNT_LAUNCH();
+  ORCA_LAUNCH_CHECK();
+  mrd::mrd_kernel<<<1, mrd::T, 0, s>>>(d_nodes, d_nbr, n_edges, bs, k, n_nodes, budget, w, d_plan_flat, plan_cap,
+                                       d_plan_off, d_stats, d_status);
+  ORCA_COUNT_LAUNCH();
+  ORCA_LAUNCH_CHECK();
+  return ORCA_OK;
+}

@@ -35,6 +35,15 @@ def _worker(rank, world, port, case, out_dir):
         plan = unpack(gold[f"plan_{spec.strategy}_flat"], gold[f"plan_{spec.strategy}_off"])
         tgn = make_model(g, device=f"cuda:{rank}")
         tgn.set_distributed(rank, world)
+        # planned once on rank 0 by the product planner, received by broadcast on the other rank
+        import argparse
+        from orca_b200.cache import get_cache_plan
+        ns = argparse.Namespace(bs=spec.bs, n_degree=spec.n_degree, budget=spec.budget)
+        shared = get_cache_plan(ns, g, tgn.embedding_module.neighbor_finder, g.n_nodes, spec.strategy,
+                                broadcast_from=0)
+        assert len(shared) == len(plan)
+        for a, w in zip(shared, plan):
+            assert np.array_equal(a, w)
         neg, scores = gold["neg"], gold["scores"]
         got = []
         worst = 0.0
