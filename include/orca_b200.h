@@ -110,6 +110,18 @@ int orca_csr_build_host(const int64_t *h_src, const int64_t *h_dst, const int64_
                         const double *h_ts, int64_t n_edges, int64_t n_nodes, int64_t *h_indptr,
                         int32_t *h_nbr, int32_t *h_eid, double *h_adj_ts);
 
+/* The same adjacency built on the device from device arrays: a stable radix sort of the 2*n_edges
+ * records by (node, timestamp), least significant byte first (8 passes over the timestamp's bytes, then
+ * the bytes of the node id), so any stream order and any ties come out as the reference's stable sort
+ * leaves them.  Outputs are device arrays of the sizes above; ids outside [0, n_nodes) are reported in
+ * d_status (ORCA_E_BOUNDS).  Enqueues on `stream`; the workspace (256-byte aligned) is sized by
+ * orca_csr_build_workspace_bytes. */
+int64_t orca_csr_build_workspace_bytes(int64_t n_edges, int64_t n_nodes);
+int orca_csr_build(const int64_t *d_src, const int64_t *d_dst, const int64_t *d_eidx, const double *d_ts,
+                   int64_t n_edges, int64_t n_nodes, int64_t *d_indptr, int32_t *d_nbr, int32_t *d_eid,
+                   double *d_adj_ts, int32_t *d_status, void *d_workspace, int64_t workspace_bytes,
+                   void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * Temporal neighbour sampling.  Replaces NeighborFinder.get_temporal_neighbor and find_before
  * (utils/util.py:129-151): per query the interactions strictly before the query time, the last k

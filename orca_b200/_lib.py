@@ -110,6 +110,8 @@ SYMBOLS = {
     "orca_gru_scratch_bytes": (_I64, [_I32]),
     "orca_gru_update_static": (C.c_int, [C.POINTER(GruWeights), C.POINTER(MemoryT), _V, _I32, _V, _I32, _V]),
     "orca_plan_host": (C.c_int, [_I32, _V, _V, _I64, _I32, _I32, _V, _I64, _I32, C.c_uint32, _V, _I64, _V, _V]),
+    "orca_csr_build_workspace_bytes": (_I64, [_I64, _I64]),
+    "orca_csr_build": (C.c_int, [_V, _V, _V, _V, _I64, _I64, _V, _V, _V, _V, _V, _V, _I64, _V]),
     "orca_plan_mrd_workspace_bytes": (_I64, [_I64, _I32, _I32, _I64, _I32]),
     "orca_plan_mrd": (C.c_int, [_V, _I64, _I32, _I32, _V, _I64, _I32, _V, _I64, _V, _V, _V, _V, _I64, _V]),
     "orca_eval_workspace_bytes": (_I64, [_I32, _I32, _I32, _I64]),

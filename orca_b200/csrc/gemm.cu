@@ -500,7 +500,12 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
   }
   if (projection_mode() == 0) {
     // (the tensor-core kernel zeroes the whole first source of an invalid row: zero_cols == its width)
-    ORCA_CHECK_ARG(w->G_tc && w->W2t_tc && d_scratch_hidden);
+    ORCA_CHECK_ARG(w->G_tc && w->W2t_tc);
+    // One kernel: relu([ctx | feat] . G + b1 + valid * g) stays on the SM as the A operand of the second
+    // product (. W2t + b2), whose epilogue is the LayerNorm with the history push.  (The hidden tile never
+    // goes to HBM; d_scratch_hidden is not used in this mode.)
+    (void)rows_hint;
+    (void)d_scratch_hidden;
     tc::Args a{};
     a.a0 = tc::RowSrc{d_ctx, nullptr, QT, 0, 0};
     a.a1 = tc::RowSrc{d_feat, d_idx, D, 0, 0};
@@ -513,34 +518,19 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
     a.d_m = d_n_rows;
     a.bias = w->b1;
     a.bias2 = w->g;
-    a.out = d_scratch_hidden;
-    // (19 k-blocks per row block and only ~47-61 row blocks per batch: the projection runs as two tiles of 96
-    // columns -- G is packed for that width -- so that twice as many SMs take part, each with half the tensor
-    // time and half the weight bytes per k-block.  Splitting K over a cluster of 3 CTAs instead was measured
-    // slower and removed: the clusters do not all fit at once and the summing pass over distributed shared
-    // memory takes 5 us.)
-    (void)rows_hint;
-    int rc = tc::launch(tc::EPI_HIDDEN2, a, 2, (cudaStream_t)stream);
-    if (rc) return rc;
-    tc::Args b{};
-    b.a0 = tc::RowSrc{d_scratch_hidden, nullptr, D, 0, 0};
-    b.Kd = D;
-    b.w_packed = w->W2t_tc;
-    b.n_kblocks = kblocks(D);
-    b.m_cap = n_rows_cap;
-    b.d_m = d_n_rows;
-    b.bias = w->b2;
-    b.ln_w = w->ln_w;
-    b.ln_b = w->ln_b;
-    b.out = d_out;
-    b.push_table = d_push_table;
-    b.push_ids = d_push_ids;
-    b.push_win = d_last_pos ? nullptr : d_push_win;
-    b.push_last_pos = reinterpret_cast<const unsigned long long *>(d_last_pos);
-    b.push_base = base;
-    b.push_all_from = all_from;
-    if (peer != nullptr) b.peer = *peer;
-    return tc::launch(tc::EPI_LAYERNORM, b, 1, (cudaStream_t)stream);
+    a.w2_packed = w->W2t_tc;
+    a.bias_out = w->b2;
+    a.ln_w = w->ln_w;
+    a.ln_b = w->ln_b;
+    a.out = d_out;
+    a.push_table = d_push_table;
+    a.push_ids = d_push_ids;
+    a.push_win = d_last_pos ? nullptr : d_push_win;
+    a.push_last_pos = reinterpret_cast<const unsigned long long *>(d_last_pos);
+    a.push_base = base;
+    a.push_all_from = all_from;
+    if (peer != nullptr) a.peer = *peer;
+    return tc::launch(tc::EPI_MERGER, a, 1, (cudaStream_t)stream);
   }
   int rc = ensure_f2_smem();
   if (rc) return rc;

@@ -197,10 +197,8 @@ __device__ __align__(16) float g_zero16[4] = {0.f, 0.f, 0.f, 0.f};
 // memory, lanes along the columns (two 16-byte pieces per lane); four rows are in flight per warp so
 // that their load / shuffle / store chains overlap.  meta_a / meta_b: lane i of warp w holds the
 // per-row inputs of row w + 10*i (validity, push winner and id, GRU node).
-// columns of a tile: the hidden projection of the merger may run as two tiles of 96 columns (EPI_HIDDEN2),
-// which halves the tensor time and the weight bytes per CTA and doubles the CTAs
 template <int EPI>
-constexpr int tile_bn() { return EPI == EPI_HIDDEN2 ? 96 : BN; }
+constexpr int tile_bn() { return BN; }
 
 template <int EPI>
 __device__ __forceinline__ void tile_output(const Args &g, const float *tile, const float *s_bias, const float *s_v1,
@@ -213,10 +211,10 @@ __device__ __forceinline__ void tile_output(const Args &g, const float *tile, co
   }
   constexpr int RB = 4;   // (2 measured the same, 8 spills)
   constexpr int BNv = tile_bn<EPI>();
-  constexpr bool kHidden = EPI == EPI_HIDDEN || EPI == EPI_HIDDEN2;
+  constexpr bool kHidden = EPI == EPI_HIDDEN;
   const int c0 = nt * BNv;
   const int j0 = lane, j1 = lane + 32;
-  const int nj = (EPI == EPI_BIAS || EPI == EPI_GRU) ? BNv / 4 : (EPI == EPI_HIDDEN2 ? min(BNv, D - c0) / 4 : D / 4);
+  const int nj = (EPI == EPI_BIAS || EPI == EPI_GRU) ? BNv / 4 : D / 4;
   const bool has0 = j0 < nj;      // (only a 96-column tile leaves lanes without a first piece)
   const bool has1 = j1 < nj;
   const float4 f4z = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -351,6 +349,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   const int rsub = lane >> 3, f = lane & 7;
   const int w0 = g.a0.width, w1 = g.a1.width, Kd = g.Kd;
   constexpr int BNv = tile_bn<EPI>();
+  constexpr bool kMerger = EPI == EPI_MERGER;
   constexpr uint32_t BvLBO = BNv * 16, BvBYTES = CHUNKS * BvLBO;   // weight images of this tile width
   const int rstride = g.row_stride > 1 ? g.row_stride : 1;
   const int nkb = g.n_kblocks;
@@ -363,9 +362,14 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   // w + 10*i needs).  For the CTA's first tile they are issued before the live row count is known (rows
   // up to m_cap: the arrays are sized for it) and discarded afterwards if the row is not live.
   int ri0 = -1, ri1 = -1, meta_a = 0, meta_b = 0;
+  float row_on = 0.f;   // merger: validity of the accumulator row this thread moves in the first epilogue
   auto prefetch_rows = [&](int m0, int limit) {
     ri0 = ri1 = -1;
     meta_a = meta_b = 0;
+    if (kMerger && producer) {
+      const int m = m0 + (warp & 3) * 32 + lane;
+      row_on = (m < limit && (g.row_valid == nullptr || g.row_valid[m] != 0)) ? 1.f : 0.f;
+    }
     if (producer) {
       const int m = m0 + pw * 32 + lane;
       if (m < limit) {
@@ -381,8 +385,8 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     const int r = warp + (THREADS / 32) * lane;
     const int m = m0 + r;
     if (r < BM && m < limit) {
-      if (EPI == EPI_HIDDEN || EPI == EPI_HIDDEN2) meta_a = g.row_valid == nullptr ? 1 : g.row_valid[m];
-      if (EPI == EPI_LAYERNORM && g.push_table != nullptr) {
+      if (EPI == EPI_HIDDEN) meta_a = g.row_valid == nullptr ? 1 : g.row_valid[m];
+      if ((EPI == EPI_LAYERNORM || kMerger) && g.push_table != nullptr) {
         meta_b = g.push_ids[m];
         if (g.push_win != nullptr) meta_a = g.push_win[m];
       }
@@ -393,11 +397,14 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   const uint32_t raw_addr = smem_addr(raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   const Smem sm{base};
-  const uint32_t bar_base = base + STAGES * STAGE_BYTES;
+  const uint32_t bar_base = base + (kMerger ? MERGER_RING_BYTES : STAGES * STAGE_BYTES);
   auto full = [&](int s) { return bar_base + 8u * s; };
   auto empty = [&](int s) { return bar_base + 64u + 8u * s; };
   const uint32_t accbar = bar_base + 128u;
   const uint32_t slot = bar_base + 136u;
+  // merger only: k-block 0 of the second weights has landed / k-blocks 1 and 2 have landed / the hidden
+  // tile is in shared memory as an A image
+  const uint32_t w2bar0 = bar_base + 144u, w2bar1 = bar_base + 152u, a2bar = bar_base + 160u;
   volatile uint32_t *slot_ptr = reinterpret_cast<volatile uint32_t *>(raw + (slot - raw_addr));
 
   // Producer lane layout inside a stage: 8 lanes cover the 256 contiguous bytes a row contributes
@@ -427,7 +434,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   // (called after the tile's first stage has been requested: the lookup is two dependent loads and its
   // result is only needed by the output pass)
   auto push_winners = [&](int m0) {
-    if (EPI == EPI_LAYERNORM && g.push_table != nullptr && g.push_win == nullptr) {
+    if ((EPI == EPI_LAYERNORM || kMerger) && g.push_table != nullptr && g.push_win == nullptr) {
       // winners by record; only for live rows: the id of a row past the live count is not a valid index
       const int r = warp + (THREADS / 32) * lane;
       const int m = m0 + r;
@@ -442,6 +449,11 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
       mbar_init(empty(s), 1);     // one tcgen05.commit
     }
     mbar_init(accbar, 1);
+    if (kMerger) {
+      mbar_init(w2bar0, 1);
+      mbar_init(w2bar1, 1);
+      mbar_init(a2bar, 8);   // one elected lane per producer warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 5) {
@@ -452,15 +464,21 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   // epilogue vectors of this column tile, staged once (a global load per accumulator chunk would put
   // an L2 round trip into every step of the epilogue)
   __shared__ __align__(16) float s_bias[BN], s_v1[BN], s_v2[BN];
+  __shared__ __align__(16) float s_out[kMerger ? 3 : 1][kMerger ? BN : 4];   // merger: bias, weight, shift of the LayerNorm
   if (warp == 4 || warp == 5) {
     const int lim = (EPI == EPI_BIAS || EPI == EPI_GRU) ? BNv : D - nt * BNv;   // columns of this tile that exist
     for (int i = tid - 128; i < BN; i += 64) {
       const bool in = i < lim && i < BNv;
       s_bias[i] = in ? g.bias[nt * BNv + i] : 0.f;
-      const float *v1 = (EPI == EPI_HIDDEN || EPI == EPI_HIDDEN2) ? g.bias2
+      const float *v1 = (EPI == EPI_HIDDEN || kMerger) ? g.bias2
                         : EPI == EPI_LAYERNORM ? g.ln_w : EPI == EPI_SCORE ? g.w2 : nullptr;
       s_v1[i] = (v1 != nullptr && in) ? v1[nt * BNv + i] : 0.f;
       s_v2[i] = (EPI == EPI_LAYERNORM && in) ? g.ln_b[i] : 0.f;
+      if (kMerger) {
+        s_out[0][i] = in ? g.bias_out[i] : 0.f;
+        s_out[1][i] = in ? g.ln_w[i] : 0.f;
+        s_out[2][i] = in ? g.ln_b[i] : 0.f;
+      }
     }
   }
   // ---- everything below may read what the previous kernels of the stream produced
@@ -520,12 +538,27 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
       if (lane == 0) {
         const char *wsrc = reinterpret_cast<const char *>(g.w_packed) +
                            (size_t)nt * g.n_kblocks * (2 * BvBYTES);
+        // second weights of the merger: k-block 0 once per CTA (its place lies past the stage ring), k-blocks
+        // 1 and 2 into the ring as soon as the first product has finished reading it
+        const char *w2 = reinterpret_cast<const char *>(g.w2_packed);
+        if (kMerger && t == 0) {
+          mbar_expect_tx(w2bar0, 2 * B_BYTES);
+          bulk_g2s(base + W2_KB0, w2, 2 * B_BYTES, w2bar0);
+        }
         for (int kb = 0; kb < nkb; ++kb) {
           const int s = kb & 1;
           const int u = t * (s ? uses1 : uses0) + (kb >> 1);
           mbar_wait(empty(s), (u & 1) ^ 1, g.status, 200 + s, alive, g.wait_limit);
           mbar_expect_tx(full(s), 2 * BvBYTES);
           bulk_g2s(sm.b_hi(s), wsrc + (size_t)kb * (2 * BvBYTES), 2 * BvBYTES, full(s));
+        }
+        if (kMerger) {
+          mbar_wait(accbar, 0, g.status, 210, alive, g.wait_limit);
+          constexpr uint32_t kTail = W2_TAIL_CHUNKS * B_LBO;
+          mbar_expect_tx(w2bar1, 2 * B_BYTES + 2 * kTail);
+          bulk_g2s(base + W2_KB1, w2 + 2 * B_BYTES, 2 * B_BYTES, w2bar1);
+          bulk_g2s(base + W2_KB2, w2 + 4 * B_BYTES, kTail, w2bar1);
+          bulk_g2s(base + W2_KB2 + kTail, w2 + 5 * B_BYTES, kTail, w2bar1);
         }
       }
       __syncwarp();
@@ -555,6 +588,31 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
           mma_commit(empty(s));  // the stage may be refilled once these MMAs have read it
         }
         mma_commit(accbar);
+        if (kMerger) {
+          // second product: hidden tile (A image written by the first epilogue) x second weights, into the
+          // same accumulator columns (the first epilogue has read them when a2bar completes)
+          mbar_wait(a2bar, t & 1, g.status, 310, alive, g.wait_limit);
+          mbar_wait(w2bar0, 0, g.status, 311, alive, g.wait_limit);
+          tc_fence_after();
+          for (int ks = 0; ks < A2_CHUNKS / 2; ++ks) {
+            if (ks == BK / 16) {
+              mbar_wait(w2bar1, t & 1, g.status, 312, alive, g.wait_limit);
+              tc_fence_after();
+            }
+            const int kb = ks / (BK / 16), kk = ks % (BK / 16);
+            const uint32_t wb = base + (kb == 0 ? W2_KB0 : kb == 1 ? W2_KB1 : W2_KB2) + kk * 2 * B_LBO;
+            const uint32_t wtail = kb == 2 ? W2_TAIL_CHUNKS * B_LBO : B_BYTES;
+            const uint64_t ah = make_desc(base + ks * 2 * A_LBO, A_LBO, A_SBO);
+            const uint64_t al = make_desc(base + A2_BYTES + ks * 2 * A_LBO, A_LBO, A_SBO);
+            const uint64_t bh = make_desc(wb, B_LBO, B_SBO);
+            const uint64_t bl = make_desc(wb + wtail, B_LBO, B_SBO);
+            const uint32_t first = ks > 0 ? 1u : 0u;
+            mma_bf16(tmem, ah, bh, idesc, first);
+            mma_bf16(tmem + TMEM_SMALL, al, bh, idesc, first);
+            mma_bf16(tmem + TMEM_SMALL, ah, bl, idesc, 1u);
+          }
+          mma_commit(accbar);
+        }
       }
       __syncwarp();
     }
@@ -566,11 +624,37 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     // idle stage ring, so that pass 2 can write whole rows with coalesced stores.
     const int m_rows = min(BM, M - m0);
     if (producer) {
-      mbar_wait(accbar, t & 1, g.status, 400, alive, g.wait_limit);
-      tc_fence_after();
       const int quarter = warp & 3;
       const int row = quarter * 32 + lane;
       const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
+      if (kMerger) {
+        // first epilogue: hidden = relu(acc + bias + valid * bias2), split into bf16 head / tail and stored
+        // as the A image of the second product (thread = row: chunk c of the row is 16 bytes at c * A_LBO)
+        mbar_wait(accbar, 0, g.status, 401, alive, g.wait_limit);
+        tc_fence_after();
+        constexpr int kHalf = (BN / 16 + 1) / 2;
+        const uint32_t arow = base + (uint32_t)row * 16u;
+        for (int ch = grp ? kHalf : 0; ch < (grp ? BN / 16 : kHalf); ++ch) {
+          float v[16];
+          tmem_ld16_sum(trow + ch * 16, v);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i] + s_bias[ch * 16 + i] + row_on * s_v1[ch * 16 + i], 0.f);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint4 hi, lo;
+            split_chunk(make_float4(v[8 * h], v[8 * h + 1], v[8 * h + 2], v[8 * h + 3]),
+                        make_float4(v[8 * h + 4], v[8 * h + 5], v[8 * h + 6], v[8 * h + 7]), hi, lo);
+            st_shared_v4(arow + (uint32_t)(2 * ch + h) * A_LBO, hi);
+            st_shared_v4(arow + A2_BYTES + (uint32_t)(2 * ch + h) * A_LBO, lo);
+          }
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a2bar);
+      }
+      mbar_wait(accbar, kMerger ? 1 : (t & 1), g.status, 400, alive, g.wait_limit);
+      tc_fence_after();
       const uint32_t trow_sa = base + (uint32_t)(row * TILE_LD) * 4u;   // the tile starts at the stage ring
       float dot = 0.f;
       constexpr int kSplit = (BNv / 16 + 1) / 2;   // accumulator chunks of 16 columns: first half / second half
@@ -596,7 +680,11 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    tile_output<EPI>(g, tile, s_bias, s_v1, s_v2, &s_dot[0][0], m0, m_rows, nt, warp, lane, meta_a, meta_b);
+    if constexpr (kMerger)
+      tile_output<EPI_LAYERNORM>(g, tile, s_out[0], s_out[1], s_out[2], &s_dot[0][0], m0, m_rows, nt, warp, lane,
+                                 meta_a, meta_b);
+    else
+      tile_output<EPI>(g, tile, s_bias, s_v1, s_v2, &s_dot[0][0], m0, m_rows, nt, warp, lane, meta_a, meta_b);
     // the tile lives in the stage ring: the next row block's bulk copies and stores may only land
     // once every warp has read it
     fence_async_smem();
@@ -606,7 +694,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
   }
-  if ((EPI == EPI_LAYERNORM || EPI == EPI_GRU) && g.peer.world > 0) {
+  if ((EPI == EPI_LAYERNORM || EPI == EPI_GRU || kMerger) && g.peer.world > 0) {
     // every CTA (with or without rows) checks out; the last one posts the batch's sequence number to all
     // ranks, after every CTA's peer stores have been fenced system-wide
     __threadfence_system();
@@ -631,11 +719,10 @@ int launch(int epilogue, const Args &a, int n_tiles, cudaStream_t stream) {
   static thread_local int configured_device = -1;
   if (configured_device != c->device) {
     ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_HIDDEN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_LAYERNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_GRU>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_SCORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_HIDDEN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    ORCA_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<EPI_MERGER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   MERGER_SMEM_BYTES));
     configured_device = c->device;
   }
   Args b = a;
@@ -646,11 +733,11 @@ int launch(int epilogue, const Args &a, int n_tiles, cudaStream_t stream) {
   dim3 grid(n_tiles, std::min(ceil_div(a.m_cap, BM), std::max(1, c->sm_count / n_tiles)), 1);
   switch (epilogue) {
     case EPI_BIAS: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_BIAS>, grid, THREADS, SMEM_BYTES, stream, b)); break;
-    case EPI_HIDDEN: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_HIDDEN>, grid, THREADS, SMEM_BYTES, stream, b)); break;
-    case EPI_LAYERNORM: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_LAYERNORM>, grid, THREADS, SMEM_BYTES, stream, b)); break;
     case EPI_GRU: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_GRU>, grid, THREADS, SMEM_BYTES, stream, b)); break;
     case EPI_SCORE: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_SCORE>, grid, THREADS, SMEM_BYTES, stream, b)); break;
-    case EPI_HIDDEN2: ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_HIDDEN2>, grid, THREADS, SMEM_BYTES, stream, b)); break;
+    case EPI_MERGER:
+      ORCA_CUDA(launch_dep(tc_gemm_kernel<EPI_MERGER>, grid, THREADS, MERGER_SMEM_BYTES, stream, b));
+      break;
     default: return set_error(ORCA_E_BADARG, "tc::launch: unknown epilogue %d", epilogue);
   }
   ORCA_COUNT_LAUNCH();

@@ -20,6 +20,19 @@ constexpr int B_SBO = 128;
 constexpr int B_BYTES = CHUNKS * B_LBO;
 constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;   // A head, A tail, W head, W tail
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+// The merger kernel (EPI_MERGER) runs a second product from shared memory once the first is done: the
+// hidden tile as an A image of 22 chunks (176 columns) head + tail at the start of the ring, and the
+// three k-blocks of the second weight matrix behind it (the third holds only 6 chunks); k-block 0 sits past
+// the ring, so that it can be fetched while the first product still uses the stages.
+constexpr int A2_CHUNKS = BN / 8;
+constexpr int A2_BYTES = A2_CHUNKS * A_LBO;
+constexpr int W2_KB1 = 2 * A2_BYTES;
+constexpr int W2_KB2 = W2_KB1 + 2 * B_BYTES;
+constexpr int W2_TAIL_CHUNKS = A2_CHUNKS - 2 * CHUNKS;   // chunks of the last k-block that are used
+constexpr int W2_KB0 = W2_KB2 + 2 * W2_TAIL_CHUNKS * B_LBO;
+constexpr int MERGER_RING_BYTES = W2_KB0 + 2 * B_BYTES;
+constexpr int MERGER_SMEM_BYTES = MERGER_RING_BYTES + 1024 + 256;
+static_assert(W2_KB0 >= STAGES * STAGE_BYTES, "k-block 0 of the second weights must lie past the stage ring");
 constexpr int TMEM_COLS = 512;   // main accumulator at column 0, cross-term accumulator at column 256
 constexpr int TMEM_SMALL = 256;
 constexpr int TILE_LD = 180;     // floats per row of the epilogue's output tile: 16-byte row-wise stores of a
@@ -46,8 +59,10 @@ struct PeerOut {
   int world, rank, seq;
 };
 
-// (EPI_HIDDEN2: the HIDDEN epilogue on tiles of 96 columns, weights packed for that width)
-enum Epilogue { EPI_BIAS = 0, EPI_HIDDEN = 1, EPI_LAYERNORM = 2, EPI_GRU = 3, EPI_SCORE = 4, EPI_HIDDEN2 = 5 };
+// EPI_MERGER: hidden = relu(A . W + bias + valid * bias2) kept on the SM, then LayerNorm(hidden . W2 + bias_out)
+// with the LAYERNORM epilogue (push, peer fan-out).  EPI_HIDDEN / EPI_LAYERNORM name the two halves (the
+// epilogue code is shared); only the merger is launched.
+enum Epilogue { EPI_BIAS = 0, EPI_HIDDEN = 1, EPI_LAYERNORM = 2, EPI_GRU = 3, EPI_SCORE = 4, EPI_MERGER = 5 };
 
 struct Args {
   RowSrc a0, a1;             // a1.width == 0 when unused
@@ -64,8 +79,10 @@ struct Args {
   const float *bias;         // [n_tiles * BN]
   float *out;                // BIAS: [m, out_ld]; HIDDEN / LAYERNORM: [m, 172]; GRU: [m, 172]; SCORE: [m]
   int out_ld;
-  // HIDDEN: + valid * bias2
+  // MERGER, first product: + valid * bias2; second product: packed weights (3 k-blocks) and bias
   const float *bias2;
+  const void *w2_packed;
+  const float *bias_out;
   // LAYERNORM
   const float *ln_w, *ln_b;
   float *push_table;

@@ -3,8 +3,8 @@
 ``NeighborFinder.get_temporal_neighbor`` keep their names, argument meaning and return dtypes.
 
 The per-node Python lists of the reference become one time-sorted CSR (indptr int64, neighbour
-int32, edge id int32, timestamp float64) resident in HBM; a host copy is kept for ``find_before``,
-which returns array slices.
+int32, edge id int32, timestamp float64) resident in HBM, built there by ``orca_csr_build``;
+``find_before`` copies the slice it returns to the host.
 """
 from __future__ import annotations
 
@@ -34,16 +34,38 @@ class NeighborFinder:
     def _init_csr(self, indptr, nbr, eid, ts, device):
         self.device = _lib.require_cuda(device)
         self.n_nodes = len(indptr) - 1
-        self.h_indptr = np.ascontiguousarray(indptr, dtype=np.int64)
-        self.h_nbr = np.ascontiguousarray(nbr, dtype=np.int32)
-        self.h_eid = np.ascontiguousarray(eid, dtype=np.int32)
-        self.h_ts = np.ascontiguousarray(ts, dtype=np.float64)
-        self.indptr = torch.from_numpy(self.h_indptr).to(self.device)
+        self.indptr = torch.from_numpy(np.ascontiguousarray(indptr, dtype=np.int64)).to(self.device)
         # one spare element keeps the pointers valid for an empty graph
-        pad = lambda a: a if len(a) else np.zeros(1, dtype=a.dtype)
-        self.adj_nbr = torch.from_numpy(pad(self.h_nbr)).to(self.device)
-        self.adj_eid = torch.from_numpy(pad(self.h_eid)).to(self.device)
-        self.adj_ts = torch.from_numpy(pad(self.h_ts)).to(self.device)
+        pad = lambda a, dt: np.ascontiguousarray(a, dtype=dt) if len(a) else np.zeros(1, dtype=dt)
+        self.adj_nbr = torch.from_numpy(pad(nbr, np.int32)).to(self.device)
+        self.adj_eid = torch.from_numpy(pad(eid, np.int32)).to(self.device)
+        self.adj_ts = torch.from_numpy(pad(ts, np.float64)).to(self.device)
+
+    @classmethod
+    def build_on_device(cls, sources, destinations, edge_idxs, timestamps, n_nodes, device="cuda"):
+        """The adjacency of an edge stream, sorted on the GPU (utils/util.py:91-105)."""
+        self = cls.__new__(cls)
+        self.device = dev = _lib.require_cuda(device)
+        self.n_nodes = int(n_nodes)
+        E = len(sources)
+        up = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a, dtype=dt)).to(dev)
+        src, dst, eidx = (up(a, np.int64) for a in (sources, destinations, edge_idxs))
+        ts = up(timestamps, np.float64)
+        L = _lib.lib()
+        with torch.cuda.device(dev):
+            self.indptr = torch.empty(self.n_nodes + 1, dtype=torch.int64, device=dev)
+            self.adj_nbr = torch.zeros(max(2 * E, 1), dtype=torch.int32, device=dev)
+            self.adj_eid = torch.zeros(max(2 * E, 1), dtype=torch.int32, device=dev)
+            self.adj_ts = torch.zeros(max(2 * E, 1), dtype=torch.float64, device=dev)
+            ws_bytes = L.orca_csr_build_workspace_bytes(E, self.n_nodes)
+            ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+            status = torch.zeros(4, dtype=torch.int32, device=dev)
+            _lib.check(L.orca_csr_build(src.data_ptr(), dst.data_ptr(), eidx.data_ptr(), ts.data_ptr(), E,
+                                        self.n_nodes, self.indptr.data_ptr(), self.adj_nbr.data_ptr(),
+                                        self.adj_eid.data_ptr(), self.adj_ts.data_ptr(), status.data_ptr(),
+                                        ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)))
+            _lib.check(L.orca_read_status(None, status.data_ptr(), None, _lib.stream_ptr(dev)))
+        return self
 
     # --- utils/util.py:129-131
     def find_before(self, src_idx, cut_time):
@@ -55,8 +77,9 @@ class NeighborFinder:
                                       node.data_ptr(), t.data_ptr(), 1, cnt.data_ptr(),
                                       _lib.stream_ptr(self.device)))
         i = int(cnt.item())
-        b = int(self.h_indptr[int(src_idx)])
-        return self.h_nbr[b:b + i], self.h_eid[b:b + i], self.h_ts[b:b + i]
+        b = int(self.indptr[int(src_idx)].item())
+        return (self.adj_nbr[b:b + i].cpu().numpy(), self.adj_eid[b:b + i].cpu().numpy(),
+                self.adj_ts[b:b + i].cpu().numpy())
 
     # --- utils/util.py:134-151
     def get_temporal_neighbor(self, source_nodes, timestamps, n_neighbors):
@@ -94,19 +117,8 @@ class NeighborFinder:
 def get_neighbor_finder(data, max_node_idx=None, device="cuda"):
     """utils/util.py:91-105: every interaction is listed under both endpoints, each node's list
     stably sorted by time.  `data` needs .sources, .destinations, .edge_idxs, .timestamps."""
-    src = np.ascontiguousarray(data.sources, dtype=np.int64)
-    dst = np.ascontiguousarray(data.destinations, dtype=np.int64)
-    eidx = np.ascontiguousarray(data.edge_idxs, dtype=np.int64)
-    ts = np.ascontiguousarray(data.timestamps, dtype=np.float64)
+    src, dst = np.asarray(data.sources), np.asarray(data.destinations)
     if max_node_idx is None:
         max_node_idx = int(max(src.max(), dst.max())) if len(src) else 0
-    n = int(max_node_idx) + 1
-    E = len(src)
-    indptr = np.empty(n + 1, dtype=np.int64)
-    nbr = np.empty(max(2 * E, 1), dtype=np.int32)
-    eid = np.empty(max(2 * E, 1), dtype=np.int32)
-    ats = np.empty(max(2 * E, 1), dtype=np.float64)
-    _lib.check(_lib.lib().orca_csr_build_host(src.ctypes.data, dst.ctypes.data, eidx.ctypes.data, ts.ctypes.data,
-                                              E, n, indptr.ctypes.data, nbr.ctypes.data, eid.ctypes.data,
-                                              ats.ctypes.data))
-    return NeighborFinder.from_csr(indptr, nbr[:2 * E], eid[:2 * E], ats[:2 * E], device=device)
+    return NeighborFinder.build_on_device(src, dst, data.edge_idxs, data.timestamps, int(max_node_idx) + 1,
+                                          device=device)

@@ -194,6 +194,9 @@ class TGN(nn.Module):
         self._ws_key = None
         self._stage = _Staging()
         self._copy_stream = None       # created with the device ring on the first batch
+        self._status_host = None       # pinned copy of the status word, refreshed after every batch
+        self._status_event = None
+        self._status_pending = False
         self._status = torch.zeros(4, dtype=torch.int32, device=self.device)
         # last-occurrence records: push winners of even / odd batches, message winners
         self._last_pos = torch.zeros(3 * self.n_nodes, dtype=torch.int64, device=self.device)
@@ -509,6 +512,25 @@ class TGN(nn.Module):
         if ev is None:
             ev = self._ev_free[ds] = torch.cuda.Event()
         ev.record(stream)
+        # The status word follows the batch to pinned host memory without a synchronisation; the next call
+        # that finds the copy complete raises what the kernels reported (_raise_reported).
+        if self._status_host is None:
+            self._status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+            self._status_event = torch.cuda.Event()
+        self._status_host.copy_(self._status, non_blocking=True)
+        self._status_event.record(stream)
+        self._status_pending = True
+
+    def _raise_reported(self):
+        """Raises the device-side error of an earlier batch once its status copy has landed (capacity of the
+        uncached set, ids outside a table, a bounded wait that gave up): the reference API has no status
+        call, so the error surfaces at the start of a later call instead of being dropped."""
+        if self._status_pending and self._status_event.query():
+            self._status_pending = False
+            code = int(self._status_host[0])
+            if code != 0:
+                raise _lib.OrcaError(code, f"a kernel of an earlier batch reported error {code} "
+                                           f"(detail {int(self._status_host[3])}); results since then are invalid")
 
     def _eval_batch_sharded(self, desc, d_i32, d_ts, b, d_plan, n_plan, u_cap, ws, want_emb):
         if self.n_layers != 2:
@@ -543,12 +565,14 @@ class TGN(nn.Module):
         """Synchronises and raises if a kernel reported an error since the last check; returns
         (rows at layer 1, unique positives, kernel launches) of the last batch."""
         h = np.zeros(4, dtype=np.int32)
+        self._status_pending = False       # (this call reads, reports and clears the word itself)
         _lib.check(_lib.lib().orca_read_status(self._ctx, self._status.data_ptr(), h.ctypes.data,
                                                _lib.stream_ptr(self.device)))
         self.last_counts = (int(h[1]), int(h[2]), int(h[3]))
         return self.last_counts
 
     def _enter(self, reuse, train):
+        self._raise_reported()
         if train:
             raise NotImplementedError("the training path (train=True) is not part of this build")
         # model/tgn_model.py:114-120: the call's `reuse` and the budget choose the recursion

@@ -23,7 +23,6 @@ D = 172
 HEADS = 2
 QT_HEAD = 528     # column stride of one head of the projected query (516 used)
 TC_BN, TC_BK = 176, 64
-TC_BN_HIDDEN = 96   # tile width of the merger's hidden projection (two tiles cover its 172 columns)
 
 
 def _bf16_round(x):
@@ -99,7 +98,7 @@ def prepare_attention(sd, layer: int, dim: int = D, heads: int = HEADS):
     }
     out = {k: np.ascontiguousarray(v, dtype=np.float32) for k, v in out.items()}
     for k in ("Mq", "G", "W2t"):
-        out[k + "_tc"] = pack_tc(out[k], bn=TC_BN_HIDDEN if k == "G" else None)
+        out[k + "_tc"] = pack_tc(out[k])
     return out
 
 

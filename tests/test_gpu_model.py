@@ -462,3 +462,28 @@ def test_wait_for_peers_gives_up_and_leaves_the_tables_alone():
     p, q = ok.compute_edge_probabilities(src, dst, np.roll(dst, 3), ts, eidx, k, True, False, plan[0])
     ok.check_status()
     assert torch.isfinite(p).all() and torch.isfinite(q).all()
+
+
+def test_device_side_errors_surface_through_the_reference_api():
+    """The reference API has no status call.  What a kernel reports in the status word (here: the code a kernel
+    writes when the uncached set exceeds its capacity, put there by the host so that no kernel has to fail)
+    travels to pinned host memory behind each batch and is raised by the first later call that finds the copy
+    complete."""
+    from orca_b200 import _lib
+    g = graph("t_nb2")
+    spec = g.spec
+    gold = golden("t_nb2")
+    plan = unpack(gold[f"plan_{spec.strategy}_flat"], gold[f"plan_{spec.strategy}_off"])
+    m = make_model(g)
+    it = iter(batches(g, 3))
+    _, src, dst, ts, eidx = next(it)
+    m.compute_edge_probabilities(src, dst, np.roll(dst, 3), ts, eidx, spec.n_degree, True, False, plan[0])
+    torch.cuda.synchronize()
+    m._status[0] = 4                     # ORCA_E_CAPACITY, as report() would leave it
+    _, src, dst, ts, eidx = next(it)
+    m.compute_edge_probabilities(src, dst, np.roll(dst, 3), ts, eidx, spec.n_degree, True, False, plan[1])
+    torch.cuda.synchronize()
+    _, src, dst, ts, eidx = next(it)
+    with pytest.raises(_lib.OrcaError) as err:
+        m.compute_edge_probabilities(src, dst, np.roll(dst, 3), ts, eidx, spec.n_degree, True, False, plan[2])
+    assert err.value.code == 4
