@@ -517,16 +517,33 @@ __global__ void __launch_bounds__(T, 1) mrd_cluster_kernel(const int32_t *nodes,
       atomicOr(&fresh[v >> 5], 1u << (v & 31));
     }
     cluster_sync();
-    for (int i = gt; i < m2 * k; i += GT) {
-      const int32_t v = tab[i];
-      if (v == 0 || __ldcg(&w.stamp[v]) == (int32_t)b) continue;
-      w.code[v] = nt[i];
-      if ((__ldcg(&w.cached[v >> 5]) >> (v & 31)) & 1u) {
-        ++reuse;
-        dist += b - __ldcg(&w.since[v]);
-      } else {
-        ++recompute;
-        atomicOr(&fresh[v >> 5], 1u << (v & 31));
+    // (four entries at a time: the loads of one step are issued together, not entry after entry)
+    for (int i0 = gt; i0 < m2 * k; i0 += 4 * GT) {
+      int32_t v[4], st[4], sn[4], cd[4];
+      uint32_t cw_[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * GT;
+        v[u] = i < m2 * k ? tab[i] : 0;
+        cd[u] = i < m2 * k ? nt[i] : 0;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        st[u] = v[u] != 0 ? __ldcg(&w.stamp[v[u]]) : (int32_t)b;
+        cw_[u] = v[u] != 0 ? __ldcg(&w.cached[v[u] >> 5]) : 0u;
+        sn[u] = v[u] != 0 ? __ldcg(&w.since[v[u]]) : 0;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (v[u] == 0 || st[u] == (int32_t)b) continue;
+        w.code[v[u]] = cd[u];
+        if ((cw_[u] >> (v[u] & 31)) & 1u) {
+          ++reuse;
+          dist += b - sn[u];
+        } else {
+          ++recompute;
+          atomicOr(&fresh[v[u] >> 5], 1u << (v[u] & 31));
+        }
       }
     }
     cluster_sync();
@@ -561,12 +578,7 @@ __global__ void __launch_bounds__(T, 1) mrd_cluster_kernel(const int32_t *nodes,
       while (bits) {
         const int bit = __ffs(bits) - 1;
         bits &= bits - 1;
-        const int32_t v = (int32_t)(wi * 32 + bit);
-        const int32_t code = __ldcg(&w.code[v]);
-        const int32_t key = (code & 1) ? (code >> 1) - (int32_t)b : FAR_KEY;
-        w.cand[pos] = v;
-        w.e[pos] = ((uint64_t)(uint32_t)key << 32) | (uint32_t)pos;
-        ++pos;
+        w.cand[pos++] = (int32_t)(wi * 32 + bit);   // (keys follow below, one thread per position)
       }
     }
     const int keep = min(n, budget);
@@ -584,6 +596,18 @@ __global__ void __launch_bounds__(T, 1) mrd_cluster_kernel(const int32_t *nodes,
       hi[i] = (i < items && first_pos + 32 * i < n) ? n - 1 : -1;   // hi < 0: no such position
     }
     bool any = live(0, n - 1, keep);
+    cluster_sync();
+    // keys: a word of the bitmaps can hold 32 candidates, so its thread does not chase their codes one after
+    // the other; the owner of each position reads its candidate's code
+#pragma unroll
+    for (int i = 0; i < MAX_ITEMS; ++i) {
+      if (i < items && hi[i] >= 0) {
+        const int pos = first_pos + 32 * i;
+        const int32_t code = __ldcg(&w.code[__ldcg(&w.cand[pos])]);
+        const int32_t key = (code & 1) ? (code >> 1) - (int32_t)b : FAR_KEY;
+        w.e[pos] = ((uint64_t)(uint32_t)key << 32) | (uint32_t)pos;
+      }
+    }
     cluster_sync();
     if (any && gt == 0) park_pivot_cg(w, 0, n - 1);
     cluster_sync();
@@ -795,11 +819,13 @@ extern "C" int orca_plan_mrd(const int32_t *d_nodes, int64_t n_edges, int32_t bs
     ORCA_CUDA(cudaMemsetAsync(d_plan_off, 0, sizeof(int64_t), s));
     return ORCA_OK;
   }
-  // A cluster of 8 (16) CTAs shares every phase when the candidate list fits its threads' registers and
-  // the device can place such a cluster; one CTA does the same work otherwise.
+  // A cluster of 16 (else 8) CTAs shares every phase when the device can place such a cluster and the
+  // candidate list fits its threads' registers (measured at c5: 0.81 s with 16 CTAs, 0.91 s with 8, 2.3 s
+  // with one CTA; a phase costs a cluster barrier of ~600 cycles, an L2 round trip of ~300 per dependent
+  // load and the release of its stores); one CTA does the same work otherwise.
   const int64_t cap = mrd::cand_cap(bs, k, budget);
   int cluster = 0;
-  for (int c : {8, 16}) {
+  for (int c : {16, 8}) {
     if (cluster != 0 || cap > (int64_t)mrd::MAX_ITEMS * mrd::T * c) continue;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(c);

@@ -41,9 +41,10 @@ def test_mrd_plans_match_reference(case):
 
 
 @pytest.mark.parametrize("budget,bs,seed", [(7, 50, 1), (40, 120, 2), (300, 200, 3), (2, 64, 4), (1000, 400, 5),
-                                            (100000, 200, 6)])
+                                            (100000, 200, 6), (200000, 200, 7)])
 def test_mrd_matches_oracle_on_tight_budgets(budget, bs, seed):
-    """Budgets from far below to far above the number of candidates; statistics included."""
+    """Budgets from far below to far above the number of candidates; statistics included.  (The last budget
+    makes the candidate capacity larger than a thread-block cluster takes, so the one-CTA kernels run.)"""
     from oracle import planner
     from orca_b200 import synthetic
     spec = dataclasses.replace(synthetic.SPECS["t_nb2"], n_src=400, n_edges=3000, bs=bs, budget=budget)
