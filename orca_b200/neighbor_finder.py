@@ -48,7 +48,7 @@ class NeighborFinder:
         self.device = dev = _lib.require_cuda(device)
         self.n_nodes = int(n_nodes)
         E = len(sources)
-        up = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a, dtype=dt)).to(dev)
+        up = lambda a, dt: torch.as_tensor(np.array(a, dtype=dt, order="C")).to(dev)     # (a copy: the input may be read-only)
         src, dst, eidx = (up(a, np.int64) for a in (sources, destinations, edge_idxs))
         ts = up(timestamps, np.float64)
         L = _lib.lib()
