@@ -46,21 +46,17 @@ constexpr int GA_WARPS = GA_THREADS / 32;
 //     row ahead commits slow warps to one more row while fast warps run dry (measured: 38 -> 33 us);
 //   - tickets walk the rows in the order of `order` (rows sorted by falling number of valid slots,
 //     made by row_order_kernel beside the sampling), so that the launch ends on its lightest rows.
-// The projected query of the next row (4.2 KB) is staged in shared memory with cp.async during pass 2,
-// its slot indices are loaded then too: a row starts with everything but its gathers at hand.
+// The slot indices of the next row are loaded during pass 2; its projected query (4.2 KB) is read straight
+// from global memory when the row starts (staging it in shared memory with cp.async during pass 2 was
+// measured 6 % slower: the 4.2 KB per warp are better left free).
 // No block-level synchronisation; a block is eight independent warps.
 constexpr int GA_MEM_F4 = 2 * D / 4;            // 86 sixteen-byte pieces of [neighbour | edge feature]
 constexpr int GA_ROW_F4 = D / 4;                // 43 pieces per table row
 constexpr int GA_P_ITERS = 3;                   // pieces / time-column pairs per lane (the third for lanes 0..21)
 constexpr int GA_TE_LD = 172;                   // floats per parked time encoding
 constexpr int GA_PART_LD = 33;                  // 32 partial sums + 1 pad (conflict-free column reads)
-constexpr int GA_Q_FLOATS = QT_LD;              // staged query: head h at h * 528, 516 floats used
-constexpr int GA_Q_CHUNKS = KEY / 4;            // 129 sixteen-byte chunks per head
-// (a multiple of four floats: the staged query of every warp starts on a 16-byte boundary, as its 16-byte
-// asynchronous copies and 128-bit reads need)
-__host__ __device__ constexpr int ga_warp_floats(int k) {
-  return (GA_Q_FLOATS + k * GA_TE_LD + 2 * k * GA_PART_LD + 3) & ~3;
-}
+// (a multiple of four floats: every warp's area starts on a 16-byte boundary)
+__host__ __device__ constexpr int ga_warp_floats(int k) { return (k * GA_TE_LD + 2 * k * GA_PART_LD + 3) & ~3; }
 
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
@@ -68,14 +64,6 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a
 __device__ __forceinline__ float2 dup2(float v) { return make_float2(v, v); }
 __device__ __forceinline__ float2 lo2(const float4 &v) { return make_float2(v.x, v.y); }
 __device__ __forceinline__ float2 hi2(const float4 &v) { return make_float2(v.z, v.w); }
-__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
-               "l"(gsrc)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
-}
 
 // cos of two arguments below 2^15 at once: the Cody-Waite reduction of cos_small in packed arithmetic;
 // the nearest integer of x / 2pi comes from adding and subtracting 1.5 * 2^23
@@ -149,8 +137,7 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
   dep_wait();
   const int n = rows_of(n_cap, d_n);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float *s_q = smem + warp * ga_warp_floats(k);   // staged query of the coming row
-  float *s_te = s_q + GA_Q_FLOATS;                // [k][172]
+  float *s_te = smem + warp * ga_warp_floats(k);  // [k][172]
   float *s_part = s_te + k * GA_TE_LD;            // [2k][33]
   const bool third = lane + 64 < GA_MEM_F4;       // lanes 0..21 own a third piece / pair
   // this lane's time-encoding frequencies, as column pairs, and the largest frequency of each pair group
@@ -171,27 +158,13 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
       o_dt = delta[o];
     }
   };
-  // stages the projected query of row r (both heads) in this warp's buffer
-  auto stage_query = [&](int r) {
-    const float4 *src = reinterpret_cast<const float4 *>(qt + (size_t)r * QT_LD);
-    float4 *dst = reinterpret_cast<float4 *>(s_q);
-    for (int c = lane; c < 2 * GA_Q_CHUNKS; c += 32) {
-      const int h = c >= GA_Q_CHUNKS ? 1 : 0;
-      const int o = h * (QT_HEAD / 4) + (c - h * GA_Q_CHUNKS);
-      cp_async16(dst + o, src + o);
-    }
-  };
-
   int tkt = 0;
   if (lane == 0) tkt = atomicAdd(&ticket[0], 1);
   tkt = __shfl_sync(FULL, tkt, 0);
   int row = tkt < n ? row_of_ticket(tkt) : -1;
   int my_nbr = 0, my_eid = 0;
   float my_dt = 0.f;
-  if (row >= 0) {
-    load_indices(row, my_nbr, my_eid, my_dt);
-    stage_query(row);
-  }
+  if (row >= 0) load_indices(row, my_nbr, my_eid, my_dt);
   while (row >= 0) {
     int next = -1, nx_nbr = 0, nx_eid = 0;
     float nx_dt = 0.f;
@@ -199,14 +172,11 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
     if (vmask == 0) {
       // every slot is padding: the layer ignores the attention term for this row
       if (lane == 0) valid_out[row] = 0;
-      cp_async_wait_all();     // (the staged query is not used: let it land before the buffer is refilled)
-      __syncwarp();
       if (lane == 0) tkt = atomicAdd(&ticket[0], 1);
       tkt = __shfl_sync(FULL, tkt, 0);
       if (tkt < n) {
         next = row_of_ticket(tkt);
         load_indices(next, nx_nbr, nx_eid, nx_dt);
-        stage_query(next);
       }
     } else {
       const int n_valid = __popc(vmask);
@@ -238,20 +208,18 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
         my_nl = (adt * wg0 >= 32768.f ? 1 : 0) + (adt * wg1 >= 32768.f ? 1 : 0) + (adt * wg2 >= 32768.f ? 1 : 0);
         if (!(adt * wg0 < 1073741824.f)) my_nl = -1;   // beyond the fixed-point range (or not finite)
       }
-      // the lane's pieces of the two query heads, from the staged copy (requested during the previous row)
-      cp_async_wait_all();
-      __syncwarp();
+      // the lane's pieces of the two query heads
       float4 qa[3], qb[3];
       float2 qta[GA_P_ITERS], qtb[GA_P_ITERS];
+      const float *q_src = qt + (size_t)row * QT_LD;
 #pragma unroll
       for (int i = 0; i < GA_P_ITERS; ++i) {
         const int f = (i < 2 || third) ? lane + 32 * i : 0;
-        qa[i] = reinterpret_cast<const float4 *>(s_q)[f];
-        qb[i] = reinterpret_cast<const float4 *>(s_q + QT_HEAD)[f];
-        qta[i] = reinterpret_cast<const float2 *>(s_q + 2 * D)[f];
-        qtb[i] = reinterpret_cast<const float2 *>(s_q + QT_HEAD + 2 * D)[f];
+        qa[i] = __ldg(reinterpret_cast<const float4 *>(q_src) + f);
+        qb[i] = __ldg(reinterpret_cast<const float4 *>(q_src + QT_HEAD) + f);
+        qta[i] = __ldg(reinterpret_cast<const float2 *>(q_src + 2 * D) + f);
+        qtb[i] = __ldg(reinterpret_cast<const float2 *>(q_src + QT_HEAD + 2 * D) + f);
       }
-      __syncwarp();   // every lane holds its pieces: the buffer may be refilled
 
       // ---- pass 1: time encodings and partial logits, slot by slot
       auto pass1_slot = [&](int it, int j, const float4(&x)[3]) {
@@ -341,12 +309,11 @@ attn_gather_kernel(const float *__restrict__ qt, const float *__restrict__ nbr_t
         prob_lo = e_lo * inv;
         prob_hi = e_hi * inv;
       }
-      // the next row of this warp: its indices and its query are requested now and land during pass 2
+      // the next row of this warp: its indices are requested now and land during pass 2
       tkt = __shfl_sync(FULL, tkt, 0);
       if (tkt < n) {
         next = row_of_ticket(tkt);
         load_indices(next, nx_nbr, nx_eid, nx_dt);
-        stage_query(next);
       }
 
       // ---- pass 2: weighted key sum
