@@ -453,7 +453,7 @@ def parity_vs_single(a, g, neg, plan, tgn, first, device, rank, world, n_batches
 # launches captured with ncu on workload c4 (17.01 + 16.65 MB read, 0 written) over the algorithmic bytes of
 # those launches (2 x 30.68 MB), applied to the algorithmic bytes of this run's launches; the counter cannot
 # be read while timing
-GATHER_TRAFFIC_RATIO = (17.011200 + 16.645632) / (2 * 30.683416)
+GATHER_TRAFFIC_RATIO = (15.276032 + 14.909696) / (2 * 30.683416)
 
 
 def oracle_sample(g, neg, plan, first, n_batches, sub_bs, threads, min_seconds=0.0):
