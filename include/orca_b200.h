@@ -364,6 +364,20 @@ int orca_plan_mrd(const int32_t *d_nodes, int64_t n_edges, int32_t bs, int32_t k
                   int64_t *d_plan_off, int64_t *d_stats, int32_t *d_status, void *d_workspace,
                   int64_t workspace_bytes, void *stream);
 
+/* Any of the three plans on the device: strategy 0 = MRD (the call above), 1 = LRU (utils/cache.py:338-403),
+ * 2 = 2Q (:175-333).  LRU and 2Q run as one thread block: their random evictions are a serial Fisher-Yates
+ * shuffle per batch, driven by numba's Mersenne Twister (`seed` as in orca_plan_host) and walked by one
+ * thread; the split of the tables, the statistics, the ascending member lists of the sets and the
+ * least-recently-used evictions (first entries of numba's argsort of the last-use times) are data parallel
+ * around it.  Arguments, outputs and plan order as in orca_plan_mrd / orca_plan_host
+ * (plan_cap >= n_batches * budget always suffices). */
+int64_t orca_plan_device_workspace_bytes(int32_t strategy, int64_t n_edges, int32_t bs, int32_t k,
+                                         int64_t n_nodes, int32_t budget);
+int orca_plan_device(int32_t strategy, const int32_t *d_nodes, int64_t n_edges, int32_t bs, int32_t k,
+                     const int32_t *d_nbr, int64_t n_nodes, int32_t budget, uint32_t seed,
+                     int32_t *d_plan_flat, int64_t plan_cap, int64_t *d_plan_off, int64_t *d_stats,
+                     int32_t *d_status, void *d_workspace, int64_t workspace_bytes, void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * One whole eval batch: TGN.compute_edge_probabilities(..., reuse=True, train=False, cache_plan)
  * with budget != 0 (model/tgn_model.py:95-157 over modules/embedding_module.py:215-285), enqueued

@@ -114,6 +114,9 @@ SYMBOLS = {
     "orca_csr_build": (C.c_int, [_V, _V, _V, _V, _I64, _I64, _V, _V, _V, _V, _V, _V, _I64, _V]),
     "orca_plan_mrd_workspace_bytes": (_I64, [_I64, _I32, _I32, _I64, _I32]),
     "orca_plan_mrd": (C.c_int, [_V, _I64, _I32, _I32, _V, _I64, _I32, _V, _I64, _V, _V, _V, _V, _I64, _V]),
+    "orca_plan_device_workspace_bytes": (_I64, [_I32, _I64, _I32, _I32, _I64, _I32]),
+    "orca_plan_device": (C.c_int, [_I32, _V, _I64, _I32, _I32, _V, _I64, _I32, C.c_uint32, _V, _I64, _V, _V, _V, _V,
+                                   _I64, _V]),
     "orca_eval_workspace_bytes": (_I64, [_I32, _I32, _I32, _I64]),
     "orca_eval_workspace_row_list": (_I64, [_I32, _I32, _I32, _I64, _I32]),
     "orca_tgn_eval_batch": (C.c_int, [C.POINTER(TgnT), _V, _V, _I32, _V, _I32, _I32, _V, _I64, _V, _V, _V, _V]),

@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liborca_b200.so")
-SOURCES = ["sampler.cu", "attention.cu", "gemm.cu", "state.cu", "pipeline.cu", "planner.cu", "planner_mrd.cu", "csr_build.cu", "tc_gemm.cu", "context.cu"]
+SOURCES = ["sampler.cu", "attention.cu", "gemm.cu", "state.cu", "pipeline.cu", "planner.cu", "planner_mrd.cu", "planner_rand.cu", "csr_build.cu", "tc_gemm.cu", "context.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

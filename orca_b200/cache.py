@@ -3,9 +3,10 @@
 ``get_cache_plan(args, train_data, neighbor_finder, num_embeddings, strategy)`` returns one int64
 array per batch, as the reference does.  The neighbour tables of every batch are sampled in one
 launch of the GPU sampling kernel (the reference's ``read_batches`` spends its time there, batch by
-batch in Python).  The MRD policy (the reference's default) then runs on the device as well
-(``orca_plan_mrd``); LRU and 2Q, whose random evictions are one serial Mersenne-Twister shuffle per
-batch, run in the library's host code.
+batch in Python) and the policies run on the device as well (``orca_plan_device``): MRD on a thread-block
+cluster, LRU and 2Q -- whose random evictions are one serial Mersenne-Twister shuffle per batch -- on one
+block.  ``plan_from_tables`` runs the same policies in the library's host code over tables that are
+already on the host.
 """
 from __future__ import annotations
 
@@ -58,33 +59,41 @@ def plan_from_tables(strategy, sources, destinations, bs, k, nbr_table, n_nodes,
     return plan, stats
 
 
-def plan_mrd_device(nodes, nbr_table, n_edges, bs, k, n_nodes, budget):
-    """MRD over a sampled neighbour table that is still on the device.  nodes: [2E] int32 query list
+def plan_device(strategy, nodes, nbr_table, n_edges, bs, k, n_nodes, budget, seed=0):
+    """The policy over a sampled neighbour table that is still on the device.  nodes: [2E] int32 query list
     (``batch_query_order``), nbr_table: [2E, k] int32, both CUDA tensors.  Returns the plan (one int64
     array per batch) and (n_reuse, n_recompute, sum of reuse distances)."""
+    if strategy not in STRATEGIES:
+        print(f'unsupported cache strategy {strategy}')
+        sys.exit(1)
     dev = nbr_table.device
     if dev.type != "cuda":
-        raise ValueError("plan_mrd_device needs CUDA tensors")
+        raise ValueError("plan_device needs CUDA tensors")
     nodes = nodes.to(dev, torch.int32).contiguous()
     nbr_table = nbr_table.to(torch.int32).contiguous()
     nb = math.ceil(n_edges / bs)
+    code = STRATEGIES[strategy]
     L = _lib.lib()
     with torch.cuda.device(dev):
-        ws_bytes = L.orca_plan_mrd_workspace_bytes(n_edges, bs, k, n_nodes, budget)
+        ws_bytes = L.orca_plan_device_workspace_bytes(code, n_edges, bs, k, n_nodes, budget)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         cap = max(nb * budget, 1)
         flat = torch.empty(cap, dtype=torch.int32, device=dev)
         off = torch.zeros(nb + 1, dtype=torch.int64, device=dev)
         stats = torch.zeros(3, dtype=torch.int64, device=dev)
         status = torch.zeros(4, dtype=torch.int32, device=dev)
-        _lib.check(L.orca_plan_mrd(nodes.data_ptr(), n_edges, bs, k, nbr_table.data_ptr(), n_nodes, budget,
-                                   flat.data_ptr(), cap, off.data_ptr(), stats.data_ptr(), status.data_ptr(),
-                                   ws.data_ptr(), ws_bytes, _lib.stream_ptr(dev)))
+        _lib.check(L.orca_plan_device(code, nodes.data_ptr(), n_edges, bs, k, nbr_table.data_ptr(), n_nodes, budget,
+                                      seed, flat.data_ptr(), cap, off.data_ptr(), stats.data_ptr(),
+                                      status.data_ptr(), ws.data_ptr(), ws_bytes, _lib.stream_ptr(dev)))
         _lib.check(L.orca_read_status(None, status.data_ptr(), None, _lib.stream_ptr(dev)))
     off_h = off.cpu().numpy()
     flat_h = flat[:int(off_h[-1])].cpu().numpy().astype(np.int64)
     plan = [flat_h[off_h[b]:off_h[b + 1]] for b in range(nb)]
     return plan, stats.cpu().numpy().astype(np.float64)
+
+
+def plan_mrd_device(nodes, nbr_table, n_edges, bs, k, n_nodes, budget):
+    return plan_device("MRD", nodes, nbr_table, n_edges, bs, k, n_nodes, budget)
 
 
 def _plan_local(args, train_data, neighbor_finder, num_embeddings, strategy, seed):
@@ -96,12 +105,8 @@ def _plan_local(args, train_data, neighbor_finder, num_embeddings, strategy, see
     torch.cuda.synchronize(neighbor_finder.device)
     t_prepare = time.time() - t0
     t0 = time.time()
-    if strategy == "MRD":
-        plan, stats = plan_mrd_device(nodes_dev, nbr, len(train_data.sources), args.bs, args.n_degree,
-                                      num_embeddings, budget)
-    else:
-        plan, stats = plan_from_tables(strategy, train_data.sources, train_data.destinations, args.bs,
-                                       args.n_degree, nbr.cpu().numpy(), num_embeddings, budget, seed)
+    plan, stats = plan_device(strategy, nodes_dev, nbr, len(train_data.sources), args.bs, args.n_degree,
+                              num_embeddings, budget, seed)
     t_cache = time.time() - t0
     n_reuse, n_recompute = int(stats[0]), int(stats[1])
     avg = stats[2] / stats[0] if stats[0] else float("nan")

@@ -16,17 +16,10 @@
 //                     from the codes, and the first `budget` positions of numba's argsort become the
 //                     new cache.
 //
-// numba's nopython np.argsort is an unstable quicksort (median of three, pivot parked at the right
-// end, Hoare scans that stop on equal keys, ranges of fewer than 16 finished by insertion), and with
-// most keys tied at 1e8 + 1 WHICH tied nodes stay below the budget line depends on every swap it makes.
-// The kernel reproduces its result without walking it serially.  One partition step moves elements
-// only by swapping the m-th position from the left whose key is >= pivot with the m-th position from
-// the right whose key is <= pivot, for as long as the former lies left of the latter; both position
-// lists follow from prefix counts, so a step is a block-wide scan plus independent swaps, and all
-// ranges of one recursion depth are partitioned in the same step.  Ranges that start at or after the
-// budget line are left alone.  The final insertion sort is stable, so a position's place in its range is
-// its rank by (key, position).
+// The first `budget` places of numba's argsort, with its order among equal keys, come from the steps described
+// in tie_order.cuh: block-wide in the one-CTA kernel, spread over the cluster in the cluster kernel.
 #include "common.cuh"
+#include "tie_order.cuh"
 
 namespace orca {
 namespace mrd {
@@ -58,7 +51,8 @@ __host__ __device__ inline int64_t cand_cap(int32_t bs, int32_t k, int32_t budge
   return (int64_t)budget + 2ll * bs * (k + 1);
 }
 
-__device__ __forceinline__ int32_t key_of(uint64_t x) { return (int32_t)(x >> 32); }
+using tie::key_of;
+using tie::live;
 
 // ------------------------------------------------------------------------------ backward pass
 __global__ void __launch_bounds__(T) next_use_kernel(const int32_t *nodes, const int32_t *nbr, int64_t n_edges,
@@ -98,33 +92,6 @@ __global__ void __launch_bounds__(T) next_use_kernel(const int32_t *nodes, const
 }
 
 // ------------------------------------------------------------------------------ forward pass
-// median of three on (lo, mid, hi), pivot parked at hi (the head of numba's partition step)
-__device__ __forceinline__ void park_pivot(const Work &w, int lo, int hi, int32_t *swaps) {
-  const int mid = (lo + hi) >> 1;
-  uint64_t a = w.e[lo], c = w.e[mid], d = w.e[hi];
-  uint64_t t;
-  if (key_of(c) < key_of(a)) { t = a; a = c; c = t; }
-  if (key_of(d) < key_of(c)) { t = d; d = c; c = t; }
-  if (key_of(c) < key_of(a)) { t = a; a = c; c = t; }
-  w.e[lo] = a;
-  w.e[mid] = d;
-  w.e[hi] = c;
-  w.pivot[lo] = key_of(c);
-  swaps[lo] = 0;
-}
-
-__device__ __forceinline__ bool live(int lo, int hi, int keep) { return hi - lo >= 15 && lo < keep; }
-
-// where the pivot of range (lo, hi) ends up once its pair swaps are done
-__device__ __forceinline__ int pivot_place(const Work &w, int lo, int hi, const int32_t *swaps) {
-  const int2 a = w.pre[lo], z = w.pre[hi];
-  const int n_left = z.x - a.x;
-  const int m = swaps[lo];
-  const int from_left = m < n_left ? w.lpos[lo + m] : hi;
-  const int from_right = m > 0 ? w.rpos[lo + m - 1] : hi;
-  return min(from_left, from_right);
-}
-
 __global__ void __launch_bounds__(T) mrd_kernel(const int32_t *nodes, const int32_t *nbr, int64_t n_edges, int32_t bs,
                                                 int32_t k, int64_t n_nodes, int32_t budget, Work w,
                                                 int32_t *plan, int64_t plan_cap, int64_t *plan_off,
@@ -216,7 +183,6 @@ __global__ void __launch_bounds__(T) mrd_kernel(const int32_t *nodes, const int3
         const int32_t key = (code & 1) ? (code >> 1) - (int32_t)b : FAR_KEY;
         w.cand[pos] = v;
         w.e[pos] = ((uint64_t)(uint32_t)key << 32) | (uint32_t)pos;
-        w.seg[pos] = make_int2(0, n - 1);
         ++pos;
       }
     }
@@ -225,130 +191,18 @@ __global__ void __launch_bounds__(T) mrd_kernel(const int32_t *nodes, const int3
       if (tid == 0) report(status, ORCA_E_CAPACITY, (int)b);
       break;
     }
-    __syncthreads();
     // ---- the first `keep` positions of numba's argsort
-    bool any = live(0, n - 1, keep);
-    int32_t *swaps = w.swaps, *swaps_next = w.swaps + cap;
-    if (any && tid == 0) park_pivot(w, 0, n - 1, swaps);
-    __syncthreads();
-    const int chunk = ((n + NW - 1) / NW + 31) & ~31;  // positions per warp in the scan
-    int depth = 0;
-    while (any) {
-      if (++depth > n) break;   // every step shortens the longest live range: more steps than entries is a fault
-      // prefix counts of the left list (key >= pivot) and the right list (key <= pivot) over [lo, hi)
-      int cl = 0, cr = 0;
-      for (int j = 0; j < chunk; j += 32) {
-        const int pos = warp * chunk + j + lane;
-        bool is_l = false, is_r = false;
-        if (pos < n) {
-          const int2 sg = w.seg[pos];
-          if (live(sg.x, sg.y, keep) && pos < sg.y) {
-            const int32_t kv = key_of(w.e[pos]), pv = w.pivot[sg.x];
-            is_l = kv >= pv;
-            is_r = kv <= pv;
-          }
-        }
-        cl += __popc(__ballot_sync(0xffffffffu, is_l));
-        cr += __popc(__ballot_sync(0xffffffffu, is_r));
-      }
-      if (lane == 0) {
-        s_l[warp] = cl;
-        s_r[warp] = cr;
-      }
-      __syncthreads();
-      int bl = 0, br = 0;
-      for (int i = 0; i < warp; ++i) {
-        bl += s_l[i];
-        br += s_r[i];
-      }
-      for (int j = 0; j < chunk; j += 32) {
-        const int pos = warp * chunk + j + lane;
-        bool is_l = false, is_r = false;
-        if (pos < n) {
-          const int2 sg = w.seg[pos];
-          if (live(sg.x, sg.y, keep) && pos < sg.y) {
-            const int32_t kv = key_of(w.e[pos]), pv = w.pivot[sg.x];
-            is_l = kv >= pv;
-            is_r = kv <= pv;
-          }
-        }
-        const uint32_t ml = __ballot_sync(0xffffffffu, is_l), mr = __ballot_sync(0xffffffffu, is_r);
-        if (pos < n) w.pre[pos] = make_int2(bl + __popc(ml & lt_mask), br + __popc(mr & lt_mask));
-        bl += __popc(ml);
-        br += __popc(mr);
-      }
-      __syncthreads();
-      // the two position lists of every range
-      for (int pos = tid; pos < n; pos += T) {
-        const int2 sg = w.seg[pos];
-        if (!live(sg.x, sg.y, keep) || pos >= sg.y) continue;
-        const int32_t kv = key_of(w.e[pos]), pv = w.pivot[sg.x];
-        const int2 me = w.pre[pos];
-        if (kv >= pv) w.lpos[sg.x + me.x - w.pre[sg.x].x] = pos;
-        if (kv <= pv) w.rpos[sg.x + w.pre[sg.y].y - me.y - 1] = pos;
-      }
-      __syncthreads();
-      // pair m swaps while its left position is left of its right position
-      for (int pos = tid; pos < n; pos += T) {
-        const int2 sg = w.seg[pos];
-        if (!live(sg.x, sg.y, keep) || pos >= sg.y) continue;
-        const int2 a = w.pre[sg.x], z = w.pre[sg.y];
-        const int pairs = min(z.x - a.x, z.y - a.y);
-        const int m = pos - sg.x;
-        if (m >= pairs) continue;
-        const int pl = w.lpos[pos], pr = w.rpos[pos];
-        if (pl >= pr) continue;
-        const uint64_t x = w.e[pl], y = w.e[pr];
-        w.e[pl] = y;
-        w.e[pr] = x;
-        if (m + 1 >= pairs || w.lpos[pos + 1] >= w.rpos[pos + 1]) swaps[sg.x] = m + 1;
-      }
-      __syncthreads();
-      // pivot into place, ranges split, next pivots parked
-      bool more = false;
-      for (int pos = tid; pos < n; pos += T) {
-        int2 sg = w.seg[pos];
-        if (!live(sg.x, sg.y, keep)) continue;
-        const int p = pivot_place(w, sg.x, sg.y, swaps);
-        if (pos == p + 1) {
-          // the first position right of the pivot's place moves the pivot there (nobody else reads
-          // either slot in this phase: hi belongs to the right part, p to no part)
-          const uint64_t x = w.e[p], y = w.e[sg.y];
-          w.e[p] = y;
-          w.e[sg.y] = x;
-        }
-        if (pos < p) sg.y = p - 1;
-        else if (pos > p) sg.x = p + 1;
-        else sg.x = sg.y = p;
-        w.seg[pos] = sg;
-        if (live(sg.x, sg.y, keep)) {
-          more = true;
-          if (pos == sg.x) park_pivot(w, sg.x, sg.y, swaps_next);
-        }
-      }
-      any = __syncthreads_or(more);
-      int32_t *t = swaps;
-      swaps = swaps_next;
-      swaps_next = t;
-    }
-    if (depth > n) {   // uniform over the block
+    const tie::Buf sb{w.e, w.seg, w.pre, w.lpos, w.rpos, w.pivot, w.swaps, cap};
+    if (!tie::sort_first(sb, n, keep, s_l, s_r)) {   // uniform over the block
       if (tid == 0) report(status, ORCA_E_TIMEOUT, (int)b);
       break;
     }
     // ranges shorter than 16: stable order by key; the first `keep` places are the new cache
     if (tid == 0) plan_off[b] = used;
     for (int pos = tid; pos < n; pos += T) {
-      const int2 sg = w.seg[pos];
-      if (sg.x >= keep) continue;
-      const uint64_t me = w.e[pos];
-      const int32_t kv = key_of(me);
-      int place = sg.x;
-      for (int qpos = sg.x; qpos <= sg.y; ++qpos) {
-        const int32_t ko = key_of(w.e[qpos]);
-        place += (ko < kv || (ko == kv && qpos < pos)) ? 1 : 0;
-      }
-      if (place >= keep) continue;
-      const int32_t v = w.cand[(uint32_t)me];
+      const int place = tie::place_of(sb, pos, keep);
+      if (place < 0) continue;
+      const int32_t v = w.cand[(uint32_t)w.e[pos]];
       plan[used + place] = v;
       atomicOr(&w.cached[v >> 5], 1u << (v & 31));
       if ((__ldcg(&w.fresh[v >> 5]) >> (v & 31)) & 1u) w.since[v] = (int32_t)b;

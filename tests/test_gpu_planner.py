@@ -1,7 +1,7 @@
-"""The device MRD planner (orca_plan_mrd) against the reference's plans (golden fixtures) and against
-the oracle's planner on inputs that put many equal keys at the budget line, where the order numba's
-argsort leaves among equal keys decides which nodes stay cached.  Plans are compared entry by entry, in
-order; the statistics are compared as integers."""
+"""The device planners (orca_plan_device: MRD, LRU, 2Q) against the reference's plans (golden fixtures) and
+against the oracle's planner on inputs that put many equal keys at the budget line, where the order numba's
+argsort leaves among equal keys -- and, for LRU and 2Q, the stream of its Mersenne Twister -- decide which
+nodes stay cached.  Plans are compared entry by entry, in order; the statistics are compared as integers."""
 import dataclasses
 
 import numpy as np
@@ -13,7 +13,7 @@ from helpers import golden, graph, unpack
 pytestmark = pytest.mark.gpu
 
 
-def _device_plan(g, bs, k, budget, tables_from_oracle=True):
+def _device_plan(g, bs, k, budget, tables_from_oracle=True, strategy="MRD", seed=0):
     """Plan of the device planner; the neighbour table comes from the oracle's sampler (so that the test
     isolates the planner) or from the product sampler."""
     from oracle import tgn_oracle
@@ -25,16 +25,19 @@ def _device_plan(g, bs, k, budget, tables_from_oracle=True):
     else:
         from orca_b200.neighbor_finder import get_neighbor_finder
         nbr = get_neighbor_finder(g, g.n_nodes - 1, device="cuda").sample_device(nodes, ts, k)[0]
-    plan, stats = cache.plan_mrd_device(torch.as_tensor(nodes).cuda(), nbr, g.n_edges, bs, k, g.n_nodes, budget)
+    plan, stats = cache.plan_device(strategy, torch.as_tensor(nodes).cuda(), nbr, g.n_edges, bs, k, g.n_nodes, budget,
+                                    seed)
     return adj, plan, stats
 
 
 @pytest.mark.parametrize("case", ["c1", "t_bip2", "t_nb2", "t_lru", "t_2q"])
-def test_mrd_plans_match_reference(case):
+@pytest.mark.parametrize("strategy", ["MRD", "LRU", "2Q"])
+def test_plans_match_reference(case, strategy):
     gold = golden(case)
     g = graph(str(gold["spec"]))
-    _, got, _ = _device_plan(g, g.spec.bs, g.spec.n_degree, g.spec.budget, tables_from_oracle=False)
-    want = unpack(gold["plan_MRD_flat"], gold["plan_MRD_off"])
+    _, got, _ = _device_plan(g, g.spec.bs, g.spec.n_degree, g.spec.budget, tables_from_oracle=False,
+                             strategy=strategy)
+    want = unpack(gold[f"plan_{strategy}_flat"], gold[f"plan_{strategy}_off"])
     assert len(got) == len(want)
     for b, (a, w) in enumerate(zip(got, want)):
         assert a.dtype == np.int64 and np.array_equal(a, w), f"batch {b}"
@@ -42,16 +45,17 @@ def test_mrd_plans_match_reference(case):
 
 @pytest.mark.parametrize("budget,bs,seed", [(7, 50, 1), (40, 120, 2), (300, 200, 3), (2, 64, 4), (1000, 400, 5),
                                             (100000, 200, 6), (200000, 200, 7)])
-def test_mrd_matches_oracle_on_tight_budgets(budget, bs, seed):
+@pytest.mark.parametrize("strategy", ["MRD", "LRU", "2Q"])
+def test_plans_match_oracle_on_tight_budgets(strategy, budget, bs, seed):
     """Budgets from far below to far above the number of candidates; statistics included.  (The last budget
     makes the candidate capacity larger than a thread-block cluster takes, so the one-CTA kernels run.)"""
     from oracle import planner
     from orca_b200 import synthetic
     spec = dataclasses.replace(synthetic.SPECS["t_nb2"], n_src=400, n_edges=3000, bs=bs, budget=budget)
     g = synthetic.make_graph(spec, seed=seed)
-    adj, got, stats = _device_plan(g, bs, 10, budget)
+    adj, got, stats = _device_plan(g, bs, 10, budget, strategy=strategy, seed=seed)
     rb = planner.read_batches(g.sources, g.destinations, g.timestamps, bs, 10, adj, g.n_nodes)
-    want, wstats = planner.solve("MRD", rb, g.n_nodes, budget, seed=seed)
+    want, wstats = planner.solve(strategy, rb, g.n_nodes, budget, seed=seed)
     assert len(got) == len(want)
     for b, (a, w) in enumerate(zip(got, want)):
         assert np.array_equal(a, w), f"batch {b}"
