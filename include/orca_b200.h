@@ -242,7 +242,8 @@ int orca_attn_gather_profile_read(orca_ctx_t *ctx, double *h_ms_total, int64_t *
  * utils/util.py:21-24): d_out[r] = LN(fc2(relu(fc1([attn | h_src])))).  If d_push_table is
  * non-NULL the row is also written to d_push_table[d_push_ids[r]] when d_push_win[r] != 0, which
  * is History.push (modules/history.py:38-40) with the last occurrence of an id winning.
- * d_scratch_hidden: [n_rows_cap, 172] floats for the merger's hidden layer. */
+ * d_scratch_hidden: no longer used (both projection kernels keep the merger's hidden tile on the SM); may be
+ * NULL. */
 int orca_attn_output(const orca_attn_weights_t *w, const float *d_ctx, const uint8_t *d_valid,
                      const float *d_feat, const int32_t *d_idx, int32_t n_rows_cap,
                      const int32_t *d_n_rows, float *d_out, float *d_push_table,
