@@ -42,6 +42,9 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="direct", choices=["direct", "nccl"],
                     help="N > 1: how the layer-1 rows travel between the GPUs (peer stores or an NCCL all-gather)")
+    ap.add_argument("--split", default="layers", choices=["layers", "rows"],
+                    help="N > 1: layers = the first N // 2 GPUs compute layer 1 and the memory update, the others "
+                         "the top layer and the scores (default); rows = every GPU its share of both layers' rows")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="N > 1: strong = the workload's batch split over the GPUs (default); weak = a batch of "
                          "bs edges PER GPU, i.e. the same stream cut into batches of bs * N edges")
@@ -226,7 +229,7 @@ def run_ours(a):
     L = _lib.lib()
     g, neg, plan, tgn = build_setup(a, device, quiet=rank != 0)
     if world > 1:
-        tgn.set_distributed(rank, world, exchange=a.exchange)
+        tgn.set_distributed(rank, world, exchange=a.exchange, split=a.split)
     spec = g.spec
     K, W = a.steps, a.warmup
     nb_avail = len(plan)
@@ -389,7 +392,12 @@ def run_ours(a):
                 "timing": f"median of {rep_dev} windows of {K} steps, each after a state reset and {W} warm-up steps",
                 **({"weak_scaling": f"batches of {spec.bs // world} edges per GPU: the stream is cut into batches "
                                     f"of {spec.bs} edges"} if (world > 1 and a.scaling == "weak") else {}),
-                "sharding": ("replicated tables; attention rows and scores split by row/edge % n_gpus; layer-1 rows "
+                "sharding": ("replicated tables; "
+                             + (f"layer 1 and the memory update on {tgn._layer1_ranks} GPU(s) (rows by row % "
+                                f"{tgn._layer1_ranks}), top layer and scores on the other {world - tgn._layer1_ranks} "
+                                f"(edges by edge % {world - tgn._layer1_ranks}); " if tgn._layer1_ranks
+                                else "attention rows and scores split by row/edge % n_gpus; ")
+                             + "layer-1 rows and updated memory rows "
                              + ("written to every GPU by peer stores over NVLink" if tgn._exchange is not None
                                 else "all-gathered with NCCL") + " once per batch") if world > 1 else "single GPU"}),
             "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches_per_batch * K), "clocks": clocks,

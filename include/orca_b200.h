@@ -39,9 +39,11 @@ extern "C" {
 #define ORCA_HEADS 2
 #define ORCA_MAX_K 32
 #define ORCA_MAX_WORLD 8   /* GPUs of one node */
-#define ORCA_FLAG_WORDS 32    /* flag words of one rank's exchange buffer: [0,8) layer-1 rows posted by rank q, [8]
+#define ORCA_FLAG_WORDS 48    /* flag words of one rank's exchange buffer: [0,8) layer-1 rows posted by rank q, [8]
                                  check-out counter of the layer-1 kernel, [16,24) memory rows posted by rank q,
-                                 [24] check-out counter of the memory-update kernel */
+                                 [24] check-out counter of the memory-update kernel, [32,40) (split by layer)
+                                 last batch whose buffers top-layer rank q has finished reading */
+#define ORCA_FLAG_CONSUMED 32
 #define ORCA_EXCHANGE_SLOTS 4 /* batches whose layer-1 rows an exchange buffer holds: with the lanes of the
                                  batch pipeline a rank's layer 1 may be two batches ahead of a peer's layer 2 */
 #define ORCA_CAND_CAP 2048 /* listed candidates of the uncached set; more fall back to a bitmap scan */
@@ -443,6 +445,13 @@ typedef struct {
                             /* ready, e.g. a copy stream; NULL = the call's `stream`.  Only with an    */
                             /* input stream of its own can the index work of a batch run ahead of the  */
                             /* previous batch's kernels on `stream`.                                   */
+  /* Split by layer (direct exchange only): 0 = every rank computes its share of both layers' rows.
+   * layer1_ranks = a (0 < a < world): ranks 0..a-1 compute layer 1 (row i on rank i % a) and the memory
+   * update (node split over the same ranks) and deliver the rows to ALL ranks; ranks a..world-1 compute
+   * the top layer and the scores (edge e on rank a + e % (world - a)).  Every rank still applies all
+   * rows to its replicas of the history and memory tables.  The two halves of a batch's kernel chain
+   * then run on different GPUs, a batch apart. */
+  int32_t layer1_ranks;
 } orca_tgn_t;
 
 /* Workspace sizing: bytes needed for batches of up to b_cap edges with at most u_cap uncached

@@ -19,7 +19,7 @@ QT_LD = 1056
 MSG_DIM = 688
 CAND_CAP = 2048   # ORCA_CAND_CAP
 EXCHANGE_SLOTS = 4  # ORCA_EXCHANGE_SLOTS
-FLAG_WORDS = 32     # ORCA_FLAG_WORDS
+FLAG_WORDS = 48     # ORCA_FLAG_WORDS
 # options of orca_ctx_set
 OPT_PROJECTION_MODE, OPT_OVERLAP, OPT_DEPENDENT_LAUNCH, OPT_LOOKAHEAD, OPT_WAIT_LIMIT, OPT_TRACE = range(6)
 
@@ -70,6 +70,7 @@ class TgnT(C.Structure):
         ("exchange_seq", C.POINTER(C.c_int64)),
         ("ctx", C.c_void_p),
         ("input_stream", C.c_void_p),
+        ("layer1_ranks", C.c_int32),
     ]
 
 

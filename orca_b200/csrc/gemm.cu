@@ -556,7 +556,7 @@ int attn_output_impl(const orca_attn_weights_t *w, const float *d_ctx, const uin
 namespace orca {
 
 int gru_project(const orca_gru_weights_t *w, const orca_memory_t *mem, const int32_t *d_nodes, int32_t n_cap,
-                const int32_t *d_n, float *d_scratch_h, cudaStream_t s, const tc::PeerOut *peer) {
+                const int32_t *d_n, float *d_scratch_h, cudaStream_t s, const tc::PeerOut *peer, int split) {
   ORCA_CHECK_ARG(w && w->Wg && w->bg && mem && mem->memory && mem->last_update && mem->messages &&
                  mem->msg_ts && mem->msg_flag && d_nodes && d_scratch_h && n_cap >= 0);
   if (n_cap == 0) return ORCA_OK;
@@ -577,8 +577,9 @@ int gru_project(const orca_gru_weights_t *w, const orca_memory_t *mem, const int
     if (peer != nullptr) {
       // one rank of the multi-GPU split: every world-th listed node from `rank`, rows delivered to all ranks
       a.peer = *peer;
-      a.row_stride = peer->world, a.row_off = peer->rank, a.idx_limit = n_cap;
-      a.m_cap = ceil_div(n_cap, peer->world);
+      const int stride = split > 0 ? split : peer->world;
+      a.row_stride = stride, a.row_off = peer->rank, a.idx_limit = n_cap;
+      a.m_cap = ceil_div(n_cap, stride);
     }
     return tc::launch(tc::EPI_GRU, a, 4, s);
   }

@@ -39,10 +39,12 @@ int launch_row_order(const int32_t *d_nbr_a, int n_cap_a, const int32_t *d_n_a, 
 // the two halves of orca_gru_update (gemm.cu): the projection + gates into d_scratch_h reads the tables
 // only; the scatter writes memory / last_update and clears the message flags
 // (peer, multi-GPU: this rank computes every world-th listed node from its rank and stores the rows into
-// every rank's buffer peer->rows[q] + peer->off instead of d_scratch_h, then posts peer->seq)
+// every rank's buffer peer->rows[q] + peer->off instead of d_scratch_h, then posts peer->seq; split > 0: the
+// nodes are split over the first `split` ranks only, the rows still go to all peer->world ranks)
 namespace tc { struct PeerOut; }
 int gru_project(const orca_gru_weights_t *w, const orca_memory_t *mem, const int32_t *d_nodes, int32_t n_cap,
-                const int32_t *d_n, float *d_scratch_h, cudaStream_t s, const tc::PeerOut *peer = nullptr);
+                const int32_t *d_n, float *d_scratch_h, cudaStream_t s, const tc::PeerOut *peer = nullptr,
+                int split = 0);
 // (d_skip_if_set, optional: a device status word; the scatter leaves the table alone when it is non-zero)
 int gru_scatter(const orca_memory_t *mem, const int32_t *d_nodes, int32_t n_cap, const int32_t *d_n,
                 int32_t clear_flags, const float *d_scratch_h, cudaStream_t s, const int32_t *d_skip_if_set = nullptr);

@@ -190,16 +190,18 @@ __global__ void push_gathered_kernel(float *__restrict__ table, const float *__r
 }
 
 // top-layer rows of the local edges e = rank + j * world: local row p * b_loc + j <- batch row p * b + e
+// (rows_world: the number of ranks the layer-1 rows are dealt out over, which fixes where a row sits in the
+// gathered buffer)
 __global__ void shard_l2_kernel(const int32_t *__restrict__ nbr2, const int32_t *__restrict__ eid2,
-                                const float *__restrict__ dt2, int b, int k, int rank, int world, int rpr,
-                                int b_loc, int32_t *__restrict__ feat_idx, int32_t *__restrict__ nbr_loc,
+                                const float *__restrict__ dt2, int b, int k, int rank, int world, int rows_world,
+                                int rpr, int b_loc, int32_t *__restrict__ feat_idx, int32_t *__restrict__ nbr_loc,
                                 int32_t *__restrict__ eid_loc, float *__restrict__ dt_loc) {
   const int lr = blockIdx.x * blockDim.x / 32 + threadIdx.x / 32;   // one warp per local row
   const int lane = threadIdx.x % 32;
   if (lr >= 3 * b_loc) return;
   const int p = lr / b_loc, j = lr - p * b_loc;
   const int row = p * b + rank + j * world;
-  if (lane == 0) feat_idx[lr] = (row % world) * rpr + row / world;
+  if (lane == 0) feat_idx[lr] = (row % rows_world) * rpr + row / rows_world;
   if (lane < k) {
     nbr_loc[(size_t)lr * k + lane] = nbr2[(size_t)row * k + lane];
     eid_loc[(size_t)lr * k + lane] = eid2[(size_t)row * k + lane];
@@ -275,6 +277,18 @@ __global__ void exchange_wait_kernel(const int32_t *__restrict__ flags, int worl
       }
     }
   }
+}
+
+// Split by layer: a top-layer rank tells the layer-1 ranks that it has finished reading batch `seq` out of
+// its exchange and memory-row buffers (word ORCA_FLAG_CONSUMED + rank of their flag arrays).
+__global__ void post_consumed_kernel(Peers p, int first, int count, int rank, int seq) {
+  dep_trigger();
+  dep_wait();
+  __threadfence_system();
+  const int q = first + (int)threadIdx.x;
+  if ((int)threadIdx.x < count)
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.flags[q] + ORCA_FLAG_CONSUMED + rank), "r"(seq)
+                 : "memory");
 }
 
 __global__ void publish_counts_kernel(const int32_t *n1, const int32_t *n_win, int32_t *status) {
@@ -438,8 +452,13 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
   const int k = m->k, world = m->world > 1 ? m->world : 1, rank = world > 1 ? m->rank : 0;
   const bool sharded = world > 1;
   const int N = 3 * b, R1 = N + u_cap;
-  const int rpr = ceil_div(R1, world);
-  const int b_loc = (b - rank + world - 1) / world;
+  // split by layer: ranks [0, wa) own the layer-1 rows and the memory update, ranks [wa, world) the top layer
+  const bool staged = sharded && m->layer1_ranks > 0;
+  const int wa = staged ? m->layer1_ranks : world, wb = staged ? world - m->layer1_ranks : world;
+  const bool in_a = !staged || rank < wa, in_b = !staged || rank >= wa;
+  const int rb = staged ? rank - wa : rank;
+  const int rpr = ceil_div(R1, wa);
+  const int b_loc = in_b ? (b - rb + wb - 1) / wb : 0;
   Tracer &tr = c->trace;
   const bool lanes = c->lookahead && c->overlap && !tr.on;
   cudaStream_t si = lanes ? c->idx : s;                       // index lane
@@ -448,10 +467,11 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
   const bool direct = sharded && m->peer_rows[rank] != nullptr;   // rows exchanged by peer stores
   if (direct) {
     ORCA_CHECK_ARG(world <= ORCA_MAX_WORLD && m->exchange_seq != nullptr && m->peer_flags[rank] != nullptr);
-    if ((int64_t)world * rpr * D > m->exchange_cap)
+    if ((int64_t)wa * rpr * D > m->exchange_cap)
       return set_error(ORCA_E_CAPACITY, "orca_tgn_eval_batch_sharded: exchange buffer of %lld floats, %lld needed",
-                       (long long)m->exchange_cap, (long long)world * rpr * D);
+                       (long long)m->exchange_cap, (long long)wa * rpr * D);
   }
+  if (staged) ORCA_CHECK_ARG(direct && wa < world && m->peer_gru[rank] != nullptr && projections_on_tensor_cores());
 
   const bool gru_split = direct && m->peer_gru[rank] != nullptr && projections_on_tensor_cores();
   if (gru_split && (int64_t)2 * b * D > m->gru_cap)
@@ -500,14 +520,16 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
     ORCA_TRY(tr.mark(PH_UNCACHED, s));
     if (sharded) {
       // this rank's layer-1 rows, and the top-layer tables of its edges
-      shard_l1_kernel<<<ceil_div(rpr, 256), 256, 0, si>>>(x.nodes1, x.ts1, x.n1, rank, world, rpr, x.loc_nodes,
-                                                          x.loc_ts, x.n1_loc);
-      ORCA_COUNT_LAUNCH();
-      ORCA_LAUNCH_CHECK();
-      ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, x.loc_nodes, x.loc_ts, rpr,
-                                x.n1_loc, k, x.nbr1, x.eid1, nullptr, x.dt1, d_status, si));
+      if (in_a) {
+        shard_l1_kernel<<<ceil_div(rpr, 256), 256, 0, si>>>(x.nodes1, x.ts1, x.n1, rank, wa, rpr, x.loc_nodes,
+                                                            x.loc_ts, x.n1_loc);
+        ORCA_COUNT_LAUNCH();
+        ORCA_LAUNCH_CHECK();
+        ORCA_TRY(orca_sample_topk(m->indptr, m->adj_nbr, m->adj_eid, m->adj_ts, m->n_nodes, x.loc_nodes, x.loc_ts,
+                                  rpr, x.n1_loc, k, x.nbr1, x.eid1, nullptr, x.dt1, d_status, si));
+      }
       if (b_loc > 0) {
-        shard_l2_kernel<<<ceil_div(3 * b_loc, 8), 256, 0, si>>>(x.nbr2, x.eid2, x.dt2, b, k, rank, world, rpr, b_loc,
+        shard_l2_kernel<<<ceil_div(3 * b_loc, 8), 256, 0, si>>>(x.nbr2, x.eid2, x.dt2, b, k, rb, wb, wa, rpr, b_loc,
                                                                 x.feat_idx, x.nbr2_loc, x.eid2_loc, x.dt2_loc);
         ORCA_COUNT_LAUNCH();
         ORCA_LAUNCH_CHECK();
@@ -519,7 +541,8 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
     }
     // the order in which the two gather launches hand out their rows (heaviest first)
     if (sharded)
-      ORCA_TRY(launch_row_order(x.nbr1, rpr, x.n1_loc, x.order1, x.nbr2_loc, 3 * b_loc, nullptr, x.order2, k, si));
+      ORCA_TRY(launch_row_order(x.nbr1, in_a ? rpr : 0, x.n1_loc, x.order1, x.nbr2_loc, 3 * b_loc, nullptr, x.order2, k,
+                                si));
     else
       ORCA_TRY(launch_row_order(x.nbr1, R1, x.n1, x.order1, x.nbr1, N, nullptr, x.order2, k, si));
     ORCA_TRY(tr.mark(PH_SAMPLE_L1, s));
@@ -557,9 +580,18 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
     ORCA_TRY(orca_message_store(&m->mem, m->edge_table, m->time_w, d_batch_i32, x.cat_dst, d_batch_ts,
                                 d_batch_i32 + 3 * b, b, x.win_pos, 2 * b, x.n_win, x.win_nodes, sx));
     ORCA_TRY(tr.mark(PH_MESSAGE, s));
-    if (gru_split) {
-      // the memory update is split by node: this rank computes every world-th unique positive and stores the
-      // new rows into every rank's buffer; the scatter (phase 2) waits for all ranks' rows
+    if (gru_split && !in_a) {
+      // (split by layer: the layer-1 ranks compute the memory update; this rank only receives the rows)
+    } else if (gru_split) {
+      // the memory update is split by node: this rank computes every wa-th unique positive and stores the
+      // new rows into every rank's buffer; the scatter (phase 2) waits for all computing ranks' rows
+      if (staged) {
+        // (the top-layer ranks run behind: their buffers of two batches ago must have been read)
+        ORCA_CUDA(launch_dep(exchange_wait_kernel, 1, 32, 0, sx,
+                             (const int32_t *)(m->peer_flags[rank] + ORCA_FLAG_CONSUMED + wa), wb, (int)c->xseq - 2,
+                             d_status, c->wait_limit));
+        ORCA_COUNT_LAUNCH();
+      }
       tc::PeerOut po{};
       for (int q = 0; q < world; ++q) {
         ORCA_CHECK_ARG(m->peer_gru[q] != nullptr && m->peer_flags[q] != nullptr);
@@ -569,7 +601,7 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
       po.counter = m->peer_flags[rank] + 24;
       po.off = (c->xseq & 1) * m->gru_cap;
       po.world = world, po.rank = rank, po.seq = (int)c->xseq;
-      ORCA_TRY(gru_project(&m->gru, &m->mem, x.win_nodes, 2 * b, x.n_win, w.gru_h, sx, &po));
+      ORCA_TRY(gru_project(&m->gru, &m->mem, x.win_nodes, 2 * b, x.n_win, w.gru_h, sx, &po, wa));
     } else {
       ORCA_TRY(gru_project(&m->gru, &m->mem, x.win_nodes, 2 * b, x.n_win, w.gru_h, sx));
     }
@@ -578,6 +610,7 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
     // ------------------------------------------------------------------ layer-1 lane
     ORCA_TRY(wait_on(sa, si, c->ev_idx[p]));
     if (sa != sx && c->state_recorded) ORCA_CUDA(cudaStreamWaitEvent(sa, c->ev_state, 0));
+    if (in_a) {
     const int32_t *rows1 = sharded ? x.loc_nodes : x.nodes1;
     const int32_t *d_n1 = sharded ? x.n1_loc : x.n1;
     const int cap1 = sharded ? rpr : R1;
@@ -605,6 +638,12 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
       po.counter = m->peer_flags[rank] + ORCA_MAX_WORLD;
       po.off = (seq % ORCA_EXCHANGE_SLOTS) * m->exchange_cap + (long long)rank * rpr * D;
       po.world = world, po.rank = rank, po.seq = (int)seq;
+      if (staged) {
+        ORCA_CUDA(launch_dep(exchange_wait_kernel, 1, 32, 0, sa,
+                             (const int32_t *)(m->peer_flags[rank] + ORCA_FLAG_CONSUMED + wa), wb, (int)seq - 2,
+                             d_status, c->wait_limit));
+        ORCA_COUNT_LAUNCH();
+      }
       ORCA_TRY(attn_output_impl(&m->attn[0], l1.ctx, l1.valid, m->mem.memory, x.loc_nodes, rpr, x.n1_loc, emb1,
                                 nullptr, nullptr, nullptr, nullptr, 0, 0, l1.hidden, 0, sa, &po));
     } else {
@@ -625,6 +664,7 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
         ORCA_COUNT_LAUNCH();
       }
     }
+    }   // in_a
     ORCA_TRY(tr.mark(PH_OUTPUT_L1, s));
     if (sa != s || sx != s) ORCA_CUDA(cudaEventRecord(c->ev_o1, sa));
 
@@ -644,7 +684,7 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
   if ((phases & 2) && gru_split) {
     // ------------------------------------------------------------------ side lane: all ranks' memory rows
     ORCA_TRY(wait_on(sx, sa, c->ev_o1));
-    ORCA_CUDA(launch_dep(exchange_wait_kernel, 1, 32, 0, sx, (const int32_t *)(m->peer_flags[rank] + 16), world,
+    ORCA_CUDA(launch_dep(exchange_wait_kernel, 1, 32, 0, sx, (const int32_t *)(m->peer_flags[rank] + 16), wa,
                          (int)c->xseq, d_status, c->wait_limit));
     ORCA_COUNT_LAUNCH();
     ORCA_TRY(gru_scatter(&m->mem, x.win_nodes, 2 * b, x.n_win, 1, m->peer_gru[rank] + (c->xseq & 1) * m->gru_cap, sx,
@@ -664,16 +704,18 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
     if (sharded) {
       if (direct) {
         const long long seq = c->xseq;
-        ORCA_CUDA(launch_dep(exchange_wait_kernel, 1, 32, 0, s, (const int32_t *)m->peer_flags[rank], world, (int)seq,
+        ORCA_CUDA(launch_dep(exchange_wait_kernel, 1, 32, 0, s, (const int32_t *)m->peer_flags[rank], wa, (int)seq,
                              d_status, c->wait_limit));
         ORCA_COUNT_LAUNCH();
         d_emb1_all = m->peer_rows[rank] + (seq % ORCA_EXCHANGE_SLOTS) * m->exchange_cap;
       }
       ORCA_CHECK_ARG(d_emb1_all != nullptr);
       // every replica of the history table receives every layer-1 row (winners by the head kernel's records)
+      // (measured with the split by layer on 2 GPUs: moving this push to the layer-1 stream costs 9 us per
+      // batch on the layer-1 rank, whose lane is the critical one; on the top-layer rank it gains nothing)
       push_gathered_kernel<<<std::min(ceil_div(R1, 4), c->sm_count * 8), 256, 0, s>>>(m->hist_emb, d_emb1_all, x.nodes1,
                                                            reinterpret_cast<const unsigned long long *>(lp_push),
-                                                           base1, N, x.n1, world, rpr, d_status);
+                                                           base1, N, x.n1, wa, rpr, d_status);
       ORCA_COUNT_LAUNCH();
       ORCA_LAUNCH_CHECK();
       feat2 = d_emb1_all, feat2_idx = x.feat_idx;
@@ -701,6 +743,12 @@ static int eval_budget(const orca_tgn_t *m, Ctx *c, int phases, const int32_t *d
     // the batch is complete on the caller's stream once the other lanes' parts of it are
     if (sx != s) ORCA_CUDA(cudaStreamWaitEvent(s, c->ev_state, 0));
     if (si != s) ORCA_CUDA(cudaStreamWaitEvent(s, c->ev_flags, 0));
+    if (staged && !in_a) {
+      Peers pr{};
+      for (int q = 0; q < world; ++q) pr.flags[q] = m->peer_flags[q];
+      ORCA_CUDA(launch_dep(post_consumed_kernel, 1, 32, 0, s, pr, 0, wa, rank, (int)c->xseq));
+      ORCA_COUNT_LAUNCH();
+    }
     if (lanes) {
       ORCA_CUDA(cudaEventRecord(c->ev_done[p], s));
       c->done_recorded[p] = true;
@@ -839,7 +887,10 @@ int orca_tgn_eval_epoch(const orca_tgn_t *m, const orca_epoch_t *e, int32_t u_ca
     if (sharded) {
       ORCA_TRY(orca_tgn_eval_batch_sharded(&mm, 0, d_i32, d_ts, b, d_plan, n_plan > 0 ? n_plan : 0, u_cap, d_workspace,
                                            workspace_bytes, nullptr, nullptr, prob, nullptr, d_status, stream));
-      n_scores = 2 * ((b - m->rank + m->world - 1) / m->world);
+      // (split by layer: only the top-layer ranks hold scores)
+      const int wa = m->layer1_ranks > 0 ? m->layer1_ranks : 0;
+      const int wb = m->world - wa, rb = m->rank - wa;
+      n_scores = rb < 0 ? 0 : 2 * ((b - rb + wb - 1) / wb);
     } else {
       ORCA_TRY(orca_tgn_eval_batch(&mm, d_i32, d_ts, b, d_plan, n_plan > 0 ? n_plan : 0, u_cap, d_workspace,
                                    workspace_bytes, prob, nullptr, d_status, stream));

@@ -213,6 +213,7 @@ class TGN(nn.Module):
         self._dummy_prev = np.full(1, -1, dtype=np.int32)
         self.last_counts = None
         self._rank, self._world, self._group = 0, 1, None
+        self._layer1_ranks = 0         # multi-GPU split by layer: ranks that compute layer 1 (0: split by rows only)
         self._exchange = None          # direct exchange buffers of the multi-GPU split (set_distributed)
         self._mode = MODE_BUDGET
 
@@ -239,15 +240,19 @@ class TGN(nn.Module):
         torch.cuda.synchronize(self.device)
         return self._ws[off: off + 4 * n_rows].view(torch.int32).cpu().numpy()
 
-    def set_distributed(self, rank, world, group=None, exchange="direct"):
+    def set_distributed(self, rank, world, group=None, exchange="direct", split="layers"):
         """Shard every batch's attention rows and link scores over `world` GPUs of one node (one
         process per GPU, torch.distributed initialised by the caller, NCCL).  Every rank keeps full
         replicas and must be fed the same batches; results are identical on all ranks.
 
         exchange="direct": the layer-1 rows travel by peer stores over NVLink into exchange buffers that
         the ranks map into each other through CUDA IPC (handles are swapped here, once);
-        exchange="nccl": one all-gather per batch instead."""
+        exchange="nccl": one all-gather per batch instead.
+        split="layers" (direct exchange only): the first world // 2 ranks compute layer 1 and the memory
+        update, the others the top layer and the scores, a batch apart; split="rows": every rank computes
+        its share of the rows of both layers."""
         self._rank, self._world, self._group = int(rank), int(world), group
+        self._layer1_ranks = 0
         self._ws_key = None
         self._desc_ref = None
         self._exchange = None
@@ -297,14 +302,17 @@ class TGN(nn.Module):
                               "are all-gathered with NCCL instead")
                 return
             self.set_exchange(rows, flags, cap, keep, grus, gcap)
+            if split == "layers":
+                self._layer1_ranks = self._world // 2
             dist.barrier(group=group)
 
     @staticmethod
     def exchange_floats(bs, world, k, n_nodes):
-        """Floats per slot of an exchange buffer for batches of up to `bs` edges: `world` blocks of
-        rows_per_rank(3*bs + u_cap) rows, u_cap = min(3*bs*k, n_nodes) being the most uncached
-        neighbours a batch can have (a cold cache on the first batch reaches it)."""
-        return world * shard.rows_per_rank(3 * bs + min(3 * bs * k, n_nodes), world) * _lib.DIM
+        """Floats per slot of an exchange buffer for batches of up to `bs` edges: one block of
+        rows_per_rank(3*bs + u_cap) rows per computing rank (at most `world` of them), u_cap =
+        min(3*bs*k, n_nodes) being the most uncached neighbours a batch can have (a cold cache on the first
+        batch reaches it)."""
+        return (3 * bs + min(3 * bs * k, n_nodes) + world) * _lib.DIM
 
     def set_exchange(self, row_ptrs, flag_ptrs, cap, keep_alive=(), gru_ptrs=None, gru_cap=0):
         """Device addresses, as seen by this process, of every rank's exchange buffer (EXCHANGE_SLOTS *
@@ -371,6 +379,7 @@ class TGN(nn.Module):
                 t.n_prev_plan = h.n_prev.ctypes.data_as(C.POINTER(C.c_int32))
                 t.plan_cap = h.prev_plan.numel()
             t.rank, t.world = self._rank, self._world
+            t.layer1_ranks = self._layer1_ranks
             t.mode = self._mode
             t.input_stream = self._input_stream
             return t
@@ -411,6 +420,7 @@ class TGN(nn.Module):
         t.last_pos = self._last_pos.data_ptr()
         t.epoch_base = self._epoch.ctypes.data_as(C.POINTER(C.c_int64))
         t.rank, t.world = self._rank, self._world
+        t.layer1_ranks = self._layer1_ranks
         t.cand_bitmap = self._cand_bitmap.data_ptr()
         t.mode = self._mode
         t.ctx = self._ctx
@@ -537,8 +547,9 @@ class TGN(nn.Module):
             raise NotImplementedError("the multi-GPU split is built for the two-layer model")
         L = _lib.lib()
         world = self._world
-        rpr = shard.rows_per_rank(3 * b + u_cap, world)
-        b_max = shard.rows_per_rank(b, world)
+        wa = self._layer1_ranks                 # split by layer: only ranks wa.. hold scores
+        rpr = shard.rows_per_rank(3 * b + u_cap, wa if wa else world)
+        b_max = shard.rows_per_rank(b, world - wa)
         s = _lib.stream_ptr(self.device)
         direct = getattr(self, "_exchange", None) is not None
         prob_local = torch.zeros(2 * b_max, device=self.device)
@@ -557,8 +568,8 @@ class TGN(nn.Module):
             _lib.check(L.orca_tgn_eval_batch_sharded(desc, 2, d_i32, d_ts, b, d_plan, n_plan, u_cap, ws.data_ptr(),
                                                      ws.numel(), None, emb1_all.data_ptr(), prob_local.data_ptr(),
                                                      _lib.ptr(emb2_local), self._status.data_ptr(), s))
-        prob = shard.assemble_edges(shard.all_gather_rows(prob_local, self._group), b, 2)
-        emb = shard.assemble_edges(shard.all_gather_rows(emb2_local, self._group), b, 3) if want_emb else None
+        prob = shard.assemble_edges(shard.all_gather_rows(prob_local, self._group)[wa:], b, 2)
+        emb = shard.assemble_edges(shard.all_gather_rows(emb2_local, self._group)[wa:], b, 3) if want_emb else None
         return prob, emb
 
     def check_status(self):
@@ -640,7 +651,14 @@ class TGN(nn.Module):
         off_i32 = np.zeros(nb, dtype=np.int64)
         np.cumsum(ints[:-1], out=off_i32[1:])
         off_ts = np.arange(nb, dtype=np.int64) * bs
-        b_loc = (b.astype(np.int64) - rank + world - 1) // world if world > 1 else b.astype(np.int64)
+        wa = self._layer1_ranks if world > 1 else 0     # split by layer: ranks wa.. hold the scores
+        wb, rb = world - wa, rank - wa
+        if world == 1:
+            b_loc = b.astype(np.int64)
+        elif rb < 0:
+            b_loc = np.zeros(nb, dtype=np.int64)
+        else:
+            b_loc = (b.astype(np.int64) - rb + wb - 1) // wb
         off_prob = np.zeros(nb, dtype=np.int64)
         np.cumsum(2 * b_loc[:-1], out=off_prob[1:])
         n_scores = int(2 * b_loc.sum())
@@ -714,19 +732,20 @@ class TGN(nn.Module):
                     o, n, lo = int(off_prob[i]), int(b[i]), i * bs
                     pos[lo:lo + n], neg[lo:lo + n] = local[o:o + n], local[o + n:o + 2 * n]
             return pos, neg
-        # every rank holds the scores of its edges (edge e of a batch: rank e % world): one exchange per epoch
+        # every scoring rank holds the scores of its edges (edge e of a batch: scoring rank e % wb): one exchange
+        # per epoch
         import torch.distributed as dist
-        most = 2 * int(((b.astype(np.int64) + world - 1) // world).sum())
+        most = 2 * int(((b.astype(np.int64) + wb - 1) // wb).sum())
         mine = torch.zeros(most, dtype=torch.float32, device=self.device)
         mine[:n_scores] = dev["prob"][:n_scores]
         every = shard.all_gather_rows(mine, self._group).cpu().numpy()
-        for r in range(world):
-            bl = (b.astype(np.int64) - r + world - 1) // world
+        for r in range(wb):
+            bl = (b.astype(np.int64) - r + wb - 1) // wb
             o = 0
             for i in range(nb):
                 n, lo = int(bl[i]), i * bs
-                pos[lo + r:lo + int(b[i]):world] = every[r, o:o + n]
-                neg[lo + r:lo + int(b[i]):world] = every[r, o + n:o + 2 * n]
+                pos[lo + r:lo + int(b[i]):wb] = every[wa + r, o:o + n]
+                neg[lo + r:lo + int(b[i]):wb] = every[wa + r, o + n:o + 2 * n]
                 o += 2 * n
         return pos, neg
 

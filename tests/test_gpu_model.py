@@ -329,13 +329,16 @@ def test_unsupported_modes_fail_loudly():
         tgn.compute_edge_probabilities(src, dst, dst, ts, eidx, 10, True, True, None)
 
 
-@pytest.mark.parametrize("world,direct", [(4, False), (8, False), (2, True), (8, True), (3, "split")])
+@pytest.mark.parametrize("world,direct", [(4, False), (8, False), (2, True), (8, True), (3, "split"), (2, "layers"),
+                                          (5, "layers"), (8, "layers")])
 def test_sharded_entry_points_with_emulated_ranks(world, direct):
     """The row/edge split of the multi-GPU path for more ranks than GPUs at hand: every rank is a model
     replica of its own on this GPU, the two phases are called rank after rank through the C ABI (all ranks'
     phase 1 before any phase 2, so no kernel ever waits for a later launch).  The exchange between the
     phases is a stack of the ranks' layer-1 rows, or -- direct -- the library's own peer stores into every
-    replica's exchange buffer.  Scores and state must equal the unsharded run."""
+    replica's exchange buffer.  "split": the memory update is split by node too; "layers": the first half of
+    the ranks computes layer 1 and the memory update, the second half the top layer and the scores.  Scores
+    and state must equal the unsharded run."""
     from orca_b200 import _lib, shard
     L = _lib.lib()
     g = graph("t_nb2")
@@ -359,11 +362,15 @@ def test_sharded_entry_points_with_emulated_ranks(world, direct):
         flags = [torch.zeros(_lib.FLAG_WORDS, dtype=torch.int32, device=dev) for _ in range(world)]
         # "split": the memory update is split by node as well, its rows exchanged the same way
         gcap = 2 * spec.bs * 172
-        grus = [torch.zeros(2 * gcap, device=dev) for _ in range(world)] if direct == "split" else None
+        grus = [torch.zeros(2 * gcap, device=dev) for _ in range(world)] if direct in ("split", "layers") else None
         for m in ranks:
             m.set_exchange([x.data_ptr() for x in bufs], [f.data_ptr() for f in flags], cap, bufs + flags,
                            [x.data_ptr() for x in grus] if grus else None, gcap)
             m._keep_gru = grus
+            if direct == "layers":
+                m._layer1_ranks = world // 2
+    wa = world // 2 if direct == "layers" else 0        # ranks wa.. hold the scores
+    wb = world - wa
     stream = _lib.stream_ptr(dev)
     k = spec.n_degree
     worst = 0.0
@@ -380,7 +387,7 @@ def test_sharded_entry_points_with_emulated_ranks(world, direct):
         for m in ranks:
             desc = m._descriptor(k)
             ws, u_cap = m._workspace(n, k)
-            rpr = shard.rows_per_rank(3 * n + u_cap, world)
+            rpr = shard.rows_per_rank(3 * n + u_cap, wa if wa else world)
             emb1 = torch.zeros(rpr, 172, device=dev)
             _lib.check(L.orca_tgn_eval_batch_sharded(desc, 1, ints.data_ptr(), tsd.data_ptr(), n, d_plan, len(pl),
                                                      u_cap, ws.data_ptr(), ws.numel(),
@@ -393,16 +400,17 @@ def test_sharded_entry_points_with_emulated_ranks(world, direct):
         q = torch.zeros(n, device=dev)
         for r, m in enumerate(ranks):
             desc, ws, u_cap = ctx[r]
-            n_loc = shard.local_count(n, r, world)
-            prob = torch.zeros(2 * shard.rows_per_rank(n, world), device=dev)
+            n_loc = shard.local_count(n, r - wa, wb) if r >= wa else 0
+            prob = torch.zeros(2 * shard.rows_per_rank(n, wb), device=dev)
             _lib.check(L.orca_tgn_eval_batch_sharded(desc, 2, ints.data_ptr(), tsd.data_ptr(), n, d_plan, len(pl),
                                                      u_cap, ws.data_ptr(), ws.numel(), None,
                                                      None if direct else emb1_all.data_ptr(),
                                                      prob.data_ptr(), None, m._status.data_ptr(), stream))
             m.check_status()
-            e = torch.arange(r, n, world, device=dev)
-            p[e] = prob[:n_loc]
-            q[e] = prob[n_loc:2 * n_loc]
+            if r >= wa:
+                e = torch.arange(r - wa, n, wb, device=dev)
+                p[e] = prob[:n_loc]
+                q[e] = prob[n_loc:2 * n_loc]
         worst = max(worst, float((p - p_ref.view(-1)).abs().max()), float((q - q_ref.view(-1)).abs().max()))
     assert worst < 1e-6, worst
     for m in ranks:
