@@ -45,6 +45,8 @@ def parse():
     ap.add_argument("--split", default="layers", choices=["layers", "rows"],
                     help="N > 1: layers = the first N // 2 GPUs compute layer 1 and the memory update, the others "
                          "the top layer and the scores (default); rows = every GPU its share of both layers' rows")
+    ap.add_argument("--layer1-ranks", type=int, default=None,
+                    help="--split layers: how many GPUs compute layer 1 and the memory update (default N // 2)")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="N > 1: strong = the workload's batch split over the GPUs (default); weak = a batch of "
                          "bs edges PER GPU, i.e. the same stream cut into batches of bs * N edges")
@@ -229,7 +231,7 @@ def run_ours(a):
     L = _lib.lib()
     g, neg, plan, tgn = build_setup(a, device, quiet=rank != 0)
     if world > 1:
-        tgn.set_distributed(rank, world, exchange=a.exchange, split=a.split)
+        tgn.set_distributed(rank, world, exchange=a.exchange, split=a.split, layer1_ranks=a.layer1_ranks)
     spec = g.spec
     K, W = a.steps, a.warmup
     nb_avail = len(plan)

@@ -240,7 +240,7 @@ class TGN(nn.Module):
         torch.cuda.synchronize(self.device)
         return self._ws[off: off + 4 * n_rows].view(torch.int32).cpu().numpy()
 
-    def set_distributed(self, rank, world, group=None, exchange="direct", split="layers"):
+    def set_distributed(self, rank, world, group=None, exchange="direct", split="layers", layer1_ranks=None):
         """Shard every batch's attention rows and link scores over `world` GPUs of one node (one
         process per GPU, torch.distributed initialised by the caller, NCCL).  Every rank keeps full
         replicas and must be fed the same batches; results are identical on all ranks.
@@ -248,9 +248,9 @@ class TGN(nn.Module):
         exchange="direct": the layer-1 rows travel by peer stores over NVLink into exchange buffers that
         the ranks map into each other through CUDA IPC (handles are swapped here, once);
         exchange="nccl": one all-gather per batch instead.
-        split="layers" (direct exchange only): the first world // 2 ranks compute layer 1 and the memory
-        update, the others the top layer and the scores, a batch apart; split="rows": every rank computes
-        its share of the rows of both layers."""
+        split="layers" (direct exchange only): the first `layer1_ranks` ranks (default world // 2) compute
+        layer 1 and the memory update, the others the top layer and the scores, a batch apart;
+        split="rows": every rank computes its share of the rows of both layers."""
         self._rank, self._world, self._group = int(rank), int(world), group
         self._layer1_ranks = 0
         self._ws_key = None
@@ -303,7 +303,10 @@ class TGN(nn.Module):
                 return
             self.set_exchange(rows, flags, cap, keep, grus, gcap)
             if split == "layers":
-                self._layer1_ranks = self._world // 2
+                a = self._world // 2 if layer1_ranks is None else int(layer1_ranks)
+                if not 0 < a < self._world:
+                    raise ValueError("layer1_ranks must lie between 1 and world - 1")
+                self._layer1_ranks = a
             dist.barrier(group=group)
 
     @staticmethod
