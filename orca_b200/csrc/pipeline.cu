@@ -17,6 +17,12 @@
 // Index-side buffers and the layer-1 output exist twice (batch parity); a parity is reused only when
 // the batch that used it has completed.  All four lanes collapse onto the caller's stream while tracing
 // or when look-ahead is switched off.
+//
+// Several GPUs of one node share a batch (orca_tgn_eval_batch_sharded, one process per GPU, replicated
+// tables): either every rank takes its share of the rows of both layers, or -- orca_tgn_t.layer1_ranks --
+// the first ranks run the layer-1 and side lanes and the others the caller's-stream part, a batch apart.
+// In both, the rows a rank computes reach the other ranks by peer stores from the epilogue of the kernel
+// that computes them, followed by a flag; every wait on a flag is bounded.
 #include <algorithm>
 #include <cstring>
 #include <vector>
