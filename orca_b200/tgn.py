@@ -223,6 +223,9 @@ class TGN(nn.Module):
             self.__dict__["_ctx"] = None
             try:
                 _lib.lib().orca_ctx_destroy(ctx)
+                for base, off in self.__dict__.get("_ipc_open") or []:
+                    _lib.lib().orca_ipc_close(base, off)
+                self.__dict__["_ipc_open"] = []
             except Exception:      # interpreter shutdown
                 pass
 
@@ -251,6 +254,7 @@ class TGN(nn.Module):
         split="layers" (direct exchange only): the first `layer1_ranks` ranks (default world // 2) compute
         layer 1 and the memory update, the others the top layer and the scores, a batch apart;
         split="rows": every rank computes its share of the rows of both layers."""
+        self._release_exchange()
         self._rank, self._world, self._group = int(rank), int(world), group
         self._layer1_ranks = 0
         self._ws_key = None
@@ -286,6 +290,7 @@ class TGN(nn.Module):
                             out = C.c_void_p(0)
                             _lib.check(L.orca_ipc_open(h, handles[r][1], C.byref(out)))
                             base = out.value
+                            self._ipc_open.append((base, handles[r][1]))
                         rows.append(base)
                         grus.append(base + 4 * _lib.EXCHANGE_SLOTS * cap)
                         flags.append(base + 4 * (_lib.EXCHANGE_SLOTS * cap + 2 * gcap))
@@ -308,6 +313,25 @@ class TGN(nn.Module):
                     raise ValueError("layer1_ranks must lie between 1 and world - 1")
                 self._layer1_ranks = a
             dist.barrier(group=group)
+
+    def _release_exchange(self):
+        """Lets go of the exchange buffers of an earlier set_distributed call: every rank first finishes
+        what it has enqueued (peers may still be storing into this rank's buffer, and this rank into
+        theirs), then the mappings of the peers' buffers are closed and the own buffer is dropped."""
+        opened = self.__dict__.get("_ipc_open") or []
+        if self.__dict__.get("_exchange") is not None:
+            torch.cuda.synchronize(self.device)
+            if self._world > 1:
+                import torch.distributed as dist
+                if dist.is_available() and dist.is_initialized():
+                    dist.barrier(group=self._group)
+        if opened:
+            L = _lib.lib()
+            with torch.cuda.device(self.device):
+                for base, off in opened:
+                    L.orca_ipc_close(base, off)
+        self.__dict__["_ipc_open"] = []
+        self.__dict__["_exchange"] = None
 
     @staticmethod
     def exchange_floats(bs, world, k, n_nodes):

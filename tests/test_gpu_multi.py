@@ -50,6 +50,10 @@ def _worker(rank, world, port, case, out_dir):
         for b, src, dst, ts, eidx in batches(g, scores.shape[0]):
             n = len(src)
             ng = neg[b * spec.bs: b * spec.bs + n]
+            if b == 5:
+                # reconfigured in mid-stream: from the split by layer to the split by rows (the first exchange
+                # buffers are released after a barrier, the peers' mappings closed, new ones opened)
+                tgn.set_distributed(rank, world, split="rows")
             if b == 3:
                 # the embedding API advances the state exactly like the scoring API
                 s_e, d_e, n_e = tgn.compute_temporal_embeddings(src, dst, ng, ts, eidx, spec.n_degree, True, False,
