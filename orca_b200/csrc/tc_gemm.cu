@@ -33,6 +33,12 @@
 // stage ring; all warps then write whole rows with coalesced stores (bias / ReLU / LayerNorm + push /
 // GRU gates applied on the way).
 //
+// The merger of an attention layer (EPI_MERGER) chains a second product behind the first without leaving
+// the SM: the first epilogue applies bias + ReLU to the 128 x 176 accumulator tile, splits it into bf16 head /
+// tail and stores it in shared memory as the A image of (hidden . W2), whose three weight k-blocks are
+// fetched while the first product still runs (k-block 0) and right after it (k-blocks 1, 2); the second
+// product reuses the accumulator columns and ends in the LayerNorm epilogue.
+//
 // Every wait on an mbarrier is bounded; a wait that gives up records ORCA_E_TIMEOUT and the kernel
 // runs to its end (tensor memory is always released).
 #include <algorithm>
@@ -211,7 +217,6 @@ __device__ __forceinline__ void tile_output(const Args &g, const float *tile, co
   }
   constexpr int RB = 4;   // (2 measured the same, 8 spills)
   constexpr int BNv = tile_bn<EPI>();
-  constexpr bool kHidden = EPI == EPI_HIDDEN;
   const int c0 = nt * BNv;
   const int j0 = lane, j1 = lane + 32;
   const int nj = (EPI == EPI_BIAS || EPI == EPI_GRU) ? BNv / 4 : D / 4;
@@ -257,20 +262,6 @@ __device__ __forceinline__ void tile_output(const Args &g, const float *tile, co
           float *o = g.out + (size_t)m[k] * g.out_ld + c0;
           *reinterpret_cast<float4 *>(o + 4 * j0) = a[k];
           if (has1) *reinterpret_cast<float4 *>(o + 4 * j1) = b[k];
-        }
-    } else if (kHidden) {
-#pragma unroll
-      for (int k = 0; k < RB; ++k)
-        if (ok[k] && has0) {
-          const float rvf = ma[k] != 0 ? 1.f : 0.f;
-          float *o = g.out + (size_t)m[k] * D + c0;
-          *reinterpret_cast<float4 *>(o + 4 * j0) =
-              make_float4(fmaxf(a[k].x + rvf * vA.x, 0.f), fmaxf(a[k].y + rvf * vA.y, 0.f),
-                          fmaxf(a[k].z + rvf * vA.z, 0.f), fmaxf(a[k].w + rvf * vA.w, 0.f));
-          if (has1)
-            *reinterpret_cast<float4 *>(o + 4 * j1) =
-                make_float4(fmaxf(b[k].x + rvf * vB.x, 0.f), fmaxf(b[k].y + rvf * vB.y, 0.f),
-                            fmaxf(b[k].z + rvf * vB.z, 0.f), fmaxf(b[k].w + rvf * vB.w, 0.f));
         }
     } else if (EPI == EPI_LAYERNORM) {
       // both moments in one sweep (the row is O(1) after the merger, so E[y^2] - mean^2 loses nothing
@@ -385,8 +376,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     const int r = warp + (THREADS / 32) * lane;
     const int m = m0 + r;
     if (r < BM && m < limit) {
-      if (EPI == EPI_HIDDEN) meta_a = g.row_valid == nullptr ? 1 : g.row_valid[m];
-      if ((EPI == EPI_LAYERNORM || kMerger) && g.push_table != nullptr) {
+      if (kMerger && g.push_table != nullptr) {
         meta_b = g.push_ids[m];
         if (g.push_win != nullptr) meta_a = g.push_win[m];
       }
@@ -434,7 +424,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
   // (called after the tile's first stage has been requested: the lookup is two dependent loads and its
   // result is only needed by the output pass)
   auto push_winners = [&](int m0) {
-    if ((EPI == EPI_LAYERNORM || kMerger) && g.push_table != nullptr && g.push_win == nullptr) {
+    if (kMerger && g.push_table != nullptr && g.push_win == nullptr) {
       // winners by record; only for live rows: the id of a row past the live count is not a valid index
       const int r = warp + (THREADS / 32) * lane;
       const int m = m0 + r;
@@ -470,10 +460,9 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     for (int i = tid - 128; i < BN; i += 64) {
       const bool in = i < lim && i < BNv;
       s_bias[i] = in ? g.bias[nt * BNv + i] : 0.f;
-      const float *v1 = (EPI == EPI_HIDDEN || kMerger) ? g.bias2
-                        : EPI == EPI_LAYERNORM ? g.ln_w : EPI == EPI_SCORE ? g.w2 : nullptr;
+      const float *v1 = kMerger ? g.bias2 : EPI == EPI_SCORE ? g.w2 : nullptr;
       s_v1[i] = (v1 != nullptr && in) ? v1[nt * BNv + i] : 0.f;
-      s_v2[i] = (EPI == EPI_LAYERNORM && in) ? g.ln_b[i] : 0.f;
+      s_v2[i] = 0.f;
       if (kMerger) {
         s_out[0][i] = in ? g.bias_out[i] : 0.f;
         s_out[1][i] = in ? g.ln_w[i] : 0.f;
@@ -694,7 +683,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(Args g) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
   }
-  if ((EPI == EPI_LAYERNORM || EPI == EPI_GRU || kMerger) && g.peer.world > 0) {
+  if ((EPI == EPI_GRU || kMerger) && g.peer.world > 0) {
     // every CTA (with or without rows) checks out; the last one posts the batch's sequence number to all
     // ranks, after every CTA's peer stores have been fenced system-wide
     __threadfence_system();

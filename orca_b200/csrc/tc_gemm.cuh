@@ -60,9 +60,9 @@ struct PeerOut {
 };
 
 // EPI_MERGER: hidden = relu(A . W + bias + valid * bias2) kept on the SM, then LayerNorm(hidden . W2 + bias_out)
-// with the LAYERNORM epilogue (push, peer fan-out).  EPI_HIDDEN / EPI_LAYERNORM name the two halves (the
-// epilogue code is shared); only the merger is launched.
-enum Epilogue { EPI_BIAS = 0, EPI_HIDDEN = 1, EPI_LAYERNORM = 2, EPI_GRU = 3, EPI_SCORE = 4, EPI_MERGER = 5 };
+// with the LayerNorm epilogue (push, peer fan-out).  EPI_LAYERNORM names that epilogue inside the kernel; it
+// is not a kernel of its own (values 1 and 2 were the two separate kernels the merger replaced).
+enum Epilogue { EPI_BIAS = 0, EPI_LAYERNORM = 2, EPI_GRU = 3, EPI_SCORE = 4, EPI_MERGER = 5 };
 
 struct Args {
   RowSrc a0, a1;             // a1.width == 0 when unused
