@@ -724,9 +724,14 @@ class TGN(nn.Module):
         stream = torch.cuda.current_stream(self.device)
         # The stream goes to the library in chunks of a few batches: while the GPU works on one chunk the next
         # one is packed into its own part of the pinned image (the library never waits for the host).
-        chunk = 8
-        for i0 in range(0, nb, chunk):
-            i1 = min(nb, i0 + chunk)
+        # (The first chunks are short -- 1, 2, 4 batches -- so that the GPU starts while most of the stream is
+        # still being packed.)
+        bounds, i0, chunk = [], 0, 1
+        while i0 < nb:
+            bounds.append((i0, min(nb, i0 + chunk)))
+            i0 += chunk
+            chunk = min(8, 2 * chunk)
+        for i0, i1 in bounds:
             if int(b[-1]) == bs and cache_plan is None:
                 lo, up = i0 * bs, i1 * bs
                 v = hi[int(off_i32[i0]):int(off_i32[i0]) + 4 * (up - lo)].reshape(i1 - i0, 4, bs)
