@@ -704,7 +704,7 @@ class TGN(nn.Module):
         h_ts = pinned("ts", E, torch.float64)
         h_prob = pinned("prob", n_scores, torch.float32)
         hi = h_i32.numpy()
-        h_ts.numpy()[:E] = timestamps
+        hts = h_ts.numpy()
         if self.n_layers == 2 and cache_plan is not None:
             h = self.embedding_module.histories[0]
             most = int(n_plan.max())
@@ -732,6 +732,7 @@ class TGN(nn.Module):
             i0 += chunk
             chunk = min(8, 2 * chunk)
         for i0, i1 in bounds:
+            hts[i0 * bs:min(E, i1 * bs)] = timestamps[i0 * bs:min(E, i1 * bs)]
             if int(b[-1]) == bs and cache_plan is None:
                 lo, up = i0 * bs, i1 * bs
                 v = hi[int(off_i32[i0]):int(off_i32[i0]) + 4 * (up - lo)].reshape(i1 - i0, 4, bs)
